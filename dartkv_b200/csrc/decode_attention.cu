@@ -1,0 +1,337 @@
+// Fused single-token decode attention over the device-resident paged cache.
+//
+// Split-K over the token range: every (batch, KV head, split) block keeps an fp32 online-softmax
+// state (m, l, acc) for the query heads of its KV head (GQA group) and writes one partial; a merge
+// kernel combines the partials, normalizes and casts.  Numerics follow the reference's
+// page-streaming attention (src/dart/attention.py:60-87): dequantize to the cache dtype, fp32
+// logits q.k * scale, fp32 online softmax, acc / max(l, 1e-20), cast to the query dtype.
+//
+// This file holds the generic kernel (any page geometry, bit width, dtype; CUDA-core fp32 math)
+// and the merge; the tensor-core kernel for the headline geometry is in decode_fast.cu.
+
+#include "common.cuh"
+
+#define GEN_THREADS 128
+#define GEN_TILE 32
+#define GEN_MAX_REP 16
+#define GEN_MAX_D 256
+
+__device__ __forceinline__ int gen_find_page(const dartkv_cache_desc& d, int pages, int t) {
+  int lo = 0, hi = pages - 1;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (d.page_start[mid] + d.page_tokens[mid] > t) hi = mid; else lo = mid + 1;
+  }
+  return lo;
+}
+
+// Tokens [sink_tokens, fast_range_end) are whole pages packed on both the key and the value side.
+__host__ __device__ __forceinline__ int dartkv_fast_range_end(int sink_tokens, int page_size, int k_end, int v_end,
+                                                              int sink_filled) {
+  int packed = min(k_end, v_end);
+  if (packed <= sink_tokens) return sink_filled;
+  return sink_tokens + (packed - sink_tokens) / page_size * page_size;
+}
+
+struct GenericArgs {
+  const void* q;
+  int q_dt, query_heads, flavour;
+  float scale;
+  int tok_begin, tok_end;   // tok_end < 0: up to the number of tokens seen
+  int chunk, split_base, total_splits;
+  float* part_m;
+  float* part_l;
+  float* part_acc;
+};
+
+__global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cache_desc d, GenericArgs a) {
+  extern __shared__ float smem[];
+  const int D = d.head_dim, DP = D + 1;
+  const int rep = a.query_heads / d.kv_heads;
+  float* s_q = smem;                              // [rep][D]
+  float* s_tile = s_q + rep * D;                  // [GEN_TILE][D+1]
+  float* s_p = s_tile + GEN_TILE * DP;            // [rep][GEN_TILE]
+  float* s_alpha = s_p + rep * GEN_TILE;          // [rep]
+  float* s_m = s_alpha + rep;                     // [rep]
+  float* s_l = s_m + rep;                         // [rep]
+  int* s_slot = reinterpret_cast<int*>(s_l + rep);// [D]
+
+  const int bh = blockIdx.x, split = blockIdx.y;
+  const int b = bh / d.kv_heads, h = bh % d.kv_heads;
+  const int tid = threadIdx.x;
+  const int seen = d.state[0], pages = d.state[1], k_end = d.state[2], v_end = d.state[3], sink_filled = d.state[4];
+  const int end = a.tok_end < 0 ? seen : min(a.tok_end, seen);
+  // tok_begin < 0: start where the tensor-core kernel stops (last full page packed on both sides)
+  int begin = a.tok_begin;
+  if (begin < 0) begin = dartkv_fast_range_end(d.sink_tokens, d.page_size, k_end, v_end, sink_filled);
+  const int lo = begin + split * a.chunk;
+  const int hi = (int)min((int64_t)lo + a.chunk, (int64_t)end);
+
+  for (int i = tid; i < rep * D; i += GEN_THREADS) {
+    int r = i / D, c = i % D;
+    s_q[i] = load_f(a.q, a.q_dt, ((int64_t)b * a.query_heads + h * rep + r) * D + c);
+  }
+  if (tid < rep) { s_m[tid] = -INFINITY; s_l[tid] = 0.0f; }
+  float acc[GEN_MAX_REP][GEN_MAX_D / GEN_THREADS];
+#pragma unroll
+  for (int r = 0; r < GEN_MAX_REP; ++r)
+#pragma unroll
+    for (int k = 0; k < GEN_MAX_D / GEN_THREADS; ++k) acc[r][k] = 0.0f;
+  __syncthreads();
+
+  int t = lo;
+  while (t < hi) {
+    // ---- locate the key segment that holds token t
+    int seg_end, kind, page_first = 0, page_n = 0;
+    const uint8_t* page = nullptr;
+    if (t < sink_filled) {
+      kind = 0; seg_end = min(hi, sink_filled);
+    } else if (t < k_end) {
+      kind = 1;
+      int pg = gen_find_page(d, pages, t);
+      page_first = d.page_start[pg];
+      page_n = d.page_tokens[pg];
+      seg_end = min(hi, page_first + page_n);
+      page = d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes;
+      if (d.key_mode == DARTKV_MIXED_PAGE) {
+        __syncthreads();
+        for (int c = tid; c < D; c += GEN_THREADS) s_slot[c] = -1;
+        __syncthreads();
+        const int32_t* idx = reinterpret_cast<const int32_t*>(page + d.key_off_index);
+        for (int k = tid; k < d.promoted; k += GEN_THREADS) {
+          int c = idx[k];
+          if (c >= 0 && c < D) s_slot[c] = k;
+        }
+        __syncthreads();
+      }
+    } else {
+      kind = 2; seg_end = hi;
+    }
+    for (int tile0 = t; tile0 < seg_end; tile0 += GEN_TILE) {
+      const int nt = min(GEN_TILE, seg_end - tile0);
+      // ---- K tile, dequantized to the cache dtype
+      for (int i = tid; i < nt * D; i += GEN_THREADS) {
+        int tt = i / D, c = i % D, tok = tile0 + tt;
+        float v;
+        if (kind == 0) v = load_f(d.k_sink, d.dtype, ((int64_t)bh * d.sink_tokens + tok) * D + c);
+        else if (kind == 2) v = load_f(d.k_ring, d.dtype, ((int64_t)bh * d.ring_tokens + (tok % d.ring_tokens)) * D + c);
+        else {
+          const int Gk = d.key_group, G = ceil_div(page_n, Gk), j = tok - page_first, g = j / Gk;
+          float s = load_f(page + d.key_off_scale, d.md_dtype, c * G + g);
+          float z = load_f(page + d.key_off_zero, d.md_dtype, c * G + g);
+          uint32_t code;
+          if (d.key_mode == DARTKV_MIXED_PAGE) {
+            const int pb = ceil_div(Gk, 4), jj = j % Gk, slot = s_slot[c];
+            code = (page[(c * G + g) * pb + jj / 4] >> ((jj % 4) * 2)) & 3u;
+            if (slot >= 0) code |= ((page[d.key_off_high + (slot * G + g) * pb + jj / 4] >> ((jj % 4) * 2)) & 3u) << 2;
+          } else {
+            const int bits = d.key_bits, vpb = 8 / bits, row_bytes = ceil_div(G * Gk, vpb);
+            code = (page[(int64_t)c * row_bytes + j / vpb] >> ((j % vpb) * bits)) & ((1u << bits) - 1u);
+          }
+          v = affine_restore((float)code, s, z, d.md_dtype, d.dtype, a.flavour);
+        }
+        s_tile[tt * DP + c] = v;
+      }
+      __syncthreads();
+      // ---- logits
+      for (int i = tid; i < rep * nt; i += GEN_THREADS) {
+        int r = i / nt, tt = i % nt;
+        const float* qr = s_q + r * D;
+        const float* kr = s_tile + tt * DP;
+        float dot = 0.0f;
+        for (int c = 0; c < D; ++c) dot = fmaf(qr[c], kr[c], dot);
+        s_p[r * GEN_TILE + tt] = dot * a.scale;
+      }
+      __syncthreads();
+      // ---- online softmax state per query head
+      if (tid < rep) {
+        float* pr = s_p + tid * GEN_TILE;
+        float mx = -INFINITY;
+        for (int tt = 0; tt < nt; ++tt) mx = fmaxf(mx, pr[tt]);
+        float m_old = s_m[tid], m_new = fmaxf(m_old, mx);
+        float alpha = expf(m_old - m_new);
+        float sum = 0.0f;
+        for (int tt = 0; tt < nt; ++tt) { float p = expf(pr[tt] - m_new); pr[tt] = p; sum += p; }
+        s_alpha[tid] = alpha;
+        s_m[tid] = m_new;
+        s_l[tid] = s_l[tid] * alpha + sum;
+      }
+      __syncthreads();
+      // ---- V tile
+      for (int i = tid; i < nt * D; i += GEN_THREADS) {
+        int tt = i / D, c = i % D, tok = tile0 + tt;
+        float v;
+        if (tok < sink_filled) v = load_f(d.v_sink, d.dtype, ((int64_t)bh * d.sink_tokens + tok) * D + c);
+        else if (tok >= v_end) v = load_f(d.v_ring, d.dtype, ((int64_t)bh * d.ring_tokens + (tok % d.ring_tokens)) * D + c);
+        else {
+          int64_t row = (int64_t)bh * d.max_value_tokens + (tok - d.sink_tokens);
+          const int bits = d.value_bits, vpb = 8 / bits, g = c / d.value_group;
+          uint32_t code = (d.v_codes[row * d.value_row_bytes + c / vpb] >> ((c % vpb) * bits)) & ((1u << bits) - 1u);
+          float s = load_f(d.v_meta, d.md_dtype, (row * 2 + 0) * d.value_groups + g);
+          float z = load_f(d.v_meta, d.md_dtype, (row * 2 + 1) * d.value_groups + g);
+          v = affine_restore((float)code, s, z, d.md_dtype, d.dtype, a.flavour);
+        }
+        s_tile[tt * DP + c] = v;
+      }
+      __syncthreads();
+      // ---- accumulate
+#pragma unroll
+      for (int k = 0; k < GEN_MAX_D / GEN_THREADS; ++k) {
+        int c = tid + k * GEN_THREADS;
+        if (c < D) {
+#pragma unroll
+          for (int r = 0; r < GEN_MAX_REP; ++r) {
+            if (r < rep) {
+              float sum = 0.0f;
+              const float* pr = s_p + r * GEN_TILE;
+              for (int tt = 0; tt < nt; ++tt) sum = fmaf(pr[tt], s_tile[tt * DP + c], sum);
+              acc[r][k] = acc[r][k] * s_alpha[r] + sum;
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    t = seg_end;
+  }
+
+  const int slot = a.split_base + split;
+#pragma unroll
+  for (int r = 0; r < GEN_MAX_REP; ++r) {
+    if (r < rep) {
+      int64_t row = ((int64_t)b * a.query_heads + h * rep + r) * a.total_splits + slot;
+      if (tid == 0) { a.part_m[row] = s_m[r]; a.part_l[row] = s_l[r]; }
+#pragma unroll
+      for (int k = 0; k < GEN_MAX_D / GEN_THREADS; ++k) {
+        int c = tid + k * GEN_THREADS;
+        if (c < D) a.part_acc[row * D + c] = acc[r][k];
+      }
+    }
+  }
+}
+
+// one block per (batch, query head): combine split partials, normalize, cast
+__global__ void decode_merge_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
+                                    const float* __restrict__ part_acc, int splits, int D, void* out, int out_dt) {
+  int64_t row = blockIdx.x;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_m[row * splits + s]);
+  float l = 0.0f;
+  for (int s = 0; s < splits; ++s) {
+    float ms = part_m[row * splits + s];
+    if (ms != -INFINITY) l += part_l[row * splits + s] * expf(ms - m);
+  }
+  float inv = 1.0f / fmaxf(l, 1e-20f);
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float acc = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+      float ms = part_m[row * splits + s];
+      if (ms != -INFINITY) acc += part_acc[(row * splits + s) * D + c] * expf(ms - m);
+    }
+    store_f(out, out_dt, row * D + c, acc * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+struct DecodeLayout {
+  int generic_splits, generic_chunk;   // generic kernel over the whole range (fallback)
+  int fast;                            // 1: tensor-core kernel handles the packed pages
+  int fast_splits, fast_pages_per_split;
+  int total_splits;
+};
+
+int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
+int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
+                              int flavour, int splits, int pages_per_split, int split_base, int total_splits,
+                              float* part_m, float* part_l, float* part_acc, cudaStream_t stream);
+
+static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int query_heads, int max_tokens) {
+  DecodeLayout L{};
+  const int bh = d->batch * d->kv_heads;
+  const int target_blocks = 148 * 4;
+  L.fast = dartkv_decode_fast_supported(d, q_dtype, query_heads);
+  if (L.fast) {
+    int max_pages = max(1, (max_tokens - d->sink_tokens) / d->page_size);
+    int want = max(1, (target_blocks + bh - 1) / bh);
+    L.fast_splits = min(want, max_pages);
+    L.fast_pages_per_split = (max_pages + L.fast_splits - 1) / L.fast_splits;
+    L.fast_splits = (max_pages + L.fast_pages_per_split - 1) / L.fast_pages_per_split;
+    L.total_splits = L.fast_splits + 2;   // + sink prefix + dense tail, each one generic split
+    L.generic_splits = 0;
+    L.generic_chunk = 0;
+  } else {
+    int max_splits = max(1, (max_tokens + 63) / 64);
+    int want = max(1, (target_blocks + bh - 1) / bh);
+    L.generic_splits = min(want, max_splits);
+    int chunk = (max_tokens + L.generic_splits - 1) / L.generic_splits;
+    L.generic_chunk = max(GEN_TILE, (chunk + GEN_TILE - 1) / GEN_TILE * GEN_TILE);
+    L.generic_splits = max(1, (max_tokens + L.generic_chunk - 1) / L.generic_chunk);
+    L.total_splits = L.generic_splits;
+  }
+  return L;
+}
+
+extern "C" int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* d, int query_heads, int max_tokens) {
+  if (!d || query_heads <= 0 || max_tokens <= 0) return 0;
+  // the split count does not depend on the query dtype except through fast-path eligibility; take the larger
+  int64_t best = 0;
+  for (int dt = 0; dt < 3; ++dt) {
+    DecodeLayout L = decode_layout(d, dt, query_heads, max_tokens);
+    int64_t rows = (int64_t)d->batch * query_heads * L.total_splits;
+    int64_t bytes = rows * (2 + d->head_dim) * (int64_t)sizeof(float);
+    if (bytes > best) best = bytes;
+  }
+  return best;
+}
+
+extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads,
+                                       float scale, int flavour, int max_tokens, void* workspace,
+                                       int64_t workspace_bytes, void* out, void* stream_) {
+  DARTKV_REQUIRE(d != nullptr, "null descriptor");
+  DARTKV_REQUIRE(query && out && workspace, "decode_attention received a null pointer");
+  DARTKV_REQUIRE(dartkv_valid_dtype(q_dtype), "query must be f32, f16 or bf16");
+  DARTKV_REQUIRE(query_heads > 0 && query_heads % d->kv_heads == 0, "query heads must be divisible by cache KV heads");
+  DARTKV_REQUIRE(max_tokens > 0, "cache is empty");
+  DARTKV_REQUIRE(flavour == DARTKV_DEQUANT_PER_OP || flavour == DARTKV_DEQUANT_FP32, "unknown dequant flavour %d", flavour);
+  const int rep = query_heads / d->kv_heads;
+  DARTKV_REQUIRE(rep <= GEN_MAX_REP, "at most %d query heads per KV head are supported", GEN_MAX_REP);
+  DARTKV_REQUIRE(d->head_dim <= GEN_MAX_D, "decode attention supports head_dim up to %d", GEN_MAX_D);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  DecodeLayout L = decode_layout(d, q_dtype, query_heads, max_tokens);
+  const int64_t rows = (int64_t)d->batch * query_heads * L.total_splits;
+  DARTKV_REQUIRE(workspace_bytes >= rows * (2 + d->head_dim) * (int64_t)sizeof(float),
+                 "decode workspace too small: need %lld bytes", (long long)(rows * (2 + d->head_dim) * sizeof(float)));
+  float* part_m = reinterpret_cast<float*>(workspace);
+  float* part_l = part_m + rows;
+  float* part_acc = part_l + rows;
+  const int bh = d->batch * d->kv_heads;
+  const int D = d->head_dim;
+  size_t smem = ((size_t)rep * D + (size_t)GEN_TILE * (D + 1) + (size_t)rep * GEN_TILE + 3 * rep) * sizeof(float) +
+                (size_t)D * sizeof(int);
+  GenericArgs a;
+  a.q = query; a.q_dt = q_dtype; a.query_heads = query_heads; a.flavour = flavour; a.scale = scale;
+  a.total_splits = L.total_splits; a.part_m = part_m; a.part_l = part_l; a.part_acc = part_acc;
+  if (smem > 48 * 1024)
+    DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (L.fast) {
+    int rc = dartkv_decode_fast_launch(d, query, q_dtype, query_heads, scale, flavour, L.fast_splits,
+                                       L.fast_pages_per_split, 0, L.total_splits, part_m, part_l, part_acc, stream);
+    if (rc) return rc;
+    // dense sink prefix and dense tail (tokens past the last full packed page) as one generic split each
+    a.tok_begin = 0; a.tok_end = d->sink_tokens; a.chunk = max(1, d->sink_tokens); a.split_base = L.fast_splits;
+    decode_generic_kernel<<<dim3(bh, 1), GEN_THREADS, smem, stream>>>(*d, a);
+    DARTKV_LAUNCH_OK("decode_generic_kernel (sink)");
+    a.tok_begin = -1; a.tok_end = -1; a.chunk = 1 << 30; a.split_base = L.fast_splits + 1;
+    decode_generic_kernel<<<dim3(bh, 1), GEN_THREADS, smem, stream>>>(*d, a);
+    DARTKV_LAUNCH_OK("decode_generic_kernel (tail)");
+  } else {
+    a.tok_begin = 0; a.tok_end = -1; a.chunk = L.generic_chunk; a.split_base = 0;
+    DARTKV_REQUIRE(L.generic_splits <= 65535, "too many splits");
+    decode_generic_kernel<<<dim3(bh, L.generic_splits), GEN_THREADS, smem, stream>>>(*d, a);
+    DARTKV_LAUNCH_OK("decode_generic_kernel");
+  }
+  decode_merge_kernel<<<(unsigned)((int64_t)d->batch * query_heads), 128, 0, stream>>>(part_m, part_l, part_acc,
+                                                                                        L.total_splits, D, out, q_dtype);
+  DARTKV_LAUNCH_OK("decode_merge_kernel");
+  return DARTKV_OK;
+}

@@ -1,0 +1,102 @@
+"""Fused single-token decode attention over packed pages (reference ``fused_dart_attention``).
+
+Mirrors ``src/dart/fused_attention.py:654-771``: same signature and validation, but one
+split-K kernel walks the cache's device-side page metadata instead of a Python loop that
+launches one Triton program per page.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import LIB, check, ptr, require_cuda, stream_ptr
+from .cache import DartKVCache
+from .page_table import DartPageRun, DartPageTable
+
+
+def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional[float] = None,
+                     flavour: int = _lib.DEQUANT_PER_OP, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One query token per (batch, query head): ``query`` and the result are ``[B, Hq, D]``."""
+
+    if cache.shape is None or cache.seen_tokens == 0:
+        raise ValueError("cache is empty")
+    batch, kv_heads, seen, head_dim = cache.shape
+    if query.ndim != 3 or query.shape[0] != batch or query.shape[-1] != head_dim:
+        raise ValueError("query batch and head_dim must match the cache")
+    if query.shape[1] % kv_heads:
+        raise ValueError("query heads must be divisible by cache KV heads")
+    if query.dtype not in _lib.DTYPE_CODE:
+        raise TypeError("query must be float32, float16 or bfloat16")
+    device = require_cuda(query)
+    if device != cache._device:
+        raise ValueError("query and cache must be on the same device")
+    q = query.contiguous()
+    if out is None:
+        out = torch.empty_like(q)
+    factor = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    workspace, capacity = cache.decode_workspace(q.shape[1])
+    with torch.cuda.device(device):
+        check(LIB.dartkv_decode_attention(
+            ctypes.byref(cache.descriptor), ptr(q), _lib.DTYPE_CODE[q.dtype], q.shape[1], float(factor), flavour,
+            capacity, ptr(workspace), workspace.numel(), ptr(out), stream_ptr(device)))
+    return out
+
+
+def fused_dart_attention(
+    query: torch.Tensor,
+    cache: DartKVCache,
+    *,
+    scale: Optional[float] = None,
+    fallback: bool = True,
+    page_table: Optional[DartPageTable] = None,
+    page_runs: Optional[Sequence[DartPageRun]] = None,
+) -> torch.Tensor:
+    """Single-token page attention, ``query [B, Hq, 1, D] -> [B, Hq, 1, D]``.
+
+    ``fallback`` only decides what happens for more than one query token (the streamed
+    per-token path, as in the reference); there is no CPU fallback.  ``page_table`` and
+    ``page_runs`` are validated against the cache like the reference does and otherwise
+    unused: the kernel reads the device-resident metadata.
+    """
+
+    if query.ndim != 4:
+        raise ValueError("query must have shape [B, Hq, 1, D]")
+    if query.shape[-2] != 1:
+        if fallback:
+            from .attention import streamed_dart_attention
+
+            return streamed_dart_attention(query, cache, scale=scale)
+        raise ValueError("fused_dart_attention currently supports one query token")
+    if not query.is_cuda:
+        raise RuntimeError("fused_dart_attention requires CUDA (dartkv_b200 has no CPU fallback)")
+    cache_shape = cache.shape
+    if cache_shape is None or cache_shape[2] == 0:
+        raise ValueError("cache is empty")
+    batch, kv_heads, _, head_dim = cache_shape
+    if query.shape[0] != batch or query.shape[-1] != head_dim:
+        raise ValueError("query batch and head_dim must match the cache")
+    if query.shape[1] % kv_heads:
+        raise ValueError("query heads must be divisible by cache KV heads")
+    if page_table is not None:
+        rows = cache.segment_table()
+        if page_table.page_count != len(rows) or page_table.seen_tokens != cache.seen_tokens:
+            raise ValueError("page_table does not describe the current cache segments")
+    if page_runs is not None:
+        starts = set()
+        total = len(cache.segment_table())
+        for run in page_runs:
+            run.validate()
+            if run.first_page_index in starts:
+                raise ValueError("page_runs contain duplicate first_page_index")
+            if run.first_page_index < 0 or run.first_page_index + run.page_count > total:
+                raise ValueError("page_run is outside the current cache page range")
+            starts.add(run.first_page_index)
+    return decode_attention(query[:, :, 0], cache, scale=scale).unsqueeze(2)
+
+
+__all__ = ["fused_dart_attention", "decode_attention"]

@@ -1,0 +1,182 @@
+/*
+ * dartkv_b200 -- C ABI of the B200 (sm_100a) DartKV KV-cache hot path.
+ *
+ * Every entry point is plain C: device pointers, sizes and a CUDA stream passed
+ * as void*.  Nothing here allocates device memory unless stated; the caller
+ * (PyTorch in the Python binding, anything else through FFI) owns every buffer.
+ * All functions return 0 on success or a negative DARTKV_E* code;
+ * dartkv_last_error() returns the message of the calling thread's last failure.
+ *
+ * Each declaration cites the reference interface it replaces, by path inside
+ * the reference project.
+ */
+#ifndef DARTKV_B200_H
+#define DARTKV_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of data and of scale / zero-point metadata */
+enum { DARTKV_F32 = 0, DARTKV_F16 = 1, DARTKV_BF16 = 2 };
+/* key page modes, numbered like src/dart/page_table.py:24-26 */
+enum { DARTKV_DENSE_PAGE = 0, DARTKV_QUANTIZED_PAGE = 1, DARTKV_MIXED_PAGE = 2 };
+/* scale = range / qmax evaluated as a true division (PyTorch CPU) or as range * (1/qmax) (PyTorch CUDA scalar path) */
+enum { DARTKV_DIV_TRUE = 0, DARTKV_DIV_RECIPROCAL = 1 };
+/* dequantization arithmetic: multiply and add each rounded to the metadata dtype
+ * (src/dart/quantization.py:103-106, src/dart/mixed.py:91-94), or one fp32 multiply-add
+ * rounded once to the output dtype (src/dart/triton_ops.py:59,110,201) */
+enum { DARTKV_DEQUANT_PER_OP = 0, DARTKV_DEQUANT_FP32 = 1 };
+/* channel scoring, src/dart/mixed.py:154-162 */
+enum { DARTKV_SCORE_MAGNITUDE = 0, DARTKV_SCORE_VARIANCE = 1 };
+
+enum {
+  DARTKV_OK = 0,
+  DARTKV_EINVAL = -1,   /* bad argument (message says which) */
+  DARTKV_ECUDA = -2,    /* a CUDA runtime call failed */
+  DARTKV_ELIMIT = -3    /* size beyond a documented limit of this build */
+};
+
+const char* dartkv_last_error(void);
+int dartkv_version(void);
+
+/* ------------------------------------------------------------------ bit packing
+ * Replaces _pack / _unpack (src/dart/quantization.py:25-45): element i of a byte
+ * occupies bits [i*bits, (i+1)*bits); rows are padded with zero bits to a byte. */
+int dartkv_pack(const uint8_t* codes, int64_t rows, int64_t n, int bits, uint8_t* packed, void* stream);
+int dartkv_unpack(const uint8_t* packed, int64_t rows, int64_t packed_bytes, int bits, int64_t count,
+                  uint8_t* codes, void* stream);
+
+/* ------------------------------------------------------------------ group-wise quantizer
+ * Replaces quantize / quantize_axis (src/dart/quantization.py:134-223).
+ * The input is viewed as [outer, n, inner] with element strides; the quantized
+ * axis is n.  Row r = o*inner + i.  Outputs: values [rows, packed_bytes] with
+ * packed_bytes = ceil(ceil(n/group)*group / (8/bits)); scale, zero [rows, groups]
+ * in md_dtype.  nonfinite (may be NULL) is set to 1 if any input is NaN/Inf
+ * (the reference's isfinite().all() check, src/dart/quantization.py:159, read lazily). */
+int dartkv_quantize(const void* x, int dtype, int64_t outer, int64_t n, int64_t inner,
+                    int64_t stride_outer, int64_t stride_n, int64_t stride_inner,
+                    int bits, int group_size, int md_dtype, int div_mode,
+                    uint8_t* values, void* scale, void* zero, int32_t* nonfinite, void* stream);
+
+/* Replaces QuantizedTensor.dequantize (src/dart/quantization.py:96-109) and the two uniform
+ * Triton dequant kernels (src/dart/triton_ops.py:32-110).  Output is written as
+ * [outer, n, inner] with the given element strides. */
+int dartkv_dequantize(const uint8_t* values, const void* scale, const void* zero, int md_dtype,
+                      int64_t outer, int64_t n, int64_t inner, int bits, int group_size, int flavour,
+                      void* out, int out_dtype, int64_t stride_outer, int64_t stride_n, int64_t stride_inner,
+                      void* stream);
+
+/* ------------------------------------------------------------------ promoted key channels
+ * Replaces the scoring half of select_key_channels (src/dart/mixed.py:154-162):
+ * keys [bh, tokens, head_dim] (element strides, head_dim contiguous) -> scores [bh, head_dim] in dtype. */
+int dartkv_channel_scores(const void* keys, int dtype, int64_t bh, int64_t tokens, int64_t head_dim,
+                          int64_t stride_bh, int64_t stride_token, int strategy, void* scores, void* stream);
+/* Replaces torch.topk in select_key_channels (src/dart/mixed.py:156): the `count` largest
+ * scores per row, ordered by (score descending, channel ascending); indices int32 [bh, count]. */
+int dartkv_select_channels(const void* scores, int dtype, int64_t bh, int64_t head_dim, int count,
+                           int32_t* indices, void* stream);
+/* Replaces quantize_key_mixed (src/dart/mixed.py:166-244) for given promoted channels.
+ * low [bh, D, G, ceil(Gk/4)], high [bh, K, G, ceil(Gk/4)], scale/zero [bh, D, G]. */
+int dartkv_quantize_key_mixed(const void* keys, int dtype, int64_t bh, int64_t tokens, int64_t head_dim,
+                              int64_t stride_bh, int64_t stride_token, int group_size,
+                              const int32_t* indices, int promoted, int md_dtype,
+                              uint8_t* low, uint8_t* high, void* scale, void* zero, int32_t* nonfinite,
+                              void* stream);
+/* Replaces MixedQuantizedKey.dequantize (src/dart/mixed.py:72-94) and the mixed Triton
+ * dequant kernel (src/dart/triton_ops.py:113-201); out [bh, tokens, head_dim] contiguous. */
+int dartkv_dequantize_key_mixed(const uint8_t* low, const uint8_t* high, const int32_t* indices,
+                                const void* scale, const void* zero, int md_dtype, int64_t bh, int64_t tokens,
+                                int64_t head_dim, int group_size, int promoted, int flavour,
+                                void* out, int out_dtype, void* stream);
+
+/* ------------------------------------------------------------------ device-resident paged cache
+ * Replaces the storage of DartKVCache (src/dart/cache.py:115-190): instead of Python
+ * lists of tensors, one set of caller-allocated pools per layer plus device-side
+ * page metadata that the attention kernel walks by itself.
+ *
+ * Token t of the sequence lives in exactly one place per side (K or V):
+ *   t < sink_tokens                         -> k_sink / v_sink row t
+ *   key page p with start[p] <= t < start[p]+tokens[p]  -> k_pages slot p
+ *   sink_tokens <= t < v_packed_end         -> value row t - sink_tokens
+ *   otherwise (not packed yet)              -> ring row t % ring_tokens
+ */
+typedef struct dartkv_cache_desc {
+  int32_t batch, kv_heads, head_dim;
+  int32_t dtype, md_dtype;
+  int32_t page_size, key_group, value_group;
+  int32_t key_bits, value_bits;
+  int32_t key_mode;        /* DARTKV_QUANTIZED_PAGE or DARTKV_MIXED_PAGE */
+  int32_t promoted;        /* promoted channels per head (mixed mode) */
+  int32_t sink_tokens;     /* configured sink length S */
+  int32_t ring_tokens;     /* rows of the dense ring R */
+  int32_t max_key_pages;   /* page slots per (b,h) */
+  int32_t max_value_tokens;/* packed value rows per (b,h) */
+  /* byte geometry (filled by dartkv_cache_geometry) */
+  int32_t key_page_bytes;  /* stride between page slots */
+  int32_t key_off_high, key_off_index, key_off_scale, key_off_zero;   /* field offsets in a slot; low / values at 0 */
+  int32_t value_row_bytes; /* packed codes per token */
+  int32_t value_groups;    /* groups per token */
+  int32_t regular_pages;   /* 1: every key page holds page_size tokens (pages are held until full) */
+  /* pools (device pointers) */
+  void* k_sink;            /* [B,H,S,D] dtype */
+  void* v_sink;
+  void* k_ring;            /* [B,H,R,D] dtype */
+  void* v_ring;
+  uint8_t* k_pages;        /* [B,H,max_key_pages,key_page_bytes] */
+  uint8_t* v_codes;        /* [B,H,max_value_tokens,value_row_bytes] */
+  void* v_meta;            /* [B,H,max_value_tokens,2,value_groups] md_dtype: scale row then zero row */
+  int32_t* page_start;     /* [max_key_pages] first token of each key page */
+  int32_t* page_tokens;    /* [max_key_pages] tokens in each key page */
+  int32_t* state;          /* [8]: seen, key_pages, k_packed_end, v_packed_end, sink_filled, 0.. */
+} dartkv_cache_desc;
+
+/* Fill the byte-geometry fields from the configuration fields. */
+int dartkv_cache_geometry(dartkv_cache_desc* desc);
+
+/* One append step, planned on the host (the lifecycle rules of src/dart/cache.py:168-190,403-470
+ * are integer bookkeeping) and executed by the device: tokens [chunk_start, chunk_start+chunk_tokens)
+ * arrive in keys/values [B,H,chunk_tokens,D] (element strides for b, h, token; D contiguous). */
+typedef struct dartkv_append_plan {
+  int32_t chunk_start, chunk_tokens;
+  int32_t sink_copy;           /* leading chunk tokens copied into the sink rows */
+  int32_t first_page;          /* slot of the first key page produced by this step */
+  int32_t num_pages;           /* key pages produced */
+  int32_t page_token_start;    /* absolute token of the first new key page */
+  int32_t last_page_tokens;    /* tokens in the last new page (others hold page_size) */
+  int32_t value_begin, value_end; /* absolute tokens whose values are packed by this step */
+  int32_t ring_begin;          /* chunk tokens >= ring_begin keep dense keys in the ring (values: >= value_end) */
+  int32_t reserved;
+  int32_t seen_after, k_packed_end_after, v_packed_end_after, key_pages_after;
+  int32_t requantize_last_page;   /* 1: re-quantize page first_page-1 in place first (src/dart/cache.py:427-439) */
+} dartkv_append_plan;
+
+/* indices: optional [B*H, num_pages, promoted] int32 promoted channels to use instead of
+ * selecting them (parity with a particular reference run); NULL selects by score. */
+int dartkv_cache_append(const dartkv_cache_desc* desc, const dartkv_append_plan* plan,
+                        const void* keys, const void* values,
+                        int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                        const int32_t* indices, int32_t* nonfinite, void* stream);
+
+/* Materialize tokens [t0, t1) of the cache as dense [B,H,t1-t0,D] tensors (cache.get(),
+ * src/dart/cache.py:192-199); side 0 = keys, 1 = values. */
+int dartkv_cache_materialize(const dartkv_cache_desc* desc, int side, int32_t t0, int32_t t1, int flavour,
+                             void* out, int out_dtype, void* stream);
+
+/* ------------------------------------------------------------------ fused decode attention
+ * Replaces fused_dart_attention (src/dart/fused_attention.py:654-771) and, numerically,
+ * streamed_dart_attention (src/dart/attention.py:32-87): one query token per (batch, query head),
+ * GQA by contiguous head groups, split-K over the token range with a cross-split merge.
+ * query/out [B,Hq,D] (q_dtype, contiguous).  workspace: dartkv_decode_workspace_bytes() bytes.
+ * The token count is read from desc->state on the device, so the same launch serves every step. */
+int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* desc, int query_heads, int max_tokens);
+int dartkv_decode_attention(const dartkv_cache_desc* desc, const void* query, int q_dtype, int query_heads,
+                            float scale, int flavour, int max_tokens, void* workspace, int64_t workspace_bytes,
+                            void* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DARTKV_B200_H */
