@@ -407,7 +407,8 @@ extern "C" int dartkv_cache_append(const dartkv_cache_desc* desc, const dartkv_a
   DARTKV_REQUIRE(p.first_page >= 0 && p.first_page + p.num_pages <= d.max_key_pages, "append exceeds the key page capacity");
   DARTKV_REQUIRE(p.value_end <= p.value_begin || p.value_end - d.sink_tokens <= d.max_value_tokens,
                  "append exceeds the packed value capacity");
-  DARTKV_REQUIRE(p.sink_copy >= 0 && p.sink_copy <= p.chunk_tokens && p.chunk_start + p.sink_copy <= d.sink_tokens,
+  DARTKV_REQUIRE(p.sink_copy >= 0 && p.sink_copy <= p.chunk_tokens &&
+                     (p.sink_copy == 0 || p.chunk_start + p.sink_copy <= d.sink_tokens),
                  "bad sink_copy");
   DARTKV_REQUIRE(p.num_pages == 0 || (p.last_page_tokens > 0 && p.last_page_tokens <= d.page_size), "bad last_page_tokens");
   const int bh = d.batch * d.kv_heads;
