@@ -25,7 +25,7 @@ CODE_DTYPE = {v: k for k, v in DTYPE_CODE.items()}
 
 #: every symbol ``include/dartkv_b200.h`` declares
 EXPORTS = (
-    "dartkv_last_error", "dartkv_version", "dartkv_pack", "dartkv_unpack", "dartkv_quantize", "dartkv_dequantize",
+    "dartkv_last_error", "dartkv_version", "dartkv_launch_count", "dartkv_pack", "dartkv_unpack", "dartkv_quantize", "dartkv_dequantize",
     "dartkv_channel_scores", "dartkv_select_channels", "dartkv_quantize_key_mixed", "dartkv_dequantize_key_mixed",
     "dartkv_cache_geometry", "dartkv_cache_append", "dartkv_cache_materialize", "dartkv_decode_workspace_bytes",
     "dartkv_decode_attention",
@@ -74,6 +74,7 @@ def _load() -> ctypes.CDLL:
     lib = ctypes.CDLL(LIB_PATH)
     lib.dartkv_last_error.restype = c_char_p
     lib.dartkv_version.restype = c_int
+    lib.dartkv_launch_count.restype = ctypes.c_longlong
     p, i64, i32 = c_void_p, c_int64, c_int
     lib.dartkv_pack.argtypes = [p, i64, i64, i32, p, p]
     lib.dartkv_unpack.argtypes = [p, i64, i64, i32, i64, p, p]

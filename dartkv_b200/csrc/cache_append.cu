@@ -379,11 +379,12 @@ __global__ void page_to_ring_kernel(dartkv_cache_desc d, int slot_index, int pag
 }
 
 // ---------------------------------------------------------------------------- fast page kernels
-// Headline geometry: head_dim 128, full 128-token pages, key group 128, 16-bit data.
+// Common geometry (head_dim 128, 16-bit data, full 128-token pages, key group 128): append_fast.cu.
 int dartkv_append_fast_supported(const dartkv_cache_desc* d, const dartkv_append_plan* p, int64_t st);
-int dartkv_append_fast(const dartkv_cache_desc* d, const dartkv_append_plan* p, const void* keys, const void* values,
-                       int64_t sb, int64_t sh, int64_t st, const int32_t* indices, int32_t* nonfinite,
-                       cudaStream_t stream);
+int dartkv_append_fast_keys(const dartkv_cache_desc* d, const dartkv_append_plan* p, const void* keys, int64_t sb,
+                            int64_t sh, int64_t st, const int32_t* indices, int32_t* nonfinite, cudaStream_t stream);
+int dartkv_append_fast_values(const dartkv_cache_desc* d, const dartkv_append_plan* p, const void* values, int64_t sb,
+                              int64_t sh, int64_t st, int32_t* nonfinite, cudaStream_t stream);
 
 static int validate_desc(const dartkv_cache_desc* d) {
   DARTKV_REQUIRE(d != nullptr, "null descriptor");
@@ -430,11 +431,12 @@ extern "C" int dartkv_cache_append(const dartkv_cache_desc* desc, const dartkv_a
 
   const bool copies = p.sink_copy > 0 || p.ring_begin < chunk_end || p.value_end < chunk_end;
   int fast = dartkv_append_fast_supported(desc, plan, stride_t);
-  if (fast) {
-    rc = dartkv_append_fast(desc, plan, keys, values, stride_b, stride_h, stride_t, new_page_indices, nonfinite, stream);
-    if (rc) return rc;
-  } else {
-    if (p.num_pages > 0) {
+  if (stride_b % 8 || stride_h % 8 || ((uintptr_t)keys | (uintptr_t)values) % 16) fast = 0;
+  if (p.num_pages > 0) {
+    if (fast & 1) {
+      rc = dartkv_append_fast_keys(desc, plan, keys, stride_b, stride_h, stride_t, new_page_indices, nonfinite, stream);
+      if (rc) return rc;
+    } else {
       TokenSource ks{keys, d.k_ring, stride_b, stride_h, stride_t, p.chunk_start, d.ring_tokens, d.head_dim, d.kv_heads, d.dtype};
       DARTKV_REQUIRE(p.num_pages <= 65535, "too many pages in one append (limit 65535)");
       key_pages_kernel<<<dim3(bh, p.num_pages), 128, page_smem, stream>>>(d, ks, p.first_page, p.num_pages,
@@ -442,7 +444,12 @@ extern "C" int dartkv_cache_append(const dartkv_cache_desc* desc, const dartkv_a
                                                                          new_page_indices, nonfinite);
       DARTKV_LAUNCH_OK("key_pages_kernel");
     }
-    if (p.value_end > p.value_begin) {
+  }
+  if (p.value_end > p.value_begin) {
+    if (fast & 2) {
+      rc = dartkv_append_fast_values(desc, plan, values, stride_b, stride_h, stride_t, nonfinite, stream);
+      if (rc) return rc;
+    } else {
       TokenSource vs{values, d.v_ring, stride_b, stride_h, stride_t, p.chunk_start, d.ring_tokens, d.head_dim, d.kv_heads, d.dtype};
       const int vpb = 8 / d.value_bits;
       const int unit = d.value_group / dartkv_gcd(d.value_group, vpb) * vpb;

@@ -10,6 +10,7 @@
 
 // ---------------------------------------------------------------------------- errors
 void dartkv_set_error(const char* fmt, ...);
+void dartkv_count_launch();
 
 #define DARTKV_REQUIRE(cond, ...)          \
   do {                                     \
@@ -35,6 +36,7 @@ void dartkv_set_error(const char* fmt, ...);
       dartkv_set_error("launch of %s failed: %s", name, cudaGetErrorString(err__)); \
       return DARTKV_ECUDA;                                                          \
     }                                                                               \
+    dartkv_count_launch();                                                          \
   } while (0)
 
 static inline bool dartkv_valid_dtype(int dt) { return dt == DARTKV_F32 || dt == DARTKV_F16 || dt == DARTKV_BF16; }

@@ -5,6 +5,7 @@
 // live in cache_append.cu.  Arithmetic follows the reference's per-op rounding in the data
 // dtype (src/dart/quantization.py:178-186, src/dart/mixed.py:200-209).
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -19,6 +20,10 @@ void dartkv_set_error(const char* fmt, ...) {
   vsnprintf(g_error, sizeof(g_error), fmt, args);
   va_end(args);
 }
+
+static std::atomic<long long> g_launches{0};
+void dartkv_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+extern "C" long long dartkv_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" const char* dartkv_last_error(void) { return g_error; }
 extern "C" int dartkv_version(void) { return 100; }

@@ -41,6 +41,8 @@ enum {
 
 const char* dartkv_last_error(void);
 int dartkv_version(void);
+/* Number of kernels this library has launched in this process (for launch accounting in benchmarks). */
+long long dartkv_launch_count(void);
 
 /* ------------------------------------------------------------------ bit packing
  * Replaces _pack / _unpack (src/dart/quantization.py:25-45): element i of a byte
