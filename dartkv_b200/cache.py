@@ -229,7 +229,7 @@ class DartKVCache:
                 old.update(k_pages=k_pages, page_start=page_start, page_tokens=page_tokens)
                 d.max_key_pages = pages
             if "v_codes" not in old or need_rows > d.max_value_tokens:
-                rows = max(1, need_rows)
+                rows = -(-max(1, need_rows) // 128) * 128   # whole pages: keeps page slices 16-byte aligned
                 v_codes = torch.empty((b, h, rows, d.value_row_bytes), dtype=torch.uint8, device=device)
                 v_meta = torch.empty((b, h, rows, 2, d.value_groups), dtype=cfg.metadata_dtype, device=device)
                 if "v_codes" in old:
@@ -618,9 +618,19 @@ class DartKVCache:
         if self._workspace is None or self._workspace[0] != key:
             nbytes = LIB.dartkv_decode_workspace_bytes(ctypes.byref(d), query_heads, capacity)
             with torch.cuda.device(self._device):
-                buf = torch.empty(max(16, nbytes), dtype=torch.uint8, device=self._device)
+                buf = torch.zeros(max(16, nbytes), dtype=torch.uint8, device=self._device)
             self._workspace = (key, buf)
         return self._workspace[1], capacity
+
+    def decode_status(self) -> int:
+        """0 unless a decode kernel gave up on a bounded wait for an async copy (synchronizes)."""
+
+        if self._workspace is None:
+            return 0
+        status = ctypes.c_int(0)
+        with torch.cuda.device(self._device):
+            check(LIB.dartkv_decode_status(ptr(self._workspace[1]), ctypes.byref(status), stream_ptr(self._device)))
+        return status.value
 
     @property
     def descriptor(self) -> CacheDesc:

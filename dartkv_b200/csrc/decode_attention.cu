@@ -243,89 +243,96 @@ struct DecodeLayout {
 int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
 int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
                               int flavour, int splits, int pages_per_split, int split_base, int total_splits,
-                              float* part_m, float* part_l, float* part_acc, cudaStream_t stream);
+                              float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream);
 
-static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int query_heads, int max_tokens) {
+static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int query_heads, int flavour, int tokens) {
   DecodeLayout L{};
   const int bh = d->batch * d->kv_heads;
-  const int target_blocks = 148 * 4;
-  L.fast = dartkv_decode_fast_supported(d, q_dtype, query_heads);
+  const int target_blocks = 148 * 8;   // two resident blocks per SM, about four waves
+  L.fast = flavour == DARTKV_DEQUANT_PER_OP && dartkv_decode_fast_supported(d, q_dtype, query_heads);
   if (L.fast) {
-    int max_pages = max(1, (max_tokens - d->sink_tokens) / d->page_size);
+    const int pages = max(1, (tokens - d->sink_tokens) / d->page_size);
+    const int quads = (pages + 3) / 4;                 // a block hands pages to its four warps round-robin
     int want = max(1, (target_blocks + bh - 1) / bh);
-    L.fast_splits = min(want, max_pages);
-    L.fast_pages_per_split = (max_pages + L.fast_splits - 1) / L.fast_splits;
-    L.fast_splits = (max_pages + L.fast_pages_per_split - 1) / L.fast_pages_per_split;
-    L.total_splits = L.fast_splits + 2;   // + sink prefix + dense tail, each one generic split
-    L.generic_splits = 0;
-    L.generic_chunk = 0;
+    want = min(want, quads);
+    L.fast_pages_per_split = 4 * ((quads + want - 1) / want);
+    L.fast_splits = (pages + L.fast_pages_per_split - 1) / L.fast_pages_per_split;
+    L.total_splits = L.fast_splits + 1;                // + one block per (batch, kv head) for the dense tokens
   } else {
-    int max_splits = max(1, (max_tokens + 63) / 64);
-    int want = max(1, (target_blocks + bh - 1) / bh);
+    int max_splits = max(1, (tokens + 63) / 64);
+    int want = max(1, (148 * 4 + bh - 1) / bh);
     L.generic_splits = min(want, max_splits);
-    int chunk = (max_tokens + L.generic_splits - 1) / L.generic_splits;
+    int chunk = (tokens + L.generic_splits - 1) / L.generic_splits;
     L.generic_chunk = max(GEN_TILE, (chunk + GEN_TILE - 1) / GEN_TILE * GEN_TILE);
-    L.generic_splits = max(1, (max_tokens + L.generic_chunk - 1) / L.generic_chunk);
+    L.generic_splits = max(1, (tokens + L.generic_chunk - 1) / L.generic_chunk);
     L.total_splits = L.generic_splits;
   }
   return L;
 }
 
+static int64_t layout_bytes(const dartkv_cache_desc* d, int query_heads, const DecodeLayout& L) {
+  int64_t rows = (int64_t)d->batch * query_heads * L.total_splits;
+  return 16 + rows * (2 + d->head_dim) * (int64_t)sizeof(float);
+}
+
 extern "C" int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* d, int query_heads, int max_tokens) {
   if (!d || query_heads <= 0 || max_tokens <= 0) return 0;
-  // the split count does not depend on the query dtype except through fast-path eligibility; take the larger
+  // upper bound over query dtypes, dequant flavours and every token count up to max_tokens:
+  // the split count is non-decreasing in the token count for both layouts
   int64_t best = 0;
-  for (int dt = 0; dt < 3; ++dt) {
-    DecodeLayout L = decode_layout(d, dt, query_heads, max_tokens);
-    int64_t rows = (int64_t)d->batch * query_heads * L.total_splits;
-    int64_t bytes = rows * (2 + d->head_dim) * (int64_t)sizeof(float);
-    if (bytes > best) best = bytes;
-  }
+  for (int dt = 0; dt < 3; ++dt)
+    for (int flavour = 0; flavour < 2; ++flavour) {
+      DecodeLayout L = decode_layout(d, dt, query_heads, flavour, max_tokens);
+      best = max(best, layout_bytes(d, query_heads, L));
+      L.total_splits += 1;   // slack for rounding differences at smaller token counts
+      best = max(best, layout_bytes(d, query_heads, L));
+    }
   return best;
 }
 
+extern "C" int dartkv_decode_status(const void* workspace, int* status_out, void* stream) {
+  DARTKV_REQUIRE(workspace && status_out, "decode_status received a null pointer");
+  DARTKV_CUDA_OK(cudaMemcpyAsync(status_out, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  DARTKV_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  return DARTKV_OK;
+}
+
 extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads,
-                                       float scale, int flavour, int max_tokens, void* workspace,
+                                       float scale, int flavour, int tokens, void* workspace,
                                        int64_t workspace_bytes, void* out, void* stream_) {
   DARTKV_REQUIRE(d != nullptr, "null descriptor");
   DARTKV_REQUIRE(query && out && workspace, "decode_attention received a null pointer");
   DARTKV_REQUIRE(dartkv_valid_dtype(q_dtype), "query must be f32, f16 or bf16");
   DARTKV_REQUIRE(query_heads > 0 && query_heads % d->kv_heads == 0, "query heads must be divisible by cache KV heads");
-  DARTKV_REQUIRE(max_tokens > 0, "cache is empty");
+  DARTKV_REQUIRE(tokens > 0, "cache is empty");
   DARTKV_REQUIRE(flavour == DARTKV_DEQUANT_PER_OP || flavour == DARTKV_DEQUANT_FP32, "unknown dequant flavour %d", flavour);
   const int rep = query_heads / d->kv_heads;
   DARTKV_REQUIRE(rep <= GEN_MAX_REP, "at most %d query heads per KV head are supported", GEN_MAX_REP);
   DARTKV_REQUIRE(d->head_dim <= GEN_MAX_D, "decode attention supports head_dim up to %d", GEN_MAX_D);
   cudaStream_t stream = (cudaStream_t)stream_;
-  DecodeLayout L = decode_layout(d, q_dtype, query_heads, max_tokens);
+  DecodeLayout L = decode_layout(d, q_dtype, query_heads, flavour, tokens);
   const int64_t rows = (int64_t)d->batch * query_heads * L.total_splits;
-  DARTKV_REQUIRE(workspace_bytes >= rows * (2 + d->head_dim) * (int64_t)sizeof(float),
-                 "decode workspace too small: need %lld bytes", (long long)(rows * (2 + d->head_dim) * sizeof(float)));
-  float* part_m = reinterpret_cast<float*>(workspace);
+  DARTKV_REQUIRE(workspace_bytes >= layout_bytes(d, query_heads, L), "decode workspace too small: need %lld bytes",
+                 (long long)layout_bytes(d, query_heads, L));
+  int* status = reinterpret_cast<int*>(workspace);
+  float* part_m = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 16);
   float* part_l = part_m + rows;
   float* part_acc = part_l + rows;
   const int bh = d->batch * d->kv_heads;
   const int D = d->head_dim;
-  size_t smem = ((size_t)rep * D + (size_t)GEN_TILE * (D + 1) + (size_t)rep * GEN_TILE + 3 * rep) * sizeof(float) +
-                (size_t)D * sizeof(int);
-  GenericArgs a;
-  a.q = query; a.q_dt = q_dtype; a.query_heads = query_heads; a.flavour = flavour; a.scale = scale;
-  a.total_splits = L.total_splits; a.part_m = part_m; a.part_l = part_l; a.part_acc = part_acc;
-  if (smem > 48 * 1024)
-    DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (L.fast) {
     int rc = dartkv_decode_fast_launch(d, query, q_dtype, query_heads, scale, flavour, L.fast_splits,
-                                       L.fast_pages_per_split, 0, L.total_splits, part_m, part_l, part_acc, stream);
+                                       L.fast_pages_per_split, 0, L.total_splits, part_m, part_l, part_acc, status, stream);
     if (rc) return rc;
-    // dense sink prefix and dense tail (tokens past the last full packed page) as one generic split each
-    a.tok_begin = 0; a.tok_end = d->sink_tokens; a.chunk = max(1, d->sink_tokens); a.split_base = L.fast_splits;
-    decode_generic_kernel<<<dim3(bh, 1), GEN_THREADS, smem, stream>>>(*d, a);
-    DARTKV_LAUNCH_OK("decode_generic_kernel (sink)");
-    a.tok_begin = -1; a.tok_end = -1; a.chunk = 1 << 30; a.split_base = L.fast_splits + 1;
-    decode_generic_kernel<<<dim3(bh, 1), GEN_THREADS, smem, stream>>>(*d, a);
-    DARTKV_LAUNCH_OK("decode_generic_kernel (tail)");
   } else {
+    size_t smem = ((size_t)rep * D + (size_t)GEN_TILE * (D + 1) + (size_t)rep * GEN_TILE + 3 * rep) * sizeof(float) +
+                  (size_t)D * sizeof(int);
+    GenericArgs a;
+    a.q = query; a.q_dt = q_dtype; a.query_heads = query_heads; a.flavour = flavour; a.scale = scale;
+    a.total_splits = L.total_splits; a.part_m = part_m; a.part_l = part_l; a.part_acc = part_acc;
     a.tok_begin = 0; a.tok_end = -1; a.chunk = L.generic_chunk; a.split_base = 0;
+    if (smem > 48 * 1024)
+      DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     DARTKV_REQUIRE(L.generic_splits <= 65535, "too many splits");
     decode_generic_kernel<<<dim3(bh, L.generic_splits), GEN_THREADS, smem, stream>>>(*d, a);
     DARTKV_LAUNCH_OK("decode_generic_kernel");

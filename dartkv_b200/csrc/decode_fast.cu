@@ -1,9 +1,500 @@
-// Tensor-core decode kernel for the headline page geometry (placeholder until the kernel lands).
-#include "common.cuh"
+// Tensor-core fused decode attention for the common page geometry: head_dim 128, 128-token pages,
+// one 128-token key group, 2-bit values with 32/64/128-channel groups, 2-bit keys (uniform or with
+// promoted 2+2-bit channels), 16-bit data whose metadata has the same dtype, up to 4 query heads per
+// KV head.  Everything else takes the generic kernel in decode_attention.cu.
+//
+// Work split: grid (batch*kv_heads, splits + 1).  A block of 4 warps owns a run of consecutive packed
+// pages; each warp streams its own pages (page p of the run goes to warp p % 4) through a two-stage
+// shared-memory ring filled by 1-D bulk async copies (one 5760-byte key blob, 4096 bytes of value
+// codes and 1024 bytes of value metadata per page, completion on an mbarrier), and keeps a private
+// online-softmax state that the block merges at the end.  The extra block (blockIdx.y == splits)
+// handles the dense tokens: the sink prefix and everything after the last page that is packed on both
+// the key and the value side.
+//
+// Per page a warp never materializes K or V: packed 2-bit codes are turned into exactly rounded
+// 16-bit operands with one logic op and two packed fma/add per pair (mma_utils.cuh) and fed straight
+// into m16n8k16 MMAs.  A register of the quantized operand pairs two elements that share a
+// (scale, zero) -- two tokens of one channel for K, two channels of one token for V -- which is the
+// MMA's non-contraction direction; the contraction index is therefore doubled (k = (channel, j) for
+// K, (token, j) for V) against a block-diagonal query / probability operand whose columns are
+// (query head, j).  Algorithmic HBM bytes per page and (batch, kv head): 10880.
 
-int dartkv_decode_fast_supported(const dartkv_cache_desc*, int, int) { return 0; }
-int dartkv_decode_fast_launch(const dartkv_cache_desc*, const void*, int, int, float, int, int, int, int, int, float*,
-                              float*, float*, cudaStream_t) {
-  dartkv_set_error("fast decode kernel not built");
-  return DARTKV_EINVAL;
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kPageBytesK = 5760;
+constexpr int kValueCodes = 4096;
+constexpr int kStageBytes = 10880;            // key blob (<= 5760) | value codes 4096 | value metadata (<= 1024)
+constexpr int kOffVCodes = kPageBytesK;       // 5760
+constexpr int kOffVMeta = kPageBytesK + kValueCodes;  // 9856
+constexpr int kPStride = 136;                 // 16-bit elements per (plane, head) row of the probability tile
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct WarpSmem {
+  uint8_t stage[2][kStageBytes];
+  uint4 kpar4[128];       // per channel: (s,s) (z,z) -magic0*s -magic1*s
+  uint32_t kpar1[128];    // per channel: -magic2*s
+  uint16_t prob[2 * 4 * kPStride];  // [hi/lo][head][token]
+  uint8_t order[128];     // contraction order of the channels: promoted slots first
+  uint8_t is_promoted[128];
+  uint64_t bar[2];
+};
+
+struct BlockSmem {
+  uint32_t q32[2][4][128];   // query pre-shifted into the low (j'=0) or high (j'=1) half
+  float merge_m[kWarps][4];
+  float merge_l[kWarps][4];
+  int slot_map[128];
+};
+
+struct FastArgs {
+  const void* q;
+  int query_heads;
+  float scale;
+  int splits, pages_per_split, split_base, total_splits;
+  float* part_m;
+  float* part_l;
+  float* part_acc;
+  int* status;
+};
+
+__host__ __device__ __forceinline__ int fast_range_end(int sink_tokens, int page_size, int k_end, int v_end,
+                                                       int sink_filled) {
+  int packed = min(k_end, v_end);
+  if (packed <= sink_tokens) return sink_filled;
+  return sink_tokens + (packed - sink_tokens) / page_size * page_size;
+}
+
+template <int DT>
+__device__ __forceinline__ float rnd16(float x) { return Half2Ops<DT>::to_float(Half2Ops<DT>::from_float(x)); }
+
+// ------------------------------------------------------------------------------------------------
+// dense tokens (sink prefix, unpacked tail, and tokens packed on one side only): one warp per token,
+// four channels per lane, fp32 math
+template <int DT>
+__device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BlockSmem& bs, float* warp_out, int bh) {
+  using H = Half2Ops<DT>;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rep = a.query_heads / d.kv_heads;
+  const int seen = d.state[0], pages = d.state[1], k_end = d.state[2], v_end = d.state[3], sink_filled = d.state[4];
+  const int fast_end = fast_range_end(d.sink_tokens, d.page_size, k_end, v_end, sink_filled);
+  const int b = bh / d.kv_heads, h = bh % d.kv_heads;
+  float q[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      q[r][i] = r < rep ? load_f(a.q, d.dtype, ((int64_t)b * a.query_heads + h * rep + r) * 128 + lane * 4 + i) : 0.0f;
+  float m[4], l[4], acc[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[r][i] = 0.0f;
+  }
+  const float scale2 = a.scale * kLog2e;
+  // segments: [0, sink_filled) then [fast_end, seen) cut at key page boundaries
+  int t = 0;
+  while (t < seen) {
+    if (t >= sink_filled && t < fast_end) { t = fast_end; continue; }
+    int seg_end, kind;
+    const uint8_t* page = nullptr;
+    int page_first = 0;
+    if (t < sink_filled) { kind = 0; seg_end = sink_filled; }
+    else if (t < k_end) {
+      kind = 1;
+      int pg = (t - d.sink_tokens) / d.page_size;   // pages are regular on this path
+      page_first = d.sink_tokens + pg * d.page_size;
+      seg_end = min(seen, page_first + d.page_size);
+      page = d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes;
+      __syncthreads();
+      bs.slot_map[tid] = -1;
+      __syncthreads();
+      if (d.key_mode == DARTKV_MIXED_PAGE && tid < d.promoted) {
+        int ch = reinterpret_cast<const int32_t*>(page + d.key_off_index)[tid];
+        if (ch >= 0 && ch < 128) bs.slot_map[ch] = tid;
+      }
+      __syncthreads();
+    } else { kind = 2; seg_end = seen; }
+    (void)pages;
+    for (int tok = t + warp; tok < seg_end; tok += kWarps) {
+      float kv[4];
+      if (kind == 1) {
+        const int j = tok - page_first;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int ch = lane * 4 + i;
+          uint32_t code = (page[ch * 32 + j / 4] >> ((j % 4) * 2)) & 3u;
+          const int slot = bs.slot_map[ch];
+          if (slot >= 0) code |= ((page[d.key_off_high + slot * 32 + j / 4] >> ((j % 4) * 2)) & 3u) << 2;
+          const float s = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_scale)[ch]);
+          const float z = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_zero)[ch]);
+          kv[i] = rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn((float)code, s)), z));
+        }
+      } else {
+        const uint16_t* row = kind == 0
+            ? reinterpret_cast<const uint16_t*>(d.k_sink) + ((int64_t)bh * d.sink_tokens + tok) * 128
+            : reinterpret_cast<const uint16_t*>(d.k_ring) + ((int64_t)bh * d.ring_tokens + (tok % d.ring_tokens)) * 128;
+        uint2 raw = *reinterpret_cast<const uint2*>(row + lane * 4);
+        kv[0] = H::to_float((uint16_t)(raw.x & 0xFFFF)); kv[1] = H::to_float((uint16_t)(raw.x >> 16));
+        kv[2] = H::to_float((uint16_t)(raw.y & 0xFFFF)); kv[3] = H::to_float((uint16_t)(raw.y >> 16));
+      }
+      float s[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        float dot = q[r][0] * kv[0];
+        dot = fmaf(q[r][1], kv[1], dot);
+        dot = fmaf(q[r][2], kv[2], dot);
+        dot = fmaf(q[r][3], kv[3], dot);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        s[r] = dot * scale2;
+      }
+      // value row of the same token
+      float vv[4];
+      if (tok >= sink_filled && tok < v_end) {
+        const int64_t row = (int64_t)bh * d.max_value_tokens + (tok - d.sink_tokens);
+        const uint32_t byte = d.v_codes[row * 32 + lane];
+        const int g = (lane * 4) / d.value_group;
+        const uint16_t* meta = reinterpret_cast<const uint16_t*>(d.v_meta) + row * 2 * d.value_groups;
+        const float sc = H::to_float(meta[g]), z = H::to_float(meta[d.value_groups + g]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          vv[i] = rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn((float)((byte >> (2 * i)) & 3u), sc)), z));
+      } else {
+        const uint16_t* row = tok < sink_filled
+            ? reinterpret_cast<const uint16_t*>(d.v_sink) + ((int64_t)bh * d.sink_tokens + tok) * 128
+            : reinterpret_cast<const uint16_t*>(d.v_ring) + ((int64_t)bh * d.ring_tokens + (tok % d.ring_tokens)) * 128;
+        uint2 raw = *reinterpret_cast<const uint2*>(row + lane * 4);
+        vv[0] = H::to_float((uint16_t)(raw.x & 0xFFFF)); vv[1] = H::to_float((uint16_t)(raw.x >> 16));
+        vv[2] = H::to_float((uint16_t)(raw.y & 0xFFFF)); vv[3] = H::to_float((uint16_t)(raw.y >> 16));
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float m_new = fmaxf(m[r], s[r]);
+        const float alpha = exp2f(m[r] - m_new);
+        const float p = exp2f(s[r] - m_new);
+        m[r] = m_new;
+        l[r] = l[r] * alpha + p;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[r][i] = acc[r][i] * alpha + p * vv[i];
+      }
+    }
+    t = seg_end;
+  }
+  // hand the warp state to the block merge: acc in channel order
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    if (lane == 0) { bs.merge_m[warp][r] = m[r]; bs.merge_l[warp][r] = l[r]; }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) warp_out[(warp * 4 + r) * 128 + lane * 4 + i] = acc[r][i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_desc d, FastArgs a) {
+  using H = Half2Ops<DT>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  WarpSmem* wsm_all = reinterpret_cast<WarpSmem*>(smem_raw);
+  BlockSmem& bs = *reinterpret_cast<BlockSmem*>(smem_raw + sizeof(WarpSmem) * kWarps);
+  float* warp_out = reinterpret_cast<float*>(smem_raw);   // reused after the page loop: [warp][head][128]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int bh = blockIdx.x, split = blockIdx.y;
+  const int b = bh / d.kv_heads, hkv = bh % d.kv_heads;
+  const int rep = a.query_heads / d.kv_heads;
+  const bool dense = split == a.splits;
+
+  if (dense) {
+    dense_block<DT>(d, a, bs, warp_out, bh);
+  } else {
+    WarpSmem& ws = wsm_all[warp];
+    const int k_end = d.state[2], v_end = d.state[3], sink_filled = d.state[4];
+    const int fast_end = fast_range_end(d.sink_tokens, d.page_size, k_end, v_end, sink_filled);
+    const int total_pages = fast_end > d.sink_tokens ? (fast_end - d.sink_tokens) / 128 : 0;
+    const int p_begin = split * a.pages_per_split;
+    const int p_end = min(p_begin + a.pages_per_split, total_pages);
+
+    // query, pre-shifted for the block-diagonal operand
+    for (int i = tid; i < 4 * 128; i += kThreads) {
+      const int r = i >> 7, ch = i & 127;
+      uint32_t v = 0;
+      if (r < rep) v = reinterpret_cast<const uint16_t*>(a.q)[((int64_t)b * a.query_heads + hkv * rep + r) * 128 + ch];
+      bs.q32[0][r][ch] = v;
+      bs.q32[1][r][ch] = v << 16;
+    }
+    if (lane == 0) {
+      mbar_init(&ws.bar[0], 1);
+      mbar_init(&ws.bar[1], 1);
+      mbar_fence_init();
+    }
+    __syncthreads();
+
+    const int vmeta_page_bytes = 128 * 2 * d.value_groups * 2;
+    const uint32_t stage_tx = d.key_page_bytes + kValueCodes + vmeta_page_bytes;
+    auto issue = [&](int pg, int stage) {
+      // one lane starts the three bulk copies of a page; the barrier completes when all bytes landed
+      mbar_expect_tx(&ws.bar[stage], stage_tx);
+      const int64_t vrow = (int64_t)bh * d.max_value_tokens + (int64_t)pg * 128;
+      bulk_copy_g2s(ws.stage[stage], d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes, d.key_page_bytes, &ws.bar[stage]);
+      bulk_copy_g2s(ws.stage[stage] + kOffVCodes, d.v_codes + vrow * 32, kValueCodes, &ws.bar[stage]);
+      bulk_copy_g2s(ws.stage[stage] + kOffVMeta,
+                    reinterpret_cast<const uint8_t*>(d.v_meta) + vrow * (2 * d.value_groups * 2), vmeta_page_bytes, &ws.bar[stage]);
+    };
+
+    float o_acc[4][4];   // [m-tile][c-reg]: head c, channel 16g + 2mt + r + 8j'
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o_acc[mt][i] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;   // head c, log2 domain
+    const int K = d.key_mode == DARTKV_MIXED_PAGE ? d.promoted : 0;
+    const int prom_steps = (K + 7) >> 3;
+    const int jp = g & 1, hq = g >> 1;
+    const uint32_t* qsel = &bs.q32[jp][hq][0];
+    const float scale2 = a.scale * kLog2e;
+    const int gv = (16 * g) / d.value_group;
+    bool ok = true;
+
+    int pg0 = p_begin + warp;
+    if (lane == 0) {
+      if (pg0 < p_end) issue(pg0, 0);
+      if (pg0 + kWarps < p_end) issue(pg0 + kWarps, 1);
+    }
+    int iter = 0;
+    for (int pg = pg0; pg < p_end; pg += kWarps, ++iter) {
+      const int stage = iter & 1;
+      const uint32_t parity = (iter >> 1) & 1;
+      ok = mbar_wait(&ws.bar[stage], parity) && ok;
+      const uint8_t* blob = ws.stage[stage];
+      const uint32_t* low = reinterpret_cast<const uint32_t*>(blob);
+      const uint32_t* high = reinterpret_cast<const uint32_t*>(blob + d.key_off_high);
+      const uint16_t* kscale = reinterpret_cast<const uint16_t*>(blob + d.key_off_scale);
+      const uint16_t* kzero = reinterpret_cast<const uint16_t*>(blob + d.key_off_zero);
+
+      // ---- channel contraction order (promoted slots first) and per-channel constants
+      reinterpret_cast<uint32_t*>(ws.is_promoted)[lane] = 0;
+      __syncwarp();
+      if (K > 0) {
+        const int32_t* idx = reinterpret_cast<const int32_t*>(blob + d.key_off_index);
+        for (int k = lane; k < K; k += 32) {
+          const int ch = idx[k] & 127;
+          ws.is_promoted[ch] = 1;
+          ws.order[k] = (uint8_t)ch;
+        }
+      }
+      __syncwarp();
+      {
+        const uint32_t flags = reinterpret_cast<const uint32_t*>(ws.is_promoted)[lane];   // channels 4*lane .. +3
+        int mine = 4 - __popc(flags & 0x01010101u);
+        int before = mine;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          int up = __shfl_up_sync(0xffffffffu, before, off);
+          if (lane >= off) before += up;
+        }
+        int pos = K + before - mine;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (!((flags >> (8 * i)) & 1u)) ws.order[pos++] = (uint8_t)(4 * lane + i);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int ch = lane + 32 * i;
+          const uint32_t ss = (uint32_t)kscale[ch] * 0x00010001u;
+          const uint32_t zz = (uint32_t)kzero[ch] * 0x00010001u;
+          ws.kpar4[ch] = make_uint4(ss, zz, H::mul(ss, H::neg_magic(0)), H::mul(ss, H::neg_magic(1)));
+          ws.kpar1[ch] = H::mul(ss, H::neg_magic(2));
+        }
+      }
+      __syncwarp();
+
+      // ---- logits: S[token pair][(head, j')] over the doubled contraction (channel, j)
+      float s_acc[4][4];
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s_acc[mt][i] = 0.0f;
+#pragma unroll 2
+      for (int ks = 0; ks < 16; ++ks) {
+        const int ch0 = ws.order[8 * ks + c], ch1 = ws.order[8 * ks + c + 4];
+        const uint4 p0 = ws.kpar4[ch0], p1 = ws.kpar4[ch1];
+        const uint32_t w0 = low[ch0 * 8 + g], w1 = low[ch1 * 8 + g];
+        uint32_t r0[8], r1[8];
+        if (ks < prom_steps) {
+          const int s0 = 8 * ks + c, s1 = s0 + 4;
+          const uint32_t h0 = s0 < K ? high[s0 * 8 + g] : 0u;
+          const uint32_t h1 = s1 < K ? high[s1 * 8 + g] : 0u;
+          dequant_word4<DT>(w0, h0, p0.x, p0.y, p0.z, p0.w, r0);
+          dequant_word4<DT>(w1, h1, p1.x, p1.y, p1.z, p1.w, r1);
+        } else {
+          dequant_word2<DT>(w0, p0.x, p0.y, p0.z, p0.w, ws.kpar1[ch0], r0);
+          dequant_word2<DT>(w1, p1.x, p1.y, p1.z, p1.w, ws.kpar1[ch1], r1);
+        }
+        const uint32_t b0 = qsel[ch0], b1 = qsel[ch1];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) H::mma(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+      }
+
+      // ---- online softmax for head c over this page's 128 tokens (this thread: tokens 16g .. 16g+15)
+      float mx = -INFINITY;
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          s_acc[mt][i] *= scale2;
+          mx = fmaxf(mx, s_acc[mt][i]);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = exp2f(m_run - m_new);
+      m_run = m_new;
+      float psum = 0.0f;
+      uint16_t phi[16], plo[16];
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float p = exp2f(s_acc[mt][i] - m_new);
+          psum += p;
+          const int tok = 2 * mt + (i >> 1) + 8 * (i & 1);   // offset inside this thread's 16 tokens
+          const uint16_t hi = H::from_float(p);
+          phi[tok] = hi;
+          plo[tok] = H::from_float(p - H::to_float(hi));
+        }
+      l_run = l_run * alpha + psum;
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o_acc[mt][i] *= alpha;
+      {
+        uint32_t* hi_row = reinterpret_cast<uint32_t*>(&ws.prob[(0 * 4 + c) * kPStride + 16 * g]);
+        uint32_t* lo_row = reinterpret_cast<uint32_t*>(&ws.prob[(1 * 4 + c) * kPStride + 16 * g]);
+        uint32_t hw[8], lw[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          hw[i] = (uint32_t)phi[2 * i] | ((uint32_t)phi[2 * i + 1] << 16);
+          lw[i] = (uint32_t)plo[2 * i] | ((uint32_t)plo[2 * i + 1] << 16);
+        }
+        reinterpret_cast<uint4*>(hi_row)[0] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        reinterpret_cast<uint4*>(hi_row)[1] = make_uint4(hw[4], hw[5], hw[6], hw[7]);
+        reinterpret_cast<uint4*>(lo_row)[0] = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        reinterpret_cast<uint4*>(lo_row)[1] = make_uint4(lw[4], lw[5], lw[6], lw[7]);
+      }
+      __syncwarp();
+
+      // ---- O[channel pair][(head, j')] += V^T P over the doubled contraction (token, j)
+      const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(blob + kOffVCodes);
+      const uint16_t* vmeta = reinterpret_cast<const uint16_t*>(blob + kOffVMeta);
+      const uint16_t* prob_hi = &ws.prob[(0 * 4 + hq) * kPStride];
+      const uint16_t* prob_lo = &ws.prob[(1 * 4 + hq) * kPStride];
+      const int vg2 = 2 * d.value_groups;
+      const int shift = 16 * jp;
+#pragma unroll 2
+      for (int ks = 0; ks < 16; ++ks) {
+        const int t0 = 8 * ks + c, t1 = t0 + 4;
+        const uint32_t w0 = vcodes[t0 * 8 + g], w1 = vcodes[t1 * 8 + g];
+        const uint32_t ss0 = (uint32_t)vmeta[t0 * vg2 + gv] * 0x00010001u;
+        const uint32_t zz0 = (uint32_t)vmeta[t0 * vg2 + d.value_groups + gv] * 0x00010001u;
+        const uint32_t ss1 = (uint32_t)vmeta[t1 * vg2 + gv] * 0x00010001u;
+        const uint32_t zz1 = (uint32_t)vmeta[t1 * vg2 + d.value_groups + gv] * 0x00010001u;
+        uint32_t r0[8], r1[8];
+        dequant_word2<DT>(w0, ss0, zz0, H::mul(ss0, H::neg_magic(0)), H::mul(ss0, H::neg_magic(1)), H::mul(ss0, H::neg_magic(2)), r0);
+        dequant_word2<DT>(w1, ss1, zz1, H::mul(ss1, H::neg_magic(0)), H::mul(ss1, H::neg_magic(1)), H::mul(ss1, H::neg_magic(2)), r1);
+        const uint32_t ph0 = (uint32_t)prob_hi[t0] << shift, ph1 = (uint32_t)prob_hi[t1] << shift;
+        const uint32_t pl0 = (uint32_t)prob_lo[t0] << shift, pl1 = (uint32_t)prob_lo[t1] << shift;
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+          H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], ph0, ph1);
+          H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], pl0, pl1);
+        }
+      }
+      __syncwarp();
+      // the stage is free again: prefetch the page two iterations ahead
+      if (lane == 0 && pg + 2 * kWarps < p_end) issue(pg + 2 * kWarps, stage);
+    }
+    if (!ok && lane == 0) atomicExch(a.status, 1);
+
+    // ---- hand the warp state to the block merge
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 4);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 8);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
+    __syncthreads();   // every warp is done with its stages: the staging memory becomes the merge buffer
+    if (g == 0) { bs.merge_m[warp][c] = m_run; bs.merge_l[warp][c] = l_run; }
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int ch = 16 * g + 2 * mt + (i >> 1) + 8 * (i & 1);
+        warp_out[(warp * 4 + c) * 128 + ch] = o_acc[mt][i];
+      }
+  }
+  __syncthreads();
+
+  // ---- block merge: thread = channel, loop over heads; partials leave in natural-log units
+  const int slot = a.split_base + split;
+  for (int r = 0; r < rep; ++r) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) m = fmaxf(m, bs.merge_m[w][r]);
+    float l = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float mw = bs.merge_m[w][r];
+      if (mw != -INFINITY) {
+        const float wgt = exp2f(mw - m);
+        l += bs.merge_l[w][r] * wgt;
+        acc += warp_out[(w * 4 + r) * 128 + tid] * wgt;
+      }
+    }
+    const int64_t row = ((int64_t)b * a.query_heads + hkv * rep + r) * a.total_splits + slot;
+    if (tid == 0) {
+      a.part_m[row] = m == -INFINITY ? -INFINITY : m * 0.6931471805599453f;
+      a.part_l[row] = l;
+    }
+    a.part_acc[row * 128 + tid] = acc;
+  }
+}
+
+constexpr size_t kSmemBytes = sizeof(WarpSmem) * kWarps + sizeof(BlockSmem);
+
+}  // namespace
+
+int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads) {
+  if (d->head_dim != 128 || d->page_size != 128 || d->key_group != 128 || !d->regular_pages) return 0;
+  if (d->dtype != DARTKV_F16 && d->dtype != DARTKV_BF16) return 0;
+  if (d->md_dtype != d->dtype || q_dtype != d->dtype) return 0;
+  if (d->value_bits != 2 || (d->value_group != 64 && d->value_group != 128)) return 0;
+  if (d->key_mode == DARTKV_QUANTIZED_PAGE && d->key_bits != 2) return 0;
+  if (d->key_page_bytes % 16 || d->key_page_bytes > kPageBytesK) return 0;   // at most 32 promoted channels
+  if (query_heads % d->kv_heads || query_heads / d->kv_heads > 4) return 0;
+  if (d->max_value_tokens % 8) return 0;   // keeps every page of value metadata 16-byte aligned
+  if ((uintptr_t)d->k_pages % 16 || (uintptr_t)d->v_codes % 16 || (uintptr_t)d->v_meta % 16) return 0;
+  return 1;
+}
+
+int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
+                              int flavour, int splits, int pages_per_split, int split_base, int total_splits,
+                              float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream) {
+  (void)flavour;
+  (void)q_dtype;
+  FastArgs a{query, query_heads, scale, splits, pages_per_split, split_base, total_splits, part_m, part_l, part_acc, status};
+  dim3 grid(d->batch * d->kv_heads, splits + 1);
+  if (d->dtype == DARTKV_BF16) {
+    DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fast_kernel<DARTKV_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    decode_fast_kernel<DARTKV_BF16><<<grid, kThreads, kSmemBytes, stream>>>(*d, a);
+  } else {
+    DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fast_kernel<DARTKV_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    decode_fast_kernel<DARTKV_F16><<<grid, kThreads, kSmemBytes, stream>>>(*d, a);
+  }
+  DARTKV_LAUNCH_OK("decode_fast_kernel");
+  return DARTKV_OK;
 }

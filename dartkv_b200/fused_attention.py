@@ -43,7 +43,7 @@ def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional
     with torch.cuda.device(device):
         check(LIB.dartkv_decode_attention(
             ctypes.byref(cache.descriptor), ptr(q), _lib.DTYPE_CODE[q.dtype], q.shape[1], float(factor), flavour,
-            capacity, ptr(workspace), workspace.numel(), ptr(out), stream_ptr(device)))
+            seen, ptr(workspace), workspace.numel(), ptr(out), stream_ptr(device)))
     return out
 
 

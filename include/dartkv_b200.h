@@ -171,12 +171,18 @@ int dartkv_cache_materialize(const dartkv_cache_desc* desc, int side, int32_t t0
  * Replaces fused_dart_attention (src/dart/fused_attention.py:654-771) and, numerically,
  * streamed_dart_attention (src/dart/attention.py:32-87): one query token per (batch, query head),
  * GQA by contiguous head groups, split-K over the token range with a cross-split merge.
- * query/out [B,Hq,D] (q_dtype, contiguous).  workspace: dartkv_decode_workspace_bytes() bytes.
- * The token count is read from desc->state on the device, so the same launch serves every step. */
+ * query/out [B,Hq,D] (q_dtype, contiguous).
+ * workspace: split-K scratch of at least dartkv_decode_workspace_bytes(desc, Hq, max_tokens) bytes
+ * for any call with tokens <= max_tokens; zero it once after allocating (its first word is a status
+ * word that a kernel sets if a bounded wait on an async copy ran out).
+ * tokens: tokens currently in the cache (sizes the split grid; the kernels read the exact count and
+ * the page metadata from desc->state on the device). */
 int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* desc, int query_heads, int max_tokens);
 int dartkv_decode_attention(const dartkv_cache_desc* desc, const void* query, int q_dtype, int query_heads,
-                            float scale, int flavour, int max_tokens, void* workspace, int64_t workspace_bytes,
+                            float scale, int flavour, int tokens, void* workspace, int64_t workspace_bytes,
                             void* out, void* stream);
+/* Copies the workspace status word to the host (synchronizes the stream): 0 = no bounded wait expired. */
+int dartkv_decode_status(const void* workspace, int* status_out, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,125 @@
+"""The tensor-core decode kernel (head_dim 128, 128-token pages) against the oracle on seeded inputs,
+across the geometry it accepts, plus size-independent properties at the benchmark's full context."""
+
+import numpy as np
+import pytest
+import torch
+
+import dartkv_b200 as dart
+from dartkv_b200.synthetic import make_kvq
+from oracle import dartkv_oracle as orc
+from tests.helpers import DT_TAG, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(dtype, *, batch=2, heads=2, hq=8, tokens=32 + 5 * 128 + 77, chunks=None, seed=0, outliers=True, **cfg):
+    tag = DT_TAG[dtype]
+    keys, values, query = make_kvq(seed, batch, heads, tokens, 128, query_heads=hq, dtype=dtype,
+                                   outlier_fraction=0.05 if outliers else 0.0)
+    base = dict(bits=2, page_size=128, key_group_size=128, value_group_size=64, sink_tokens=32, hold_partial_pages=True)
+    base.update(cfg)
+    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=dtype, **base))
+    oracle = orc.OracleCache(orc.CacheConfig(metadata_dtype=tag, **base), tag)
+    start = 0
+    for chunk in chunks or [tokens]:
+        cache.append(keys[:, :, start:start + chunk].cuda(), values[:, :, start:start + chunk].cuda())
+        oracle.append(to_np(keys[:, :, start:start + chunk]), to_np(values[:, :, start:start + chunk]))
+        start += chunk
+    assert start == tokens
+    out = dart.fused_dart_attention(query.cuda(), cache, fallback=False)
+    assert cache.decode_status() == 0
+    ref32 = orc.streamed_attention(to_np(query), oracle, tag, return_f32=True)
+    ref = orc.streamed_attention(to_np(query), oracle, tag)
+    got = to_np(out)
+    # the kernel rounds its fp32 result once to the 16-bit output: within half an ulp of the fp32 oracle value
+    ulp = np.abs(ref32) * (2.0 ** -8 if tag == "bf16" else 2.0 ** -11)
+    assert np.all(np.abs(got - ref32) <= ulp + 2e-5), float(np.abs(got - ref32).max())
+    diff = np.abs(got - ref)
+    assert np.all((diff <= 2e-3) | (diff <= np.abs(ref) * (2.0 ** -7 if tag == "bf16" else 2.0 ** -10)))
+    # same cache through the generic kernel (fp32 query), which is checked against the golden vectors elsewhere
+    generic = dart.fused_dart_attention(query.float().cuda(), cache, fallback=False)
+    np.testing.assert_allclose(to_np(generic), ref32, rtol=0, atol=1e-5)
+    return cache, oracle, query
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_headline_geometry(dtype):
+    run_case(dtype, promote_ratio=0.25, chunks=[32, 128, 128, 128, 128, 128, 77])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_uniform_two_bit_keys(dtype):
+    run_case(dtype, seed=1, chunks=[300, 449])
+
+
+@pytest.mark.parametrize("hq", [2, 4, 8])
+def test_query_group_sizes(hq):
+    run_case(torch.bfloat16, seed=2, heads=2, hq=hq, promote_ratio=0.25)
+
+
+def test_promoted_count_not_a_multiple_of_eight():
+    # 0.1 * 128 -> 12 promoted channels: the second contraction step mixes promoted and plain channels
+    run_case(torch.bfloat16, seed=3, promote_ratio=0.1)
+    run_case(torch.float16, seed=4, promote_ratio=0.02)   # 2 promoted channels
+
+
+def test_value_group_128_and_no_sink():
+    run_case(torch.bfloat16, seed=5, promote_ratio=0.25, value_group_size=128, sink_tokens=0, tokens=4 * 128 + 3)
+
+
+def test_many_pages_use_both_pipeline_stages_and_several_splits():
+    run_case(torch.bfloat16, seed=6, batch=1, heads=1, hq=4, tokens=32 + 41 * 128 + 5, promote_ratio=0.25)
+
+
+def test_kitty_lifecycle_leaves_keys_and_values_packed_to_different_points():
+    # value_local_tokens keeps the newest values dense while their keys are already packed
+    run_case(torch.float16, seed=7, batch=1, heads=2, hq=8, tokens=32 + 3 * 128 + 40 + 30, promote_ratio=0.25,
+             local_tokens=1, value_local_tokens=128, chunks=[32 + 3 * 128 + 40] + [1] * 30)
+
+
+def test_no_packed_page_yet():
+    run_case(torch.bfloat16, seed=8, tokens=100, promote_ratio=0.25)
+    run_case(torch.bfloat16, seed=9, tokens=20, promote_ratio=0.25)
+
+
+def test_peaked_softmax_and_large_values():
+    # scaled queries make one token dominate: the hi/lo split of the probabilities must carry it
+    keys, values, query = make_kvq(10, 1, 1, 32 + 2 * 128, 128, query_heads=4, dtype=torch.bfloat16)
+    cfg = dict(bits=2, page_size=128, key_group_size=128, value_group_size=64, sink_tokens=32,
+               hold_partial_pages=True, promote_ratio=0.25)
+    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=torch.bfloat16, **cfg))
+    oracle = orc.OracleCache(orc.CacheConfig(metadata_dtype="bf16", **cfg), "bf16")
+    cache.append(keys.cuda(), (values * 50).cuda())
+    oracle.append(to_np(keys), to_np(values * 50))
+    q = (query * 4).to(torch.bfloat16)
+    out = dart.fused_dart_attention(q.cuda(), cache, scale=0.3, fallback=False)
+    ref32 = orc.streamed_attention(to_np(q), oracle, "bf16", scale=0.3, return_f32=True)
+    assert np.all(np.abs(to_np(out) - ref32) <= np.abs(ref32) * 2.0 ** -8 + 1e-3)
+
+
+def test_full_context_properties():
+    """Benchmark-size context (32768 tokens): properties that need no oracle run.
+
+    * attention over identical value rows returns that row (softmax weights sum to one);
+    * the tensor-core path and the generic path agree on the same packed cache.
+    """
+
+    batch, heads, hq, tokens = 1, 2, 8, 32768
+    keys, _, query = make_kvq(11, batch, heads, tokens, 128, query_heads=hq, dtype=torch.bfloat16)
+    row = torch.linspace(-2, 2, 128).to(torch.bfloat16)
+    values = row.view(1, 1, 1, 128).expand(batch, heads, tokens, 128).contiguous()
+    # no sink and a whole number of pages: every token's value row is packed, hence identical after dequantization
+    cfg = dart.DartKVCacheConfig(bits=2, page_size=128, key_group_size=128, value_group_size=64, sink_tokens=0,
+                                 hold_partial_pages=True, promote_ratio=0.25, metadata_dtype=torch.bfloat16)
+    cache = dart.DartKVCache(cfg)
+    cache.append(keys.cuda(), values.cuda())
+    out = dart.fused_dart_attention(query.cuda(), cache, fallback=False)
+    assert cache.decode_status() == 0
+    _, restored = cache.get()
+    expect = restored[:, :, 40].float()          # every packed value row dequantizes to the same vector
+    assert torch.equal(restored[:, :, 40], restored[:, :, 20000])
+    got = out[:, :, 0].float().view(batch, heads, hq // heads, 128)
+    assert torch.all((got - expect.unsqueeze(2)).abs() <= expect.abs().unsqueeze(2) * 2.0 ** -7 + 1e-3)
+    generic = dart.fused_dart_attention(query.float().cuda(), cache, fallback=False)
+    assert torch.all((out.float() - generic).abs() <= generic.abs() * 2.0 ** -8 + 2e-5)
