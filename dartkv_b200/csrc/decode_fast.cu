@@ -262,6 +262,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     const float scale2 = a.scale * kLog2e;
     const int gv = (16 * g) / d.value_group;
     bool ok = true;
+    CodeConsts<DT> cc;
+    cc.init();
 
     int pg0 = p_begin + warp;
     if (lane == 0) {
@@ -321,22 +323,28 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) s_acc[mt][i] = 0.0f;
+      for (int ks = 0; ks < prom_steps; ++ks) {
+        const int s0 = 8 * ks + c, s1 = s0 + 4;
+        const int ch0 = ws.order[s0], ch1 = ws.order[s1];
+        const uint4 p0 = ws.kpar4[ch0], p1 = ws.kpar4[ch1];
+        const uint32_t w0 = low[ch0 * 8 + g], w1 = low[ch1 * 8 + g];
+        const uint32_t h0 = s0 < K ? high[s0 * 8 + g] : 0u;
+        const uint32_t h1 = s1 < K ? high[s1 * 8 + g] : 0u;
+        uint32_t r0[8], r1[8];
+        dequant_word4<DT>(cc, w0, h0, p0.x, p0.y, p0.z, p0.w, r0);
+        dequant_word4<DT>(cc, w1, h1, p1.x, p1.y, p1.z, p1.w, r1);
+        const uint32_t b0 = qsel[ch0], b1 = qsel[ch1];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) H::mma(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+      }
 #pragma unroll 2
-      for (int ks = 0; ks < 16; ++ks) {
+      for (int ks = prom_steps; ks < 16; ++ks) {
         const int ch0 = ws.order[8 * ks + c], ch1 = ws.order[8 * ks + c + 4];
         const uint4 p0 = ws.kpar4[ch0], p1 = ws.kpar4[ch1];
         const uint32_t w0 = low[ch0 * 8 + g], w1 = low[ch1 * 8 + g];
         uint32_t r0[8], r1[8];
-        if (ks < prom_steps) {
-          const int s0 = 8 * ks + c, s1 = s0 + 4;
-          const uint32_t h0 = s0 < K ? high[s0 * 8 + g] : 0u;
-          const uint32_t h1 = s1 < K ? high[s1 * 8 + g] : 0u;
-          dequant_word4<DT>(w0, h0, p0.x, p0.y, p0.z, p0.w, r0);
-          dequant_word4<DT>(w1, h1, p1.x, p1.y, p1.z, p1.w, r1);
-        } else {
-          dequant_word2<DT>(w0, p0.x, p0.y, p0.z, p0.w, ws.kpar1[ch0], r0);
-          dequant_word2<DT>(w1, p1.x, p1.y, p1.z, p1.w, ws.kpar1[ch1], r1);
-        }
+        dequant_word2<DT>(cc, w0, p0.x, p0.y, p0.z, p0.w, ws.kpar1[ch0], r0);
+        dequant_word2<DT>(cc, w1, p1.x, p1.y, p1.z, p1.w, ws.kpar1[ch1], r1);
         const uint32_t b0 = qsel[ch0], b1 = qsel[ch1];
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt) H::mma(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
@@ -355,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
       const float m_new = fmaxf(m_run, mx);
-      const float alpha = exp2f(m_run - m_new);
+      const float alpha = fast_exp2(m_run - m_new);
       m_run = m_new;
       float psum = 0.0f;
       uint16_t phi[16], plo[16];
@@ -363,7 +371,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float p = exp2f(s_acc[mt][i] - m_new);
+          const float p = fast_exp2(s_acc[mt][i] - m_new);
           psum += p;
           const int tok = 2 * mt + (i >> 1) + 8 * (i & 1);   // offset inside this thread's 16 tokens
           const uint16_t hi = H::from_float(p);
@@ -407,8 +415,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
         const uint32_t ss1 = (uint32_t)vmeta[t1 * vg2 + gv] * 0x00010001u;
         const uint32_t zz1 = (uint32_t)vmeta[t1 * vg2 + d.value_groups + gv] * 0x00010001u;
         uint32_t r0[8], r1[8];
-        dequant_word2<DT>(w0, ss0, zz0, H::mul(ss0, H::neg_magic(0)), H::mul(ss0, H::neg_magic(1)), H::mul(ss0, H::neg_magic(2)), r0);
-        dequant_word2<DT>(w1, ss1, zz1, H::mul(ss1, H::neg_magic(0)), H::mul(ss1, H::neg_magic(1)), H::mul(ss1, H::neg_magic(2)), r1);
+        dequant_word2<DT>(cc, w0, ss0, zz0, H::mul(ss0, H::neg_magic(0)), H::mul(ss0, H::neg_magic(1)), H::mul(ss0, H::neg_magic(2)), r0);
+        dequant_word2<DT>(cc, w1, ss1, zz1, H::mul(ss1, H::neg_magic(0)), H::mul(ss1, H::neg_magic(1)), H::mul(ss1, H::neg_magic(2)), r1);
         const uint32_t ph0 = (uint32_t)prob_hi[t0] << shift, ph1 = (uint32_t)prob_hi[t1] << shift;
         const uint32_t pl0 = (uint32_t)prob_lo[t0] << shift, pl1 = (uint32_t)prob_lo[t1] << shift;
 #pragma unroll

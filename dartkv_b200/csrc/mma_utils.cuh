@@ -112,6 +112,38 @@ template <> struct Half2Ops<DARTKV_F16> {
   static constexpr int kFirstPos = 2;
 };
 
+// (a & b) | c in one LOP3; b and c are kept in registers (a logic op takes at most one immediate)
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// a value the compiler must keep in a register instead of re-materializing as an immediate
+__device__ __forceinline__ uint32_t reg_const(uint32_t v) {
+  uint32_t r;
+  asm volatile("mov.b32 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// masks and magic exponents of the three in-mantissa code positions, held in registers
+template <int DT>
+struct CodeConsts {
+  uint32_t mask[3], magic[3];
+  __device__ __forceinline__ void init() {
+    using H = Half2Ops<DT>;
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      mask[j] = reg_const(0x00030003u << (2 * (H::kFirstPos + j)));
+      magic[j] = reg_const(H::magic(j));
+    }
+  }
+};
+
 // shift a packed-code word so that code index `code` of each 16-bit half lands at field position `pos`
 __device__ __forceinline__ uint32_t align_codes(uint32_t w, int code, int pos, int extra_left = 0) {
   const int left = 2 * pos + extra_left - 2 * code;
@@ -126,8 +158,8 @@ __device__ __forceinline__ uint32_t align_codes(uint32_t w, int code, int pos, i
 //   r = add(t, z)             = round16(round16(code * s) + z)
 // which is the reference's per-op rounding in the metadata dtype (src/dart/quantization.py:103-106).
 template <int DT>
-__device__ __forceinline__ void dequant_word2(uint32_t w, uint32_t ss, uint32_t zz, uint32_t ms0, uint32_t ms1,
-                                              uint32_t ms2, uint32_t (&r)[8]) {
+__device__ __forceinline__ void dequant_word2(const CodeConsts<DT>& k, uint32_t w, uint32_t ss, uint32_t zz,
+                                              uint32_t ms0, uint32_t ms1, uint32_t ms2, uint32_t (&r)[8]) {
   using H = Half2Ops<DT>;
   constexpr int P0 = H::kFirstPos;
 #pragma unroll
@@ -137,8 +169,7 @@ __device__ __forceinline__ void dequant_word2(uint32_t w, uint32_t ss, uint32_t 
     for (int j = 0; j < 3; ++j) {
       const int u = 3 * grp + j;
       if (u < 8) {
-        const uint32_t mask = 0x00030003u << (2 * (P0 + j));
-        const uint32_t m = (x & mask) | H::magic(j);
+        const uint32_t m = and_or(x, k.mask[j], k.magic[j]);
         const uint32_t ms = j == 0 ? ms0 : (j == 1 ? ms1 : ms2);
         r[u] = H::add(H::fma(m, ss, ms), zz);
       }
@@ -148,8 +179,8 @@ __device__ __forceinline__ void dequant_word2(uint32_t w, uint32_t ss, uint32_t 
 
 // 4-bit codes split over a low-bit word and a high-bit word (promoted key channels): code = low | high << 2
 template <int DT>
-__device__ __forceinline__ void dequant_word4(uint32_t wl, uint32_t wh, uint32_t ss, uint32_t zz, uint32_t ms0,
-                                              uint32_t ms1, uint32_t (&r)[8]) {
+__device__ __forceinline__ void dequant_word4(const CodeConsts<DT>& k, uint32_t wl, uint32_t wh, uint32_t ss,
+                                              uint32_t zz, uint32_t ms0, uint32_t ms1, uint32_t (&r)[8]) {
   using H = Half2Ops<DT>;
   constexpr int P0 = H::kFirstPos;
 #pragma unroll
@@ -159,9 +190,8 @@ __device__ __forceinline__ void dequant_word4(uint32_t wl, uint32_t wh, uint32_t
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int u = 2 * grp + j;
-      const uint32_t maskl = 0x00030003u << (2 * (P0 + j));
-      uint32_t m = (xl & maskl) | H::magic(j);
-      m |= xh & (maskl << 2);
+      // the high field of position j sits where the low field of position j+1 does
+      const uint32_t m = and_or(xh, k.mask[j + 1], and_or(xl, k.mask[j], k.magic[j]));
       r[u] = H::add(H::fma(m, ss, j == 0 ? ms0 : ms1), zz);
     }
   }
