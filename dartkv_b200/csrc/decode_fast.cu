@@ -1,15 +1,17 @@
 // Tensor-core fused decode attention for the common page geometry: head_dim 128, 128-token pages,
-// one 128-token key group, 2-bit values with 32/64/128-channel groups, 2-bit keys (uniform or with
-// promoted 2+2-bit channels), 16-bit data whose metadata has the same dtype, up to 4 query heads per
-// KV head.  Everything else takes the generic kernel in decode_attention.cu.
+// one 128-token key group, 2-bit values with 64/128-channel groups, 2-bit keys (uniform or with up to
+// 32 promoted 2+2-bit channels), 16-bit data whose metadata has the same dtype, up to 4 query heads
+// per KV head.  Everything else takes the generic kernel in decode_attention.cu.
 //
-// Work split: grid (batch*kv_heads, splits + 1).  A block of 4 warps owns a run of consecutive packed
-// pages; each warp streams its own pages (page p of the run goes to warp p % 4) through a two-stage
-// shared-memory ring filled by 1-D bulk async copies (one 5760-byte key blob, 4096 bytes of value
-// codes and 1024 bytes of value metadata per page, completion on an mbarrier), and keeps a private
-// online-softmax state that the block merges at the end.  The extra block (blockIdx.y == splits)
-// handles the dense tokens: the sink prefix and everything after the last page that is packed on both
-// the key and the value side.
+// Work split: grid (batch*kv_heads, splits + 1).  A block of 8 warps (4 warp pairs) owns a run of
+// consecutive packed pages; page p of the run goes to pair p % 4.  A pair streams its pages through a
+// two-stage shared-memory ring filled by 1-D bulk async copies (one key blob of up to 5760 bytes,
+// 4096 bytes of value codes and up to 1024 bytes of value metadata per page, completion on an
+// mbarrier).  The two warps of a pair split the page's tokens (codes 0-3 / 4-7 of every packed
+// 16-bit half, i.e. 64 tokens each) and keep private online-softmax states, so they only meet at two
+// named barriers per page; the block merges all eight states at the end.  The extra block
+// (blockIdx.y == splits) handles the dense tokens: the sink prefix and everything after the last
+// page that is packed on both the key and the value side.
 //
 // Per page a warp never materializes K or V: packed 2-bit codes are turned into exactly rounded
 // 16-bit operands with one logic op and two packed fma/add per pair (mma_utils.cuh) and fed straight
@@ -24,21 +26,22 @@
 
 namespace {
 
-constexpr int kWarps = 4;
+constexpr int kPairs = 4;
+constexpr int kWarps = 2 * kPairs;
 constexpr int kThreads = kWarps * 32;
 constexpr int kPageBytesK = 5760;
 constexpr int kValueCodes = 4096;
 constexpr int kStageBytes = 10880;            // key blob (<= 5760) | value codes 4096 | value metadata (<= 1024)
 constexpr int kOffVCodes = kPageBytesK;       // 5760
 constexpr int kOffVMeta = kPageBytesK + kValueCodes;  // 9856
-constexpr int kPStride = 136;                 // 16-bit elements per (plane, head) row of the probability tile
+constexpr int kPStride = 72;                  // 16-bit elements per (plane, head) row of a warp's probability tile
 constexpr float kLog2e = 1.4426950408889634f;
 
-struct WarpSmem {
+struct PairSmem {
   uint8_t stage[2][kStageBytes];
   uint4 kpar4[128];       // per channel: (s,s) (z,z) -magic0*s -magic1*s
   uint32_t kpar1[128];    // per channel: -magic2*s
-  uint16_t prob[2 * 4 * kPStride];  // [hi/lo][head][token]
+  uint16_t prob[2][2 * 4 * kPStride];  // per warp of the pair: [hi/lo][head][local token]
   uint8_t order[128];     // contraction order of the channels: promoted slots first
   uint8_t is_promoted[128];
   uint64_t bar[2];
@@ -50,6 +53,10 @@ struct BlockSmem {
   float merge_l[kWarps][4];
   int slot_map[128];
 };
+
+__device__ __forceinline__ void pair_barrier(int pair) {
+  asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
+}
 
 struct FastArgs {
   const void* q;
@@ -113,7 +120,7 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, Block
       seg_end = min(seen, page_first + d.page_size);
       page = d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes;
       __syncthreads();
-      bs.slot_map[tid] = -1;
+      if (tid < 128) bs.slot_map[tid] = -1;
       __syncthreads();
       if (d.key_mode == DARTKV_MIXED_PAGE && tid < d.promoted) {
         int ch = reinterpret_cast<const int32_t*>(page + d.key_off_index)[tid];
@@ -177,8 +184,8 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, Block
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const float m_new = fmaxf(m[r], s[r]);
-        const float alpha = exp2f(m[r] - m_new);
-        const float p = exp2f(s[r] - m_new);
+        const float alpha = fast_exp2(m[r] - m_new);
+        const float p = fast_exp2(s[r] - m_new);
         m[r] = m_new;
         l[r] = l[r] * alpha + p;
 #pragma unroll
@@ -197,12 +204,130 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, Block
 }
 
 // ------------------------------------------------------------------------------------------------
+// One warp's share of a staged page: QK over its 64 tokens, online softmax, PV over the same tokens.
+template <int DT, int HF>
+__device__ __forceinline__ void page_half(const dartkv_cache_desc& d, PairSmem& ps, const uint8_t* blob, uint16_t* prob,
+                                          const uint32_t* qsel, const CodeConsts<DT>& cc, int K, int prom_steps,
+                                          float scale2, int g, int c, int jp, int hq, int gv, float (&o_acc)[4][4],
+                                          float& m_run, float& l_run) {
+  using H = Half2Ops<DT>;
+  const uint32_t* low = reinterpret_cast<const uint32_t*>(blob);
+  const uint32_t* high = reinterpret_cast<const uint32_t*>(blob + d.key_off_high);
+
+  // ---- logits: S[token pair][(head, j')] over the doubled contraction (channel, j); this warp's
+  // token pairs are codes 4*HF .. 4*HF+3 of every half-word: m-tile mt covers local pairs 2mt, 2mt+1
+  float s_acc[2][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s_acc[mt][i] = 0.0f;
+  for (int ks = 0; ks < prom_steps; ++ks) {
+    const int s0 = 8 * ks + c, s1 = s0 + 4;
+    const int ch0 = ps.order[s0], ch1 = ps.order[s1];
+    const uint4 p0 = ps.kpar4[ch0], p1 = ps.kpar4[ch1];
+    const uint32_t w0 = low[ch0 * 8 + g], w1 = low[ch1 * 8 + g];
+    const uint32_t h0 = s0 < K ? high[s0 * 8 + g] : 0u;
+    const uint32_t h1 = s1 < K ? high[s1 * 8 + g] : 0u;
+    uint32_t r0[4], r1[4];
+    dequant_half4<DT, HF>(cc, w0, h0, p0.x, p0.y, p0.z, p0.w, r0);
+    dequant_half4<DT, HF>(cc, w1, h1, p1.x, p1.y, p1.z, p1.w, r1);
+    const uint32_t b0 = qsel[ch0], b1 = qsel[ch1];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+  }
+#pragma unroll 4
+  for (int ks = prom_steps; ks < 16; ++ks) {
+    const int ch0 = ps.order[8 * ks + c], ch1 = ps.order[8 * ks + c + 4];
+    const uint4 p0 = ps.kpar4[ch0], p1 = ps.kpar4[ch1];
+    const uint32_t w0 = low[ch0 * 8 + g], w1 = low[ch1 * 8 + g];
+    uint32_t r0[4], r1[4];
+    dequant_half2<DT, HF>(cc, w0, p0.x, p0.y, p0.z, p0.w, ps.kpar1[ch0], r0);
+    dequant_half2<DT, HF>(cc, w1, p1.x, p1.y, p1.z, p1.w, ps.kpar1[ch1], r1);
+    const uint32_t b0 = qsel[ch0], b1 = qsel[ch1];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+  }
+
+  // ---- online softmax for head c over this warp's 64 tokens (this thread: 8 of them)
+  float mx = -INFINITY;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s_acc[mt][i] *= scale2;
+      mx = fmaxf(mx, s_acc[mt][i]);
+    }
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+  const float m_new = fmaxf(m_run, mx);
+  const float alpha = fast_exp2(m_run - m_new);
+  m_run = m_new;
+  float psum = 0.0f;
+  uint16_t phi[8], plo[8];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float p = fast_exp2(s_acc[mt][i] - m_new);
+      psum += p;
+      const int li = 2 * mt + (i >> 1) + 4 * (i & 1);   // local token index inside this thread's 8: pair + 4 j'
+      const uint16_t hi = H::from_float(p);
+      phi[li] = hi;
+      plo[li] = H::from_float(p - H::to_float(hi));
+    }
+  l_run = l_run * alpha + psum;
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o_acc[mt][i] *= alpha;
+  {
+    uint4 hv, lv;
+    hv.x = (uint32_t)phi[0] | ((uint32_t)phi[1] << 16); hv.y = (uint32_t)phi[2] | ((uint32_t)phi[3] << 16);
+    hv.z = (uint32_t)phi[4] | ((uint32_t)phi[5] << 16); hv.w = (uint32_t)phi[6] | ((uint32_t)phi[7] << 16);
+    lv.x = (uint32_t)plo[0] | ((uint32_t)plo[1] << 16); lv.y = (uint32_t)plo[2] | ((uint32_t)plo[3] << 16);
+    lv.z = (uint32_t)plo[4] | ((uint32_t)plo[5] << 16); lv.w = (uint32_t)plo[6] | ((uint32_t)plo[7] << 16);
+    *reinterpret_cast<uint4*>(&prob[(0 * 4 + c) * kPStride + 8 * g]) = hv;
+    *reinterpret_cast<uint4*>(&prob[(1 * 4 + c) * kPStride + 8 * g]) = lv;
+  }
+  __syncwarp();
+
+  // ---- O[channel pair][(head, j')] += V^T P over the doubled contraction (token, j), this warp's tokens:
+  // step ks covers the eight tokens 16*ks + 4*HF + {0..3} and + 8
+  const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(blob + kOffVCodes);
+  const uint16_t* vmeta = reinterpret_cast<const uint16_t*>(blob + kOffVMeta);
+  const uint16_t* prob_hi = &prob[(0 * 4 + hq) * kPStride];
+  const uint16_t* prob_lo = &prob[(1 * 4 + hq) * kPStride];
+  const int vg = d.value_groups, vg2 = 2 * d.value_groups;
+  const int shift = 16 * jp;
+#pragma unroll 2
+  for (int ks = 0; ks < 8; ++ks) {
+    const int t0 = 16 * ks + 4 * HF + c, t1 = t0 + 8;
+    const uint32_t w0 = vcodes[t0 * 8 + g], w1 = vcodes[t1 * 8 + g];
+    const uint32_t ss0 = (uint32_t)vmeta[t0 * vg2 + gv] * 0x00010001u;
+    const uint32_t zz0 = (uint32_t)vmeta[t0 * vg2 + vg + gv] * 0x00010001u;
+    const uint32_t ss1 = (uint32_t)vmeta[t1 * vg2 + gv] * 0x00010001u;
+    const uint32_t zz1 = (uint32_t)vmeta[t1 * vg2 + vg + gv] * 0x00010001u;
+    uint32_t r0[8], r1[8];
+    dequant_word2<DT>(cc, w0, ss0, zz0, H::mul(ss0, H::neg_magic(0)), H::mul(ss0, H::neg_magic(1)), H::mul(ss0, H::neg_magic(2)), r0);
+    dequant_word2<DT>(cc, w1, ss1, zz1, H::mul(ss1, H::neg_magic(0)), H::mul(ss1, H::neg_magic(1)), H::mul(ss1, H::neg_magic(2)), r1);
+    const int l0 = 8 * ks + c, l1 = l0 + 4;
+    const uint32_t ph0 = (uint32_t)prob_hi[l0] << shift, ph1 = (uint32_t)prob_hi[l1] << shift;
+    const uint32_t pl0 = (uint32_t)prob_lo[l0] << shift, pl1 = (uint32_t)prob_lo[l1] << shift;
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) {
+      H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], ph0, ph1);
+      H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], pl0, pl1);
+    }
+  }
+}
+
 template <int DT>
 __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_desc d, FastArgs a) {
   using H = Half2Ops<DT>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  WarpSmem* wsm_all = reinterpret_cast<WarpSmem*>(smem_raw);
-  BlockSmem& bs = *reinterpret_cast<BlockSmem*>(smem_raw + sizeof(WarpSmem) * kWarps);
+  PairSmem* psm_all = reinterpret_cast<PairSmem*>(smem_raw);
+  BlockSmem& bs = *reinterpret_cast<BlockSmem*>(smem_raw + sizeof(PairSmem) * kPairs);
   float* warp_out = reinterpret_cast<float*>(smem_raw);   // reused after the page loop: [warp][head][128]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -215,7 +340,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
   if (dense) {
     dense_block<DT>(d, a, bs, warp_out, bh);
   } else {
-    WarpSmem& ws = wsm_all[warp];
+    const int pair = warp >> 1, hf = warp & 1;
+    PairSmem& ps = psm_all[pair];
     const int k_end = d.state[2], v_end = d.state[3], sink_filled = d.state[4];
     const int fast_end = fast_range_end(d.sink_tokens, d.page_size, k_end, v_end, sink_filled);
     const int total_pages = fast_end > d.sink_tokens ? (fast_end - d.sink_tokens) / 128 : 0;
@@ -230,9 +356,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       bs.q32[0][r][ch] = v;
       bs.q32[1][r][ch] = v << 16;
     }
-    if (lane == 0) {
-      mbar_init(&ws.bar[0], 1);
-      mbar_init(&ws.bar[1], 1);
+    const bool issuer = hf == 0 && lane == 0;
+    if (issuer) {
+      mbar_init(&ps.bar[0], 1);
+      mbar_init(&ps.bar[1], 1);
       mbar_fence_init();
     }
     __syncthreads();
@@ -241,12 +368,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     const uint32_t stage_tx = d.key_page_bytes + kValueCodes + vmeta_page_bytes;
     auto issue = [&](int pg, int stage) {
       // one lane starts the three bulk copies of a page; the barrier completes when all bytes landed
-      mbar_expect_tx(&ws.bar[stage], stage_tx);
+      mbar_expect_tx(&ps.bar[stage], stage_tx);
       const int64_t vrow = (int64_t)bh * d.max_value_tokens + (int64_t)pg * 128;
-      bulk_copy_g2s(ws.stage[stage], d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes, d.key_page_bytes, &ws.bar[stage]);
-      bulk_copy_g2s(ws.stage[stage] + kOffVCodes, d.v_codes + vrow * 32, kValueCodes, &ws.bar[stage]);
-      bulk_copy_g2s(ws.stage[stage] + kOffVMeta,
-                    reinterpret_cast<const uint8_t*>(d.v_meta) + vrow * (2 * d.value_groups * 2), vmeta_page_bytes, &ws.bar[stage]);
+      bulk_copy_g2s(ps.stage[stage], d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes, d.key_page_bytes, &ps.bar[stage]);
+      bulk_copy_g2s(ps.stage[stage] + kOffVCodes, d.v_codes + vrow * 32, kValueCodes, &ps.bar[stage]);
+      bulk_copy_g2s(ps.stage[stage] + kOffVMeta,
+                    reinterpret_cast<const uint8_t*>(d.v_meta) + vrow * (2 * d.value_groups * 2), vmeta_page_bytes, &ps.bar[stage]);
     };
 
     float o_acc[4][4];   // [m-tile][c-reg]: head c, channel 16g + 2mt + r + 8j'
@@ -265,37 +392,36 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     CodeConsts<DT> cc;
     cc.init();
 
-    int pg0 = p_begin + warp;
-    if (lane == 0) {
+    const int pg0 = p_begin + pair;
+    if (issuer) {
       if (pg0 < p_end) issue(pg0, 0);
-      if (pg0 + kWarps < p_end) issue(pg0 + kWarps, 1);
+      if (pg0 + kPairs < p_end) issue(pg0 + kPairs, 1);
     }
     int iter = 0;
-    for (int pg = pg0; pg < p_end; pg += kWarps, ++iter) {
+    for (int pg = pg0; pg < p_end; pg += kPairs, ++iter) {
       const int stage = iter & 1;
       const uint32_t parity = (iter >> 1) & 1;
-      ok = mbar_wait(&ws.bar[stage], parity) && ok;
-      const uint8_t* blob = ws.stage[stage];
-      const uint32_t* low = reinterpret_cast<const uint32_t*>(blob);
-      const uint32_t* high = reinterpret_cast<const uint32_t*>(blob + d.key_off_high);
+      ok = mbar_wait(&ps.bar[stage], parity) && ok;
+      const uint8_t* blob = ps.stage[stage];
       const uint16_t* kscale = reinterpret_cast<const uint16_t*>(blob + d.key_off_scale);
       const uint16_t* kzero = reinterpret_cast<const uint16_t*>(blob + d.key_off_zero);
 
-      // ---- channel contraction order (promoted slots first) and per-channel constants
-      reinterpret_cast<uint32_t*>(ws.is_promoted)[lane] = 0;
-      __syncwarp();
-      if (K > 0) {
-        const int32_t* idx = reinterpret_cast<const int32_t*>(blob + d.key_off_index);
-        for (int k = lane; k < K; k += 32) {
-          const int ch = idx[k] & 127;
-          ws.is_promoted[ch] = 1;
-          ws.order[k] = (uint8_t)ch;
+      // ---- shared per-page setup: warp 0 of the pair orders the channels (promoted slots first),
+      // both warps compute the per-channel constants of their half of the channels
+      if (hf == 0) {
+        reinterpret_cast<uint32_t*>(ps.is_promoted)[lane] = 0;
+        __syncwarp();
+        if (K > 0) {
+          const int32_t* idx = reinterpret_cast<const int32_t*>(blob + d.key_off_index);
+          for (int k = lane; k < K; k += 32) {
+            const int ch = idx[k] & 127;
+            ps.is_promoted[ch] = 1;
+            ps.order[k] = (uint8_t)ch;
+          }
         }
-      }
-      __syncwarp();
-      {
-        const uint32_t flags = reinterpret_cast<const uint32_t*>(ws.is_promoted)[lane];   // channels 4*lane .. +3
-        int mine = 4 - __popc(flags & 0x01010101u);
+        __syncwarp();
+        const uint32_t flags = reinterpret_cast<const uint32_t*>(ps.is_promoted)[lane];   // channels 4*lane .. +3
+        const int mine = 4 - __popc(flags & 0x01010101u);
         int before = mine;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
@@ -305,129 +431,26 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
         int pos = K + before - mine;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          if (!((flags >> (8 * i)) & 1u)) ws.order[pos++] = (uint8_t)(4 * lane + i);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int ch = lane + 32 * i;
-          const uint32_t ss = (uint32_t)kscale[ch] * 0x00010001u;
-          const uint32_t zz = (uint32_t)kzero[ch] * 0x00010001u;
-          ws.kpar4[ch] = make_uint4(ss, zz, H::mul(ss, H::neg_magic(0)), H::mul(ss, H::neg_magic(1)));
-          ws.kpar1[ch] = H::mul(ss, H::neg_magic(2));
-        }
+          if (!((flags >> (8 * i)) & 1u)) ps.order[pos++] = (uint8_t)(4 * lane + i);
       }
-      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int ch = 64 * hf + lane + 32 * i;
+        const uint32_t ss = (uint32_t)kscale[ch] * 0x00010001u;
+        const uint32_t zz = (uint32_t)kzero[ch] * 0x00010001u;
+        ps.kpar4[ch] = make_uint4(ss, zz, H::mul(ss, H::neg_magic(0)), H::mul(ss, H::neg_magic(1)));
+        ps.kpar1[ch] = H::mul(ss, H::neg_magic(2));
+      }
+      pair_barrier(pair);
 
-      // ---- logits: S[token pair][(head, j')] over the doubled contraction (channel, j)
-      float s_acc[4][4];
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) s_acc[mt][i] = 0.0f;
-      for (int ks = 0; ks < prom_steps; ++ks) {
-        const int s0 = 8 * ks + c, s1 = s0 + 4;
-        const int ch0 = ws.order[s0], ch1 = ws.order[s1];
-        const uint4 p0 = ws.kpar4[ch0], p1 = ws.kpar4[ch1];
-        const uint32_t w0 = low[ch0 * 8 + g], w1 = low[ch1 * 8 + g];
-        const uint32_t h0 = s0 < K ? high[s0 * 8 + g] : 0u;
-        const uint32_t h1 = s1 < K ? high[s1 * 8 + g] : 0u;
-        uint32_t r0[8], r1[8];
-        dequant_word4<DT>(cc, w0, h0, p0.x, p0.y, p0.z, p0.w, r0);
-        dequant_word4<DT>(cc, w1, h1, p1.x, p1.y, p1.z, p1.w, r1);
-        const uint32_t b0 = qsel[ch0], b1 = qsel[ch1];
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) H::mma(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
-      }
-#pragma unroll 2
-      for (int ks = prom_steps; ks < 16; ++ks) {
-        const int ch0 = ws.order[8 * ks + c], ch1 = ws.order[8 * ks + c + 4];
-        const uint4 p0 = ws.kpar4[ch0], p1 = ws.kpar4[ch1];
-        const uint32_t w0 = low[ch0 * 8 + g], w1 = low[ch1 * 8 + g];
-        uint32_t r0[8], r1[8];
-        dequant_word2<DT>(cc, w0, p0.x, p0.y, p0.z, p0.w, ws.kpar1[ch0], r0);
-        dequant_word2<DT>(cc, w1, p1.x, p1.y, p1.z, p1.w, ws.kpar1[ch1], r1);
-        const uint32_t b0 = qsel[ch0], b1 = qsel[ch1];
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) H::mma(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
-      }
+      if (hf == 0)
+        page_half<DT, 0>(d, ps, blob, ps.prob[0], qsel, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
+      else
+        page_half<DT, 1>(d, ps, blob, ps.prob[1], qsel, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
 
-      // ---- online softmax for head c over this page's 128 tokens (this thread: tokens 16g .. 16g+15)
-      float mx = -INFINITY;
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          s_acc[mt][i] *= scale2;
-          mx = fmaxf(mx, s_acc[mt][i]);
-        }
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-      const float m_new = fmaxf(m_run, mx);
-      const float alpha = fast_exp2(m_run - m_new);
-      m_run = m_new;
-      float psum = 0.0f;
-      uint16_t phi[16], plo[16];
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float p = fast_exp2(s_acc[mt][i] - m_new);
-          psum += p;
-          const int tok = 2 * mt + (i >> 1) + 8 * (i & 1);   // offset inside this thread's 16 tokens
-          const uint16_t hi = H::from_float(p);
-          phi[tok] = hi;
-          plo[tok] = H::from_float(p - H::to_float(hi));
-        }
-      l_run = l_run * alpha + psum;
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) o_acc[mt][i] *= alpha;
-      {
-        uint32_t* hi_row = reinterpret_cast<uint32_t*>(&ws.prob[(0 * 4 + c) * kPStride + 16 * g]);
-        uint32_t* lo_row = reinterpret_cast<uint32_t*>(&ws.prob[(1 * 4 + c) * kPStride + 16 * g]);
-        uint32_t hw[8], lw[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          hw[i] = (uint32_t)phi[2 * i] | ((uint32_t)phi[2 * i + 1] << 16);
-          lw[i] = (uint32_t)plo[2 * i] | ((uint32_t)plo[2 * i + 1] << 16);
-        }
-        reinterpret_cast<uint4*>(hi_row)[0] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-        reinterpret_cast<uint4*>(hi_row)[1] = make_uint4(hw[4], hw[5], hw[6], hw[7]);
-        reinterpret_cast<uint4*>(lo_row)[0] = make_uint4(lw[0], lw[1], lw[2], lw[3]);
-        reinterpret_cast<uint4*>(lo_row)[1] = make_uint4(lw[4], lw[5], lw[6], lw[7]);
-      }
-      __syncwarp();
-
-      // ---- O[channel pair][(head, j')] += V^T P over the doubled contraction (token, j)
-      const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(blob + kOffVCodes);
-      const uint16_t* vmeta = reinterpret_cast<const uint16_t*>(blob + kOffVMeta);
-      const uint16_t* prob_hi = &ws.prob[(0 * 4 + hq) * kPStride];
-      const uint16_t* prob_lo = &ws.prob[(1 * 4 + hq) * kPStride];
-      const int vg2 = 2 * d.value_groups;
-      const int shift = 16 * jp;
-#pragma unroll 2
-      for (int ks = 0; ks < 16; ++ks) {
-        const int t0 = 8 * ks + c, t1 = t0 + 4;
-        const uint32_t w0 = vcodes[t0 * 8 + g], w1 = vcodes[t1 * 8 + g];
-        const uint32_t ss0 = (uint32_t)vmeta[t0 * vg2 + gv] * 0x00010001u;
-        const uint32_t zz0 = (uint32_t)vmeta[t0 * vg2 + d.value_groups + gv] * 0x00010001u;
-        const uint32_t ss1 = (uint32_t)vmeta[t1 * vg2 + gv] * 0x00010001u;
-        const uint32_t zz1 = (uint32_t)vmeta[t1 * vg2 + d.value_groups + gv] * 0x00010001u;
-        uint32_t r0[8], r1[8];
-        dequant_word2<DT>(cc, w0, ss0, zz0, H::mul(ss0, H::neg_magic(0)), H::mul(ss0, H::neg_magic(1)), H::mul(ss0, H::neg_magic(2)), r0);
-        dequant_word2<DT>(cc, w1, ss1, zz1, H::mul(ss1, H::neg_magic(0)), H::mul(ss1, H::neg_magic(1)), H::mul(ss1, H::neg_magic(2)), r1);
-        const uint32_t ph0 = (uint32_t)prob_hi[t0] << shift, ph1 = (uint32_t)prob_hi[t1] << shift;
-        const uint32_t pl0 = (uint32_t)prob_lo[t0] << shift, pl1 = (uint32_t)prob_lo[t1] << shift;
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-          H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], ph0, ph1);
-          H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], pl0, pl1);
-        }
-      }
-      __syncwarp();
+      pair_barrier(pair);
       // the stage is free again: prefetch the page two iterations ahead
-      if (lane == 0 && pg + 2 * kWarps < p_end) issue(pg + 2 * kWarps, stage);
+      if (issuer && pg + 2 * kPairs < p_end) issue(pg + 2 * kPairs, stage);
     }
     if (!ok && lane == 0) atomicExch(a.status, 1);
 
@@ -447,9 +470,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
   }
   __syncthreads();
 
-  // ---- block merge: thread = channel, loop over heads; partials leave in natural-log units
+  // ---- block merge: thread = (channel, head parity); partials leave in natural-log units
   const int slot = a.split_base + split;
-  for (int r = 0; r < rep; ++r) {
+  const int ch = tid & 127;
+  for (int r = tid >> 7; r < rep; r += kThreads / 128) {
     float m = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) m = fmaxf(m, bs.merge_m[w][r]);
@@ -458,21 +482,21 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     for (int w = 0; w < kWarps; ++w) {
       const float mw = bs.merge_m[w][r];
       if (mw != -INFINITY) {
-        const float wgt = exp2f(mw - m);
+        const float wgt = fast_exp2(mw - m);
         l += bs.merge_l[w][r] * wgt;
-        acc += warp_out[(w * 4 + r) * 128 + tid] * wgt;
+        acc += warp_out[(w * 4 + r) * 128 + ch] * wgt;
       }
     }
     const int64_t row = ((int64_t)b * a.query_heads + hkv * rep + r) * a.total_splits + slot;
-    if (tid == 0) {
+    if (ch == 0) {
       a.part_m[row] = m == -INFINITY ? -INFINITY : m * 0.6931471805599453f;
       a.part_l[row] = l;
     }
-    a.part_acc[row * 128 + tid] = acc;
+    a.part_acc[row * 128 + ch] = acc;
   }
 }
 
-constexpr size_t kSmemBytes = sizeof(WarpSmem) * kWarps + sizeof(BlockSmem);
+constexpr size_t kSmemBytes = sizeof(PairSmem) * kPairs + sizeof(BlockSmem);
 
 }  // namespace
 

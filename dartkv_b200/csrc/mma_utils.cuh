@@ -196,3 +196,45 @@ __device__ __forceinline__ void dequant_word4(const CodeConsts<DT>& k, uint32_t 
     }
   }
 }
+
+// ---------------------------------------------------------------------------- half-word variants
+// Two warps share a staged page; warp half HF owns codes 4*HF .. 4*HF+3 of every 16-bit half.
+template <int DT, int HF>
+__device__ __forceinline__ void dequant_half2(const CodeConsts<DT>& k, uint32_t w, uint32_t ss, uint32_t zz,
+                                              uint32_t ms0, uint32_t ms1, uint32_t ms2, uint32_t (&r)[4]) {
+  using H = Half2Ops<DT>;
+  constexpr int P0 = H::kFirstPos;
+  if (HF == 0) {
+    const uint32_t xa = align_codes(w, 0, P0);   // codes 0,1,2 at positions 0,1,2
+    const uint32_t xb = align_codes(w, 3, P0);   // code 3 at position 0
+    r[0] = H::add(H::fma(and_or(xa, k.mask[0], k.magic[0]), ss, ms0), zz);
+    r[1] = H::add(H::fma(and_or(xa, k.mask[1], k.magic[1]), ss, ms1), zz);
+    r[2] = H::add(H::fma(and_or(xa, k.mask[2], k.magic[2]), ss, ms2), zz);
+    r[3] = H::add(H::fma(and_or(xb, k.mask[0], k.magic[0]), ss, ms0), zz);
+  } else {
+    const uint32_t xa = align_codes(w, 3, P0);   // codes 4,5 at positions 1,2
+    const uint32_t xb = align_codes(w, 6, P0);   // codes 6,7 at positions 0,1
+    r[0] = H::add(H::fma(and_or(xa, k.mask[1], k.magic[1]), ss, ms1), zz);
+    r[1] = H::add(H::fma(and_or(xa, k.mask[2], k.magic[2]), ss, ms2), zz);
+    r[2] = H::add(H::fma(and_or(xb, k.mask[0], k.magic[0]), ss, ms0), zz);
+    r[3] = H::add(H::fma(and_or(xb, k.mask[1], k.magic[1]), ss, ms1), zz);
+  }
+}
+
+template <int DT, int HF>
+__device__ __forceinline__ void dequant_half4(const CodeConsts<DT>& k, uint32_t wl, uint32_t wh, uint32_t ss,
+                                              uint32_t zz, uint32_t ms0, uint32_t ms1, uint32_t (&r)[4]) {
+  using H = Half2Ops<DT>;
+  constexpr int P0 = H::kFirstPos;
+#pragma unroll
+  for (int grp = 0; grp < 2; ++grp) {
+    const int code = 4 * HF + 2 * grp;
+    const uint32_t xl = align_codes(wl, code, P0);
+    const uint32_t xh = align_codes(wh, code, P0, 2);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t m = and_or(xh, k.mask[j + 1], and_or(xl, k.mask[j], k.magic[j]));
+      r[2 * grp + j] = H::add(H::fma(m, ss, j == 0 ? ms0 : ms1), zz);
+    }
+  }
+}
