@@ -28,7 +28,8 @@ EXPORTS = (
     "dartkv_last_error", "dartkv_version", "dartkv_launch_count", "dartkv_pack", "dartkv_unpack", "dartkv_quantize", "dartkv_dequantize",
     "dartkv_channel_scores", "dartkv_select_channels", "dartkv_quantize_key_mixed", "dartkv_dequantize_key_mixed",
     "dartkv_cache_geometry", "dartkv_cache_append", "dartkv_cache_materialize", "dartkv_decode_workspace_bytes",
-    "dartkv_decode_attention", "dartkv_decode_status",
+    "dartkv_decode_attention", "dartkv_decode_status", "dartkv_builtin_scratch_bytes",
+    "dartkv_decode_attention_builtin_scratch",
 )
 
 
@@ -91,6 +92,8 @@ def _load() -> ctypes.CDLL:
     lib.dartkv_decode_workspace_bytes.restype = c_int64
     lib.dartkv_decode_attention.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, i64, p, p]
     lib.dartkv_decode_status.argtypes = [p, POINTER(c_int), p]
+    lib.dartkv_builtin_scratch_bytes.restype = c_int64
+    lib.dartkv_decode_attention_builtin_scratch.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, p]
     for name in EXPORTS:
         fn = getattr(lib, name)
         if fn.restype is c_int and name not in ("dartkv_version",):

@@ -342,3 +342,61 @@ extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* q
   DARTKV_LAUNCH_OK("decode_merge_kernel");
   return DARTKV_OK;
 }
+
+// ---------------------------------------------------------------------------- built-in scratch variant
+// Split-K scratch that lives in the library image instead of caller memory.  Every device that
+// loads the library carries these 32 MiB until the process exits.
+#define DARTKV_BUILTIN_SCRATCH_BYTES (32ll << 20)
+static __device__ __align__(256) unsigned char g_builtin_scratch[DARTKV_BUILTIN_SCRATCH_BYTES];
+
+#include <mutex>
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_address[kMaxDevices] = {};   // device address of g_builtin_scratch, per device ordinal
+}  // namespace
+
+// In host code `g_builtin_scratch` is only a handle for the symbol, not memory a kernel can use:
+// the device address has to be asked for, with the target device current, once per device.
+static int builtin_scratch_address(void** out) {
+  int device = -1;
+  DARTKV_CUDA_OK(cudaGetDevice(&device));
+  DARTKV_REQUIRE(device >= 0 && device < kMaxDevices, "device ordinal %d is outside the supported range", device);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_address[device] == nullptr) {
+    void* address = nullptr;
+    DARTKV_CUDA_OK(cudaGetSymbolAddress(&address, g_builtin_scratch));
+    DARTKV_REQUIRE(address != nullptr, "cudaGetSymbolAddress returned a null address for the built-in scratch");
+    g_scratch_address[device] = address;
+  }
+  *out = g_scratch_address[device];
+  return DARTKV_OK;
+}
+
+extern "C" int64_t dartkv_builtin_scratch_bytes(void) { return DARTKV_BUILTIN_SCRATCH_BYTES; }
+
+extern "C" int dartkv_decode_attention_builtin_scratch(const dartkv_cache_desc* d, const void* query, int q_dtype,
+                                                       int query_heads, float scale, int flavour, int tokens,
+                                                       void* out, void* stream) {
+  DARTKV_REQUIRE(d != nullptr, "null descriptor");
+  DARTKV_REQUIRE(dartkv_valid_dtype(q_dtype), "query must be f32, f16 or bf16");
+  DARTKV_REQUIRE(query_heads > 0 && query_heads % d->kv_heads == 0, "query heads must be divisible by cache KV heads");
+  DARTKV_REQUIRE(tokens > 0, "cache is empty");
+  DARTKV_REQUIRE(flavour == DARTKV_DEQUANT_PER_OP || flavour == DARTKV_DEQUANT_FP32, "unknown dequant flavour %d", flavour);
+  const DecodeLayout L = decode_layout(d, q_dtype, query_heads, flavour, tokens);
+  const int64_t need = layout_bytes(d, query_heads, L);
+  if (need > DARTKV_BUILTIN_SCRATCH_BYTES) {
+    dartkv_set_error("this call needs %lld bytes of split scratch but the built-in scratch holds %lld; "
+                     "use dartkv_decode_attention with a caller-provided workspace",
+                     (long long)need, (long long)DARTKV_BUILTIN_SCRATCH_BYTES);
+    return DARTKV_ELIMIT;
+  }
+  void* scratch = nullptr;
+  int rc = builtin_scratch_address(&scratch);
+  if (rc) return rc;
+  // the array keeps whatever the previous call left; only the status word has to start at zero
+  DARTKV_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, (cudaStream_t)stream));
+  return dartkv_decode_attention(d, query, q_dtype, query_heads, scale, flavour, tokens, scratch,
+                                 DARTKV_BUILTIN_SCRATCH_BYTES, out, stream);
+}

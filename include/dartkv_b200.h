@@ -184,6 +184,25 @@ int dartkv_decode_attention(const dartkv_cache_desc* desc, const void* query, in
 /* Copies the workspace status word to the host (synchronizes the stream): 0 = no bounded wait expired. */
 int dartkv_decode_status(const void* workspace, int* status_out, void* stream);
 
+/* Decode attention for callers that cannot hand over scratch memory.  No counterpart in the
+ * reference: this exists for hosts embedding the library where device allocation is off limits at
+ * the call site -- a serving loop whose memory pool is sized and frozen at start-up, a plugin
+ * running inside another runtime's allocator-free callback, a real-time path that must not touch
+ * the driver's allocator.  Same arguments and results as dartkv_decode_attention minus the
+ * workspace: the split-K partials go to a 32 MiB array that is part of the library image (every
+ * GPU that loads the library holds it until the process exits).
+ *  - Calls whose partials need more than dartkv_builtin_scratch_bytes() fail with DARTKV_ELIMIT
+ *    and a message giving both sizes (roughly batch * query_heads * splits * 520 bytes).
+ *  - The first call on each device looks up the array's device address; make that first call
+ *    outside any stream capture.  The call itself allocates nothing.
+ *  - All calls share the one array and it keeps the previous call's contents (the status word is
+ *    re-zeroed on the stream each call): two calls that overlap on the GPU, e.g. on different
+ *    streams, race.  Serialize them or use the workspace variant. */
+int64_t dartkv_builtin_scratch_bytes(void);
+int dartkv_decode_attention_builtin_scratch(const dartkv_cache_desc* desc, const void* query, int q_dtype,
+                                            int query_heads, float scale, int flavour, int tokens, void* out,
+                                            void* stream);
+
 #ifdef __cplusplus
 }
 #endif
