@@ -262,9 +262,10 @@ def gpu_arm(args, wl) -> None:
     torch.cuda.set_device(device)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    if wl["batch"] % world:
-        raise SystemExit("batch must divide evenly over the GPUs")
-    local_batch = wl["batch"] // world
+    from dartkv_b200.sharding import shard_rows
+
+    lo, hi = shard_rows(wl["batch"], world, rank)
+    local_batch = hi - lo
     cache, query = build_device_cache(local_batch, wl["ctx"], wl["seed"], rank, device)
     hq, d = GEOM["query_heads"], GEOM["head_dim"]
     out = torch.empty((local_batch, hq, d), dtype=torch.bfloat16, device=device)

@@ -1,0 +1,144 @@
+"""Hugging Face ``Cache`` facade over per-layer device-resident Dart caches.
+
+Mirrors ``src/dart/integrations/huggingface.py:19-147`` of the reference: one ``DartKVCache`` per
+layer, PostQuant return timing (the attention call of a step sees the K/V of that step before
+they are packed), ``layer_for_attention`` / ``last_update_was_prefill`` for the fused decode hook,
+page descriptors, beam reorder and byte accounting.  Works with Transformers 4.5x and 5.x, whose
+``Cache`` constructors differ.
+"""
+
+from __future__ import annotations
+
+import inspect
+from typing import Dict, Optional
+
+import torch
+
+from ..cache import DartKVCache, DartKVCacheConfig
+
+try:
+    from transformers import Cache
+except ImportError as exc:  # pragma: no cover - exercised only without the optional dependency
+    raise ImportError("DartHFCache requires transformers; install the model dependencies first.") from exc
+
+
+class DartHFCache(Cache):
+    """A Transformers cache whose layers are packed Dart caches.
+
+    ``update`` returns dense tensors for the standard attention backends unless the caller passes
+    ``{"dart_fused_attention": True}`` in ``cache_kwargs`` (the fused decode hook does), in which
+    case only the new K/V come back and nothing is materialized.  ``max_tokens`` pre-sizes every
+    layer's pools.
+    """
+
+    is_compileable = False
+
+    def __init__(self, config: Optional[DartKVCacheConfig] = None, *, max_tokens: Optional[int] = None) -> None:
+        parameters = inspect.signature(Cache.__init__).parameters
+        if "layers" in parameters:
+            super().__init__(layers=[])      # Transformers 5.x wants an explicit (empty) layer list
+        else:
+            super().__init__()
+        self.dart_config = config or DartKVCacheConfig()
+        self._max_tokens = max_tokens
+        self._layers: Dict[int, DartKVCache] = {}
+        self._last_update_prefill: Dict[int, bool] = {}
+        self._seen_tokens = 0
+
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
+               cache_kwargs: Optional[dict] = None, *args, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
+        fused_update = bool(cache_kwargs and cache_kwargs.get("dart_fused_attention"))
+        if layer_idx == 0:
+            self._seen_tokens += key_states.shape[-2]
+        layer = self._layers.get(layer_idx)
+        if layer is None:
+            layer = DartKVCache(self.dart_config, max_tokens=self._max_tokens)
+            self._layers[layer_idx] = layer
+            self._last_update_prefill[layer_idx] = True
+            keys_to_return, values_to_return = key_states, value_states
+        else:
+            self._last_update_prefill[layer_idx] = False
+            if fused_update:
+                # the fused decode path reads the packed pages itself: nothing to materialize
+                keys_to_return, values_to_return = key_states, value_states
+            else:
+                prior_keys, prior_values = layer.get()
+                keys_to_return = torch.cat((prior_keys, key_states), dim=-2)
+                values_to_return = torch.cat((prior_values, value_states), dim=-2)
+        # append copies what it keeps (sink / ring rows) or packs it, so the inputs need no clone
+        layer.append(key_states, value_states)
+        return keys_to_return, values_to_return
+
+    def layer_for_attention(self, layer_idx: int) -> DartKVCache:
+        """A layer's packed cache for the fused attention hook."""
+
+        try:
+            return self._layers[layer_idx]
+        except KeyError as exc:
+            raise RuntimeError(f"layer {layer_idx} has not been initialized") from exc
+
+    def last_update_was_prefill(self, layer_idx: int) -> bool:
+        """Whether the most recent update for ``layer_idx`` created the layer."""
+
+        return self._last_update_prefill.get(layer_idx, False)
+
+    def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:
+        if layer_idx is None:
+            layer_idx = 0
+        layer = self._layers.get(layer_idx)
+        return layer.get_seq_length() if layer is not None else 0
+
+    def get_max_cache_shape(self, *args, **kwargs) -> None:
+        return None
+
+    def get_mask_sizes(self, cache_position, layer_idx: int = 0):
+        """(kv_length, kv_offset) for mask construction: everything cached plus the incoming tokens."""
+
+        query_length = cache_position.shape[0] if hasattr(cache_position, "shape") else int(cache_position)
+        return self.get_seq_length(layer_idx) + query_length, 0
+
+    def page_table(self, layer_idx: int = 0, *, device: torch.device | str | None = None, rebuild: bool = False):
+        layer = self._layers.get(layer_idx)
+        return layer.page_table(device=device, rebuild=rebuild) if layer is not None else None
+
+    def page_runs(self, layer_idx: int = 0, *, device: torch.device | str | None = None, rebuild: bool = False):
+        layer = self._layers.get(layer_idx)
+        return layer.page_runs(device=device, rebuild=rebuild) if layer is not None else None
+
+    def reorder_cache(self, beam_idx: torch.LongTensor) -> "DartHFCache":
+        """Rebuild the selected beams from the dequantized contents (reference huggingface.py:117-127)."""
+
+        for layer_idx, layer in list(self._layers.items()):
+            keys, values = layer.get()
+            indices = beam_idx.to(keys.device)
+            rebuilt = DartKVCache(self.dart_config, max_tokens=self._max_tokens)
+            rebuilt.update(keys.index_select(0, indices), values.index_select(0, indices))
+            self._layers[layer_idx] = rebuilt
+        self._last_update_prefill.clear()
+        return self
+
+    @property
+    def key_cache(self) -> list[torch.Tensor]:
+        return [self._layers[index].key_states for index in sorted(self._layers)]
+
+    @property
+    def value_cache(self) -> list[torch.Tensor]:
+        return [self._layers[index].value_states for index in sorted(self._layers)]
+
+    @property
+    def storage_bytes(self) -> int:
+        return sum(layer.storage_bytes for layer in self._layers.values())
+
+    @property
+    def dense_bytes(self) -> int:
+        return sum(layer.dense_bytes for layer in self._layers.values())
+
+    @property
+    def compression_ratio(self) -> float:
+        return self.dense_bytes / self.storage_bytes if self.storage_bytes else 1.0
+
+    def __len__(self) -> int:
+        return len(self._layers)
+
+
+__all__ = ["DartHFCache"]

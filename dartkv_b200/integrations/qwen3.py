@@ -1,0 +1,89 @@
+"""Qwen3 attention adapter that decodes straight from the packed Dart cache.
+
+Mirrors ``src/dart/integrations/qwen3.py:30-124`` of the reference: prefill goes through the
+model's regular attention backend, one-token decode steps call ``fused_dart_attention`` on the
+layer's packed pages.  The forward accepts both spellings of the cache argument
+(``past_key_value`` up to Transformers 4.5x, ``past_key_values`` from 5.x on).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ..fused_attention import fused_dart_attention
+from .huggingface import DartHFCache
+
+
+def _qwen3_modules():
+    from transformers.models.qwen3 import modeling_qwen3 as modules
+
+    return modules
+
+
+def build_dart_qwen3_attention_class():
+    """Build the Qwen3 attention subclass against the installed Transformers."""
+
+    modules = _qwen3_modules()
+    base = modules.Qwen3Attention
+
+    class _DartQwen3Attention(base):
+        def forward(self, hidden_states: torch.Tensor, position_embeddings, attention_mask: Optional[torch.Tensor] = None,
+                    past_key_values=None, cache_position: Optional[torch.LongTensor] = None, past_key_value=None,
+                    **kwargs):
+            cache = past_key_values if past_key_values is not None else past_key_value
+            input_shape = hidden_states.shape[:-1]
+            hidden_shape = (*input_shape, -1, self.head_dim)
+            query_states = self.q_norm(self.q_proj(hidden_states).view(hidden_shape)).transpose(1, 2)
+            key_states = self.k_norm(self.k_proj(hidden_states).view(hidden_shape)).transpose(1, 2)
+            value_states = self.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+            cos, sin = position_embeddings
+            query_states, key_states = modules.apply_rotary_pos_emb(query_states, key_states, cos, sin)
+
+            use_dart_decode = isinstance(cache, DartHFCache)
+            if cache is not None:
+                if use_dart_decode:
+                    cache_kwargs = {"sin": sin, "cos": cos, "cache_position": cache_position, "dart_fused_attention": True}
+                    key_states, value_states = cache.update(key_states, value_states, self.layer_idx, cache_kwargs)
+                else:
+                    key_states, value_states = cache.update(key_states, value_states, self.layer_idx)
+
+            output_attentions = bool(kwargs.get("output_attentions", False))
+            if (use_dart_decode and not cache.last_update_was_prefill(self.layer_idx)
+                    and query_states.shape[-2] == 1 and not output_attentions):
+                # uniform-length batches only: like the reference, the fused path ignores attention_mask
+                attn_output = fused_dart_attention(
+                    query_states, cache.layer_for_attention(self.layer_idx), scale=self.scaling, fallback=True,
+                ).transpose(1, 2).contiguous()
+                attn_weights = None
+            else:
+                interface = modules.eager_attention_forward
+                if self.config._attn_implementation != "eager":
+                    interface = modules.ALL_ATTENTION_FUNCTIONS[self.config._attn_implementation]
+                attn_output, attn_weights = interface(
+                    self, query_states, key_states, value_states, attention_mask,
+                    dropout=0.0 if not self.training else self.attention_dropout, scaling=self.scaling,
+                    sliding_window=self.sliding_window, **kwargs)
+            attn_output = attn_output.reshape(*input_shape, -1).contiguous()
+            return self.o_proj(attn_output), attn_weights
+
+    _DartQwen3Attention.__name__ = "DartQwen3Attention"
+    return _DartQwen3Attention
+
+
+def attach_dart_fused_attention(model: nn.Module) -> nn.Module:
+    """Replace every Qwen3 self-attention module with the Dart adapter (weights are shared, not copied)."""
+
+    attention_class = build_dart_qwen3_attention_class()
+    layers = getattr(getattr(model, "model", None), "layers", None)
+    if layers is None:
+        raise TypeError("attach_dart_fused_attention expects a Qwen3 causal-LM model")
+    for layer in layers:
+        original = layer.self_attn
+        original.__class__ = attention_class   # same parameters and buffers, new forward
+    return model
+
+
+__all__ = ["attach_dart_fused_attention", "build_dart_qwen3_attention_class"]

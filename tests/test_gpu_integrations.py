@@ -1,0 +1,90 @@
+"""DartHFCache and the Qwen3 decode hook on a tiny random-weight Qwen3 (reference
+tests/test_cache.py:265-308 and tests/test_reproduction.py:353-395)."""
+
+import pytest
+import torch
+
+import dartkv_b200 as dart
+from dartkv_b200.integrations import DartHFCache, attach_dart_fused_attention
+
+pytestmark = pytest.mark.gpu
+
+
+def tiny_model(head_dim=8, dtype=torch.float32):
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    torch.manual_seed(0)
+    config = Qwen3Config(vocab_size=97, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=head_dim, max_position_embeddings=128)
+    config._attn_implementation = "eager"
+    return Qwen3ForCausalLM(config).to(dtype).cuda().eval()
+
+
+def test_hf_cache_postquant_return_and_reorder():
+    torch.manual_seed(60)
+    cfg = dart.DartKVCacheConfig(page_size=4, hold_partial_pages=True, key_group_size=4, value_group_size=4,
+                                 metadata_dtype=torch.float32)
+    cache = DartHFCache(cfg)
+    keys = torch.randn(2, 2, 6, 8).cuda()
+    values = torch.randn_like(keys)
+    k0, v0 = cache.update(keys[..., :5, :], values[..., :5, :], 0)
+    # prefill returns the raw tensors (attention sees the step's K/V before they are packed)
+    assert torch.equal(k0, keys[..., :5, :]) and cache.last_update_was_prefill(0)
+    assert cache.get_seq_length() == 5
+    k1, v1 = cache.update(keys[..., 5:, :], values[..., 5:, :], 0)
+    assert not cache.last_update_was_prefill(0)
+    assert k1.shape[-2] == 6 and torch.equal(k1[..., 5:, :], keys[..., 5:, :])
+    prior, _ = cache.layer_for_attention(0).get()
+    assert torch.equal(k1[..., :5, :], prior[..., :5, :])       # history comes back dequantized
+    k2, _ = cache.update(keys[..., :1, :], values[..., :1, :], 0, {"dart_fused_attention": True})
+    assert k2.shape[-2] == 1                                     # fused update: only the new token
+    assert cache.storage_bytes < cache.dense_bytes and cache.compression_ratio > 1.0
+    assert cache.page_table(0).seen_tokens == 7 and cache.get_max_cache_shape() is None
+    before = cache.layer_for_attention(0).get()[0]
+    cache.reorder_cache(torch.tensor([1, 0]).cuda())
+    after = cache.layer_for_attention(0).get()[0]
+    assert after.shape == before.shape
+    with pytest.raises(RuntimeError, match="not been initialized"):
+        cache.layer_for_attention(3)
+
+
+@pytest.mark.parametrize("head_dim,dtype", [(8, torch.float32), (128, torch.bfloat16)])
+def test_tiny_qwen3_dart_engine_generation(head_dim, dtype):
+    model = attach_dart_fused_attention(tiny_model(head_dim, dtype))
+    page = 4 if head_dim == 8 else 128
+    cfg = dart.DartKVCacheConfig(
+        bits=2, page_size=page, hold_partial_pages=True, local_tokens=1, value_local_tokens=page,
+        key_group_size=page, value_group_size=min(64, head_dim), sink_tokens=2, promote_ratio=0.25,
+        metadata_dtype=torch.float32 if dtype == torch.float32 else dtype)
+    prompt_len, new_tokens = (13, 20) if head_dim == 8 else (150, 140)
+    torch.manual_seed(1)
+    prompt = torch.randint(0, 97, (2, prompt_len)).cuda()
+    cache = DartHFCache(cfg)
+    with torch.no_grad():
+        out = model.generate(prompt, max_new_tokens=new_tokens, min_new_tokens=new_tokens, do_sample=False,
+                             past_key_values=cache, use_cache=True, disable_compile=True, pad_token_id=0)
+    assert out.shape == (2, prompt_len + new_tokens)
+    assert cache.get_seq_length() == prompt_len + new_tokens - 1
+    for layer in range(2):
+        assert cache.layer_for_attention(layer).decode_status() == 0
+        cache.layer_for_attention(layer).check_finite()
+
+
+def test_fused_hook_matches_materializing_path_logits():
+    """One decode step: the fused hook equals dense attention over the materialized (dequantized) cache."""
+
+    model = tiny_model(8, torch.float32)
+    cfg = dart.DartKVCacheConfig(bits=4, page_size=4, hold_partial_pages=True, key_group_size=4, value_group_size=8,
+                                 sink_tokens=1, promote_ratio=0.25, metadata_dtype=torch.float32)
+    torch.manual_seed(2)
+    prompt = torch.randint(0, 97, (2, 11)).cuda()
+    nxt = torch.randint(0, 97, (2, 1)).cuda()
+    with torch.no_grad():
+        plain = DartHFCache(cfg)
+        model(prompt, past_key_values=plain, use_cache=True)
+        expected = model(nxt, past_key_values=plain, use_cache=True).logits
+        attach_dart_fused_attention(model)
+        fused = DartHFCache(cfg)
+        model(prompt, past_key_values=fused, use_cache=True)
+        got = model(nxt, past_key_values=fused, use_cache=True).logits
+    torch.testing.assert_close(got, expected, rtol=2e-3, atol=2e-3)
