@@ -39,16 +39,16 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 struct PairSmem {
   uint8_t stage[2][kStageBytes];
-  uint4 kpar4[128];       // per channel: (s,s) (z,z) -magic0*s -magic1*s
-  uint32_t kpar1[128];    // per channel: -magic2*s
+  uint4 kpar_a[128];      // by contraction position: (s,s) (z,z) -magic0*s -magic1*s of that position's channel
+  uint2 kpar_b[128];      // by contraction position: -magic2*s, byte offset of the channel's row (32 * channel)
   uint16_t prob[2][2 * 4 * kPStride];  // per warp of the pair: [hi/lo][head][local token]
-  uint8_t order[128];     // contraction order of the channels: promoted slots first
-  uint8_t is_promoted[128];
+  uint8_t order[2][128];  // per warp: contraction order of the channels, promoted slots first
+  uint8_t is_promoted[2][128];
   uint64_t bar[2];
 };
 
 struct BlockSmem {
-  uint32_t q32[2][4][128];   // query pre-shifted into the low (j'=0) or high (j'=1) half
+  uint32_t q32[128][8];      // [channel][2*head + j']: query pre-shifted into the low (j'=0) or high (j'=1) half
   float merge_m[kWarps][4];
   float merge_l[kWarps][4];
   int slot_map[128];
@@ -204,58 +204,98 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, Block
 }
 
 // ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
 // One warp's share of a staged page: QK over its 64 tokens, online softmax, PV over the same tokens.
-template <int DT, int HF>
+// GN = value groups per token (1 or 2).
+template <int DT, int HF, int GN>
 __device__ __forceinline__ void page_half(const dartkv_cache_desc& d, PairSmem& ps, const uint8_t* blob, uint16_t* prob,
-                                          const uint32_t* qsel, const CodeConsts<DT>& cc, int K, int prom_steps,
+                                          const uint8_t* q_thread, const CodeConsts<DT>& cc, int K, int prom_steps,
                                           float scale2, int g, int c, int jp, int hq, int gv, float (&o_acc)[4][4],
                                           float& m_run, float& l_run) {
   using H = Half2Ops<DT>;
-  const uint32_t* low = reinterpret_cast<const uint32_t*>(blob);
+  const uint8_t* low_thread = blob + 4 * g;   // + 32 * channel = this thread's word of the channel row
   const uint32_t* high = reinterpret_cast<const uint32_t*>(blob + d.key_off_high);
 
   // ---- logits: S[token pair][(head, j')] over the doubled contraction (channel, j); this warp's
-  // token pairs are codes 4*HF .. 4*HF+3 of every half-word: m-tile mt covers local pairs 2mt, 2mt+1
-  float s_acc[2][4];
+  // token pairs are codes 4*HF .. 4*HF+3 of every half-word: m-tile mt covers local pairs 2mt, 2mt+1.
+  // Even and odd contraction steps use separate accumulators so consecutive MMAs are independent.
+  float s_acc[2][2][4];
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int e = 0; e < 2; ++e)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) s_acc[mt][i] = 0.0f;
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s_acc[e][mt][i] = 0.0f;
   for (int ks = 0; ks < prom_steps; ++ks) {
     const int s0 = 8 * ks + c, s1 = s0 + 4;
-    const int ch0 = ps.order[s0], ch1 = ps.order[s1];
-    const uint4 p0 = ps.kpar4[ch0], p1 = ps.kpar4[ch1];
-    const uint32_t w0 = low[ch0 * 8 + g], w1 = low[ch1 * 8 + g];
+    const uint4 a0 = ps.kpar_a[s0], a1 = ps.kpar_a[s1];
+    const uint2 o0 = ps.kpar_b[s0], o1 = ps.kpar_b[s1];
+    const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
+    const uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + o1.y);
     const uint32_t h0 = s0 < K ? high[s0 * 8 + g] : 0u;
     const uint32_t h1 = s1 < K ? high[s1 * 8 + g] : 0u;
     uint32_t r0[4], r1[4];
-    dequant_half4<DT, HF>(cc, w0, h0, p0.x, p0.y, p0.z, p0.w, r0);
-    dequant_half4<DT, HF>(cc, w1, h1, p1.x, p1.y, p1.z, p1.w, r1);
-    const uint32_t b0 = qsel[ch0], b1 = qsel[ch1];
+    dequant_half4<DT, HF>(cc, w0, h0, a0.x, a0.y, a0.z, a0.w, r0);
+    dequant_half4<DT, HF>(cc, w1, h1, a1.x, a1.y, a1.z, a1.w, r1);
+    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
+    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
+    if (ks & 1) {
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+      for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[1][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+    } else {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[0][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+    }
   }
-#pragma unroll 4
-  for (int ks = prom_steps; ks < 16; ++ks) {
-    const int ch0 = ps.order[8 * ks + c], ch1 = ps.order[8 * ks + c + 4];
-    const uint4 p0 = ps.kpar4[ch0], p1 = ps.kpar4[ch1];
-    const uint32_t w0 = low[ch0 * 8 + g], w1 = low[ch1 * 8 + g];
+  // one plain step, if needed, to put the unrolled loop on an even step index
+  const int first_plain = prom_steps + (prom_steps & 1);
+#pragma unroll 1
+  for (int ks = prom_steps; ks < first_plain && ks < 16; ++ks) {
+    const uint4 a0 = ps.kpar_a[8 * ks + c], a1 = ps.kpar_a[8 * ks + c + 4];
+    const uint2 o0 = ps.kpar_b[8 * ks + c], o1 = ps.kpar_b[8 * ks + c + 4];
+    const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
+    const uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + o1.y);
     uint32_t r0[4], r1[4];
-    dequant_half2<DT, HF>(cc, w0, p0.x, p0.y, p0.z, p0.w, ps.kpar1[ch0], r0);
-    dequant_half2<DT, HF>(cc, w1, p1.x, p1.y, p1.z, p1.w, ps.kpar1[ch1], r1);
-    const uint32_t b0 = qsel[ch0], b1 = qsel[ch1];
+    dequant_half2<DT, HF>(cc, w0, a0.x, a0.y, a0.z, a0.w, o0.x, r0);
+    dequant_half2<DT, HF>(cc, w1, a1.x, a1.y, a1.z, a1.w, o1.x, r1);
+    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
+    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+    for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[1][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+  }
+#pragma unroll 2
+  for (int kp = first_plain; kp < 16; kp += 2) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int ks = kp + e;
+      const uint4 a0 = ps.kpar_a[8 * ks + c], a1 = ps.kpar_a[8 * ks + c + 4];
+      const uint2 o0 = ps.kpar_b[8 * ks + c], o1 = ps.kpar_b[8 * ks + c + 4];
+      const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
+      const uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + o1.y);
+      uint32_t r0[4], r1[4];
+      dequant_half2<DT, HF>(cc, w0, a0.x, a0.y, a0.z, a0.w, o0.x, r0);
+      dequant_half2<DT, HF>(cc, w1, a1.x, a1.y, a1.z, a1.w, o1.x, r1);
+      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
+      const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[e][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+    }
   }
 
   // ---- online softmax for head c over this warp's 64 tokens (this thread: 8 of them)
   float mx = -INFINITY;
+  float s_sum[2][4];
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      s_acc[mt][i] *= scale2;
-      mx = fmaxf(mx, s_acc[mt][i]);
+      s_sum[mt][i] = (s_acc[0][mt][i] + s_acc[1][mt][i]) * scale2;
+      mx = fmaxf(mx, s_sum[mt][i]);
     }
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
@@ -269,7 +309,7 @@ __device__ __forceinline__ void page_half(const dartkv_cache_desc& d, PairSmem& 
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float p = fast_exp2(s_acc[mt][i] - m_new);
+      const float p = fast_exp2(s_sum[mt][i] - m_new);
       psum += p;
       const int li = 2 * mt + (i >> 1) + 4 * (i & 1);   // local token index inside this thread's 8: pair + 4 j'
       const uint16_t hi = H::from_float(p);
@@ -294,31 +334,41 @@ __device__ __forceinline__ void page_half(const dartkv_cache_desc& d, PairSmem& 
 
   // ---- O[channel pair][(head, j')] += V^T P over the doubled contraction (token, j), this warp's tokens:
   // step ks covers the eight tokens 16*ks + 4*HF + {0..3} and + 8
-  const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(blob + kOffVCodes);
-  const uint16_t* vmeta = reinterpret_cast<const uint16_t*>(blob + kOffVMeta);
+  const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(blob + kOffVCodes) + g;
+  const uint8_t* vmeta = blob + kOffVMeta;
   const uint16_t* prob_hi = &prob[(0 * 4 + hq) * kPStride];
   const uint16_t* prob_lo = &prob[(1 * 4 + hq) * kPStride];
-  const int vg = d.value_groups, vg2 = 2 * d.value_groups;
-  const int shift = 16 * jp;
+  const uint32_t shift = 16 * jp;
+  // byte selectors that duplicate the scale / zero of this thread's value group into both halves
+  const uint32_t sel_s = GN == 2 ? (gv ? 0x3232u : 0x1010u) : 0x1010u;
+  const uint32_t sel_z = GN == 2 ? (gv ? 0x3232u : 0x1010u) : 0x3232u;
 #pragma unroll 2
   for (int ks = 0; ks < 8; ++ks) {
     const int t0 = 16 * ks + 4 * HF + c, t1 = t0 + 8;
-    const uint32_t w0 = vcodes[t0 * 8 + g], w1 = vcodes[t1 * 8 + g];
-    const uint32_t ss0 = (uint32_t)vmeta[t0 * vg2 + gv] * 0x00010001u;
-    const uint32_t zz0 = (uint32_t)vmeta[t0 * vg2 + vg + gv] * 0x00010001u;
-    const uint32_t ss1 = (uint32_t)vmeta[t1 * vg2 + gv] * 0x00010001u;
-    const uint32_t zz1 = (uint32_t)vmeta[t1 * vg2 + vg + gv] * 0x00010001u;
+    const uint32_t w0 = vcodes[t0 * 8], w1 = vcodes[t1 * 8];
+    uint32_t ss0, zz0, ss1, zz1;
+    if (GN == 2) {
+      const uint2 m0 = *reinterpret_cast<const uint2*>(vmeta + t0 * 8);   // {s0,s1} {z0,z1}
+      const uint2 m1 = *reinterpret_cast<const uint2*>(vmeta + t1 * 8);
+      ss0 = prmt(m0.x, m0.x, sel_s); zz0 = prmt(m0.y, m0.y, sel_z);
+      ss1 = prmt(m1.x, m1.x, sel_s); zz1 = prmt(m1.y, m1.y, sel_z);
+    } else {
+      const uint32_t m0 = *reinterpret_cast<const uint32_t*>(vmeta + t0 * 4);   // {s0, z0}
+      const uint32_t m1 = *reinterpret_cast<const uint32_t*>(vmeta + t1 * 4);
+      ss0 = prmt(m0, m0, sel_s); zz0 = prmt(m0, m0, sel_z);
+      ss1 = prmt(m1, m1, sel_s); zz1 = prmt(m1, m1, sel_z);
+    }
     uint32_t r0[8], r1[8];
     dequant_word2<DT>(cc, w0, ss0, zz0, H::mul(ss0, H::neg_magic(0)), H::mul(ss0, H::neg_magic(1)), H::mul(ss0, H::neg_magic(2)), r0);
     dequant_word2<DT>(cc, w1, ss1, zz1, H::mul(ss1, H::neg_magic(0)), H::mul(ss1, H::neg_magic(1)), H::mul(ss1, H::neg_magic(2)), r1);
     const int l0 = 8 * ks + c, l1 = l0 + 4;
     const uint32_t ph0 = (uint32_t)prob_hi[l0] << shift, ph1 = (uint32_t)prob_hi[l1] << shift;
     const uint32_t pl0 = (uint32_t)prob_lo[l0] << shift, pl1 = (uint32_t)prob_lo[l1] << shift;
+    // all hi-part MMAs first, then the lo parts: back-to-back MMAs never share an accumulator
 #pragma unroll
-    for (int mt = 0; mt < 4; ++mt) {
-      H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], ph0, ph1);
-      H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], pl0, pl1);
-    }
+    for (int mt = 0; mt < 4; ++mt) H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], ph0, ph1);
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], pl0, pl1);
   }
 }
 
@@ -353,8 +403,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       const int r = i >> 7, ch = i & 127;
       uint32_t v = 0;
       if (r < rep) v = reinterpret_cast<const uint16_t*>(a.q)[((int64_t)b * a.query_heads + hkv * rep + r) * 128 + ch];
-      bs.q32[0][r][ch] = v;
-      bs.q32[1][r][ch] = v << 16;
+      bs.q32[ch][2 * r] = v;
+      bs.q32[ch][2 * r + 1] = v << 16;
     }
     const bool issuer = hf == 0 && lane == 0;
     if (issuer) {
@@ -385,7 +435,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     const int K = d.key_mode == DARTKV_MIXED_PAGE ? d.promoted : 0;
     const int prom_steps = (K + 7) >> 3;
     const int jp = g & 1, hq = g >> 1;
-    const uint32_t* qsel = &bs.q32[jp][hq][0];
+    const uint8_t* q_thread = reinterpret_cast<const uint8_t*>(&bs.q32[0][g]);   // + 32 * channel
     const float scale2 = a.scale * kLog2e;
     const int gv = (16 * g) / d.value_group;
     bool ok = true;
@@ -406,21 +456,23 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       const uint16_t* kscale = reinterpret_cast<const uint16_t*>(blob + d.key_off_scale);
       const uint16_t* kzero = reinterpret_cast<const uint16_t*>(blob + d.key_off_zero);
 
-      // ---- shared per-page setup: warp 0 of the pair orders the channels (promoted slots first),
-      // both warps compute the per-channel constants of their half of the channels
-      if (hf == 0) {
-        reinterpret_cast<uint32_t*>(ps.is_promoted)[lane] = 0;
+      // ---- per-page setup: each warp orders the channels (promoted slots first) into its own copy, then
+      // fills the per-position constants of its half of the contraction positions
+      {
+        uint8_t* order = ps.order[hf];
+        uint8_t* flag = ps.is_promoted[hf];
+        reinterpret_cast<uint32_t*>(flag)[lane] = 0;
         __syncwarp();
         if (K > 0) {
           const int32_t* idx = reinterpret_cast<const int32_t*>(blob + d.key_off_index);
           for (int k = lane; k < K; k += 32) {
             const int ch = idx[k] & 127;
-            ps.is_promoted[ch] = 1;
-            ps.order[k] = (uint8_t)ch;
+            flag[ch] = 1;
+            order[k] = (uint8_t)ch;
           }
         }
         __syncwarp();
-        const uint32_t flags = reinterpret_cast<const uint32_t*>(ps.is_promoted)[lane];   // channels 4*lane .. +3
+        const uint32_t flags = reinterpret_cast<const uint32_t*>(flag)[lane];   // channels 4*lane .. +3
         const int mine = 4 - __popc(flags & 0x01010101u);
         int before = mine;
 #pragma unroll
@@ -431,22 +483,31 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
         int pos = K + before - mine;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          if (!((flags >> (8 * i)) & 1u)) ps.order[pos++] = (uint8_t)(4 * lane + i);
-      }
+          if (!((flags >> (8 * i)) & 1u)) order[pos++] = (uint8_t)(4 * lane + i);
+        __syncwarp();
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int ch = 64 * hf + lane + 32 * i;
-        const uint32_t ss = (uint32_t)kscale[ch] * 0x00010001u;
-        const uint32_t zz = (uint32_t)kzero[ch] * 0x00010001u;
-        ps.kpar4[ch] = make_uint4(ss, zz, H::mul(ss, H::neg_magic(0)), H::mul(ss, H::neg_magic(1)));
-        ps.kpar1[ch] = H::mul(ss, H::neg_magic(2));
+        for (int i = 0; i < 2; ++i) {
+          const int p = 64 * hf + lane + 32 * i;
+          const int ch = order[p];
+          const uint32_t ss = (uint32_t)kscale[ch] * 0x00010001u;
+          const uint32_t zz = (uint32_t)kzero[ch] * 0x00010001u;
+          ps.kpar_a[p] = make_uint4(ss, zz, H::mul(ss, H::neg_magic(0)), H::mul(ss, H::neg_magic(1)));
+          ps.kpar_b[p] = make_uint2(H::mul(ss, H::neg_magic(2)), 32u * ch);
+        }
       }
       pair_barrier(pair);
 
-      if (hf == 0)
-        page_half<DT, 0>(d, ps, blob, ps.prob[0], qsel, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
-      else
-        page_half<DT, 1>(d, ps, blob, ps.prob[1], qsel, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
+      if (d.value_groups == 2) {
+        if (hf == 0)
+          page_half<DT, 0, 2>(d, ps, blob, ps.prob[0], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
+        else
+          page_half<DT, 1, 2>(d, ps, blob, ps.prob[1], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
+      } else {
+        if (hf == 0)
+          page_half<DT, 0, 1>(d, ps, blob, ps.prob[0], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
+        else
+          page_half<DT, 1, 1>(d, ps, blob, ps.prob[1], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
+      }
 
       pair_barrier(pair);
       // the stage is free again: prefetch the page two iterations ahead
