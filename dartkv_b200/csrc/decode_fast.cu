@@ -317,10 +317,13 @@ __device__ __forceinline__ void page_half(const dartkv_cache_desc& d, PairSmem& 
       plo[li] = H::from_float(p - H::to_float(hi));
     }
   l_run = l_run * alpha + psum;
+  // the running maximum rarely moves after the first pages: skip the rescale when no lane needs it
+  if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
-  for (int mt = 0; mt < 4; ++mt)
+    for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o_acc[mt][i] *= alpha;
+      for (int i = 0; i < 4; ++i) o_acc[mt][i] *= alpha;
+  }
   {
     uint4 hv, lv;
     hv.x = (uint32_t)phi[0] | ((uint32_t)phi[1] << 16); hv.y = (uint32_t)phi[2] | ((uint32_t)phi[3] << 16);
