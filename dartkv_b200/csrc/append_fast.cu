@@ -55,11 +55,95 @@ __device__ __forceinline__ float scale_of(float mn, float mx, float qmax) {
   return rnd<DT>(__fdiv_rn(range, qmax));
 }
 
+// ---- packed code computation -------------------------------------------------------------------
+// Two elements that share (min, scale) travel as one 16-bit pair.  The reference computes
+//   code = clamp(rint(r16(r16(x - min) / scale)), 0, qmax)        (r16 = round to the data dtype)
+// which is evaluated here as
+//   a2   = x2 - min2                      packed subtract, one rounding (exact for the 16-bit formats)
+//   q    = a * (1/scale)  (bf16)          the quotient of two 8-bit significands is never within 2^-17
+//          a / scale      (fp16)          of a bf16 rounding boundary and never on one, so a reciprocal
+//                                         multiply rounds to the same bf16 as the IEEE quotient; fp16
+//                                         significands are too long for that and take the true division
+//   r2   = r16(q) packed
+//   m2   = r2 + magic                     magic = 128 (bf16) / 1024 (fp16): the sum has unit ulp, so the
+//                                         packed add rounds half-to-even to an integer = rint
+// leaving the codes in the low mantissa bits of each half.  bf16 cannot hold 128 + code for 8-bit
+// codes; that combination uses scalar rint.
+template <int DT> struct Pack16;
+template <> struct Pack16<DARTKV_BF16> {
+  static constexpr uint32_t kMagic = 0x43004300u;   // 128.0 | 128.0
+  static __device__ __forceinline__ uint32_t sub(uint32_t a, uint32_t b) {
+    uint32_t d; asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+  }
+  static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
+    uint32_t d; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+  }
+  static __device__ __forceinline__ uint32_t min2(uint32_t a, uint32_t b) {
+    uint32_t d; asm("min.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+  }
+  static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+    uint32_t d; asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+  }
+  static __device__ __forceinline__ float lo(uint32_t v) { return __uint_as_float(v << 16); }
+  static __device__ __forceinline__ float hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+  static __device__ __forceinline__ uint32_t pack(float hi_v, float lo_v) {
+    uint32_t d; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi_v), "f"(lo_v)); return d;
+  }
+  static __device__ __forceinline__ float quotient(float a, float s, float inv) { (void)s; return __fmul_rn(a, inv); }
+  static __device__ __forceinline__ uint16_t bits(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
+  // |x| as a double, from the 15 magnitude bits (subnormal inputs count as zero)
+  static __device__ __forceinline__ double abs_double(uint32_t b) {
+    const uint32_t mag = b & 0x7FFFu;
+    return __hiloint2double(mag >= 0x80u ? (int)(mag * 8192u + 0x38000000u) : 0, 0);
+  }
+};
+template <> struct Pack16<DARTKV_F16> {
+  static constexpr uint32_t kMagic = 0x64006400u;   // 1024.0 | 1024.0
+  static __device__ __forceinline__ uint32_t sub(uint32_t a, uint32_t b) {
+    uint32_t d; asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+  }
+  static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b) {
+    uint32_t d; asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+  }
+  static __device__ __forceinline__ uint32_t min2(uint32_t a, uint32_t b) {
+    uint32_t d; asm("min.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+  }
+  static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+    uint32_t d; asm("max.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+  }
+  static __device__ __forceinline__ float lo(uint32_t v) { return __half2float(__ushort_as_half((uint16_t)(v & 0xFFFFu))); }
+  static __device__ __forceinline__ float hi(uint32_t v) { return __half2float(__ushort_as_half((uint16_t)(v >> 16))); }
+  static __device__ __forceinline__ uint32_t pack(float hi_v, float lo_v) {
+    uint32_t d; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi_v), "f"(lo_v)); return d;
+  }
+  static __device__ __forceinline__ float quotient(float a, float s, float inv) { (void)inv; return __fdiv_rn(a, s); }
+  static __device__ __forceinline__ uint16_t bits(float v) { return __half_as_ushort(__float2half_rn(v)); }
+  static __device__ __forceinline__ double abs_double(uint32_t b) {
+    const uint32_t mag = b & 0x7FFFu;
+    if (mag < 0x400u) return (double)__half2float(__ushort_as_half((uint16_t)mag));   // zero / subnormal
+    return __hiloint2double((int)(mag * 1024u + 0x3F000000u), 0);
+  }
+};
+
+// codes of a pair in bits [7:0] (low element) and [23:16] (high element)
+template <int DT, int BITS>
+__device__ __forceinline__ uint32_t pair_codes(uint32_t x2, uint32_t mn2, float s, float inv, uint32_t cap2) {
+  using P = Pack16<DT>;
+  const uint32_t a2 = P::sub(x2, mn2);
+  const float q_lo = P::quotient(P::lo(a2), s, inv), q_hi = P::quotient(P::hi(a2), s, inv);
+  if (DT == DARTKV_BF16 && BITS == 8) {
+    const uint32_t r2 = P::pack(q_hi, q_lo);
+    const uint32_t c_lo = (uint32_t)fminf(rintf(P::lo(r2)), 255.0f), c_hi = (uint32_t)fminf(rintf(P::hi(r2)), 255.0f);
+    return c_lo | (c_hi << 16);
+  }
+  const uint32_t m2 = P::min2(P::add(P::pack(q_hi, q_lo), P::kMagic), cap2);   // magic + code, capped at magic + qmax
+  return m2 & (DT == DARTKV_BF16 ? 0x007F007Fu : 0x03FF03FFu);
+}
+
 template <int DT>
-__device__ __forceinline__ uint32_t code_of(float x, float mn, float scale, float qmax) {
-  float shifted = rnd<DT>(__fsub_rn(x, mn));
-  float ratio = rnd<DT>(__fdiv_rn(shifted, scale));
-  return (uint32_t)fminf(fmaxf(rintf(ratio), 0.0f), qmax);
+__device__ __forceinline__ uint32_t cap_pair(float qmax) {
+  const uint32_t one = Pack16<DT>::bits((DT == DARTKV_BF16 ? 128.0f : 1024.0f) + qmax);
+  return one * 0x00010001u;
 }
 
 // KBITS: 0 = mixed 2+2-bit keys, else uniform keys with KBITS bits
@@ -67,9 +151,8 @@ template <int DT, int KBITS>
 __global__ void __launch_bounds__(128) fast_key_pages_kernel(dartkv_cache_desc d, RowSource src, int first_slot,
                                                              int num_pages, int page_token_start,
                                                              const int32_t* __restrict__ indices, int32_t* nonfinite) {
-  using E = Elem<DT>;
-  using T = typename E::type;
-  __shared__ __align__(16) T s_page[kP * kD];
+  using P = Pack16<DT>;
+  __shared__ __align__(16) uint16_t s_page[kP * kD];
   __shared__ float s_score[kD];
   const int bh = blockIdx.x, pg = blockIdx.y, c = threadIdx.x;
   const int t0 = page_token_start + pg * kP;
@@ -83,41 +166,44 @@ __global__ void __launch_bounds__(128) fast_key_pages_kernel(dartkv_cache_desc d
   __syncthreads();
 
   uint8_t* page = d.k_pages + ((int64_t)bh * d.max_key_pages + first_slot + pg) * d.key_page_bytes;
-  float mn = INFINITY, mx = -INFINITY;
+  const uint16_t* col = s_page + c;
+  // pass 1: min / max on packed pairs, sum |k| in double (order independent for 16-bit data)
+  uint32_t mn2 = (uint32_t)col[0] * 0x00010001u, mx2 = mn2;
+  uint32_t exp_or = 0;
   double asum = 0.0;
-  bool bad = false;
-#pragma unroll 8
-  for (int t = 0; t < kP; ++t) {
-    float v = E::to_float(s_page[t * kD + c]);
-    bad |= !isfinite(v);
-    mn = fminf(mn, v);
-    mx = fmaxf(mx, v);
-    if (KBITS == 0) asum += (double)fabsf(v);
+#pragma unroll 4
+  for (int t = 0; t < kP; t += 2) {
+    const uint32_t lo = col[t * kD], hi = col[(t + 1) * kD];
+    const uint32_t x2 = lo | (hi << 16);
+    mn2 = P::min2(mn2, x2);
+    mx2 = P::max2(mx2, x2);
+    exp_or |= (DT == DARTKV_BF16) ? (((lo & 0x7F80u) == 0x7F80u) | ((hi & 0x7F80u) == 0x7F80u))
+                                   : (((lo & 0x7C00u) == 0x7C00u) | ((hi & 0x7C00u) == 0x7C00u));
+    if (KBITS == 0) asum += P::abs_double(lo) + P::abs_double(hi);
   }
+  const bool bad = exp_or != 0;   // an all-ones exponent is Inf or NaN
+  const float mn = fminf(P::lo(mn2), P::hi(mn2)), mx = fmaxf(P::lo(mx2), P::hi(mx2));
   int slot = -1;
   float qmax;
   if (KBITS == 0) {
     const int K = d.promoted;
     int32_t* idx_field = reinterpret_cast<int32_t*>(page + d.key_off_index);
     if (indices != nullptr) {
-      // forced channels: find this channel in the list
       const int32_t* mine = indices + ((int64_t)bh * num_pages + pg) * K;
-      for (int k = 0; k < K; ++k) {
-        int ch = mine[k];
-        if (ch == c) slot = k;
-      }
+      for (int k = 0; k < K; ++k)
+        if (mine[k] == c) slot = k;
       if (c < K) idx_field[c] = mine[c];
     } else if (K == kD) {
       slot = c;
       idx_field[c] = c;
     } else if (K > 0) {
-      float score = rnd<DT>(__fdiv_rn((float)asum, (float)kP));
+      const float score = rnd<DT>(__fdiv_rn((float)asum, (float)kP));
       s_score[c] = score;
       __syncthreads();
       int rank = 0;
 #pragma unroll 8
       for (int o = 0; o < kD; ++o) {
-        float other = s_score[o];
+        const float other = s_score[o];
         rank += (other > score) || (other == score && o < c);
       }
       if (rank < K) { slot = rank; idx_field[rank] = c; }
@@ -129,94 +215,98 @@ __global__ void __launch_bounds__(128) fast_key_pages_kernel(dartkv_cache_desc d
   const float scale = scale_of<DT>(mn, mx, qmax);
   store_f(page + d.key_off_scale, d.md_dtype, c, scale);
   store_f(page + d.key_off_zero, d.md_dtype, c, mn);
+  const float inv = __frcp_rn(scale);
+  const uint32_t mnp = (uint32_t)P::bits(mn) * 0x00010001u;
+  const uint32_t cap2 = cap_pair<DT>(qmax);
 
-  if (KBITS == 0) {
-    uint32_t lo[8], hi[8];
+  // pass 2: a pair is (token i, token i + step) of a 32-bit output word, so both codes fall 16 bits apart
+  constexpr int BITS = KBITS == 0 ? 2 : KBITS;      // bits per stored plane
+  constexpr int CODE_BITS = KBITS == 0 ? 4 : KBITS; // bits the quantizer produces
+  constexpr int PER_WORD = 32 / BITS;               // tokens per 32-bit word of a plane
+  constexpr int STEP = PER_WORD / 2;
+  constexpr int WORDS = kP / PER_WORD;
+  constexpr uint32_t FIELD = ((1u << BITS) - 1u) * 0x00010001u;
+  uint32_t* low_row = reinterpret_cast<uint32_t*>(page + c * (WORDS * 4));
+  uint32_t* high_row = (KBITS == 0 && slot >= 0) ? reinterpret_cast<uint32_t*>(page + d.key_off_high + slot * (WORDS * 4)) : nullptr;
+#pragma unroll 1
+  for (int w4 = 0; w4 < WORDS; w4 += 4) {
+    uint32_t lo_words[4], hi_words[4];
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      uint32_t l = 0, h = 0;
+    for (int q = 0; q < 4; ++q) {
+      uint32_t lacc = 0, hacc = 0;
+      const int base = (w4 + q) * PER_WORD;
 #pragma unroll
-      for (int k = 0; k < 16; ++k) {
-        uint32_t code = code_of<DT>(E::to_float(s_page[(w * 16 + k) * kD + c]), mn, scale, qmax);
-        l |= (code & 3u) << (2 * k);
-        h |= (code >> 2) << (2 * k);
+      for (int u = 0; u < STEP; ++u) {
+        const uint32_t x2 = (uint32_t)col[(base + u) * kD] | ((uint32_t)col[(base + u + STEP) * kD] << 16);
+        const uint32_t codes = pair_codes<DT, CODE_BITS>(x2, mnp, scale, inv, cap2);
+        lacc |= (codes & FIELD) << (BITS * u);
+        if (KBITS == 0) hacc |= ((codes >> 2) & FIELD) << (BITS * u);
       }
-      lo[w] = l;
-      hi[w] = h;
+      lo_words[q] = lacc;
+      hi_words[q] = hacc;
     }
-    uint4* lrow = reinterpret_cast<uint4*>(page + c * 32);
-    lrow[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    lrow[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-    if (slot >= 0) {
-      uint4* hrow = reinterpret_cast<uint4*>(page + d.key_off_high + slot * 32);
-      hrow[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      hrow[1] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-    }
-  } else {
-    constexpr int VPW = 32 / (KBITS ? KBITS : 2);     // codes per 32-bit word
-    constexpr int WORDS = kP / VPW;                    // 8, 16 or 32 words per channel row
-    uint32_t* row = reinterpret_cast<uint32_t*>(page + c * (WORDS * 4));
-#pragma unroll 4
-    for (int w = 0; w < WORDS; w += 4) {
-      uint32_t out[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t acc = 0;
-#pragma unroll
-        for (int k = 0; k < VPW; ++k) {
-          uint32_t code = code_of<DT>(E::to_float(s_page[((w + q) * VPW + k) * kD + c]), mn, scale, qmax);
-          acc |= code << ((KBITS ? KBITS : 2) * k);
-        }
-        out[q] = acc;
-      }
-      reinterpret_cast<uint4*>(row)[w / 4] = make_uint4(out[0], out[1], out[2], out[3]);
-    }
+    reinterpret_cast<uint4*>(low_row)[w4 / 4] = make_uint4(lo_words[0], lo_words[1], lo_words[2], lo_words[3]);
+    if (KBITS == 0 && high_row) reinterpret_cast<uint4*>(high_row)[w4 / 4] = make_uint4(hi_words[0], hi_words[1], hi_words[2], hi_words[3]);
   }
   if (bad && nonfinite) *nonfinite = 1;
 }
 
-// one warp per token row; VBITS in {2,4,8}; LPG = lanes per group (value_group / 4)
+// one warp per four token rows (loads issued together); VBITS in {2,4,8}; LPG = lanes per group
 template <int DT, int VBITS>
 __global__ void __launch_bounds__(256) fast_value_rows_kernel(dartkv_cache_desc d, RowSource src, int value_begin,
                                                               int count, int lanes_per_group, int32_t* nonfinite) {
-  using E = Elem<DT>;
-  using T = typename E::type;
+  using P = Pack16<DT>;
+  constexpr int ROWS = 4;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int64_t total = (int64_t)d.batch * d.kv_heads * count;
-  if (warp >= total) return;
-  const int bh = warp / count, j = warp % count, t = value_begin + j;
-  const uint16_t* row_ptr = src.row(bh, t);
-  uint2 raw = *reinterpret_cast<const uint2*>(row_ptr + lane * 4);
-  T e[4];
-  *reinterpret_cast<uint2*>(e) = raw;
-  float v[4];
-  bool bad = false;
-  float mn = INFINITY, mx = -INFINITY;
+  const int64_t first = (int64_t)warp * ROWS;
+  if (first >= total) return;
+  uint2 raw[ROWS];
+  int bh_of[ROWS], t_of[ROWS];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    v[k] = E::to_float(e[k]);
-    bad |= !isfinite(v[k]);
-    mn = fminf(mn, v[k]);
-    mx = fmaxf(mx, v[k]);
-  }
-  for (int off = 1; off < lanes_per_group; off <<= 1) {
-    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  for (int r = 0; r < ROWS; ++r) {
+    const int64_t row = min(first + r, total - 1);
+    bh_of[r] = (int)(row / count);
+    t_of[r] = value_begin + (int)(row % count);
+    raw[r] = *reinterpret_cast<const uint2*>(src.row(bh_of[r], t_of[r]) + lane * 4);
   }
   constexpr float qmax = (float)((1 << VBITS) - 1);
-  const float scale = scale_of<DT>(mn, mx, qmax);
-  uint32_t packed = 0;
+  const uint32_t cap2 = cap_pair<DT>(qmax);
+  bool bad = false;
 #pragma unroll
-  for (int k = 0; k < 4; ++k) packed |= code_of<DT>(v[k], mn, scale, qmax) << (VBITS * k);
-  const int64_t out_row = (int64_t)bh * d.max_value_tokens + (t - d.sink_tokens);
-  uint8_t* codes = d.v_codes + out_row * d.value_row_bytes;
-  if (VBITS == 2) codes[lane] = (uint8_t)packed;
-  else if (VBITS == 4) reinterpret_cast<uint16_t*>(codes)[lane] = (uint16_t)packed;
-  else reinterpret_cast<uint32_t*>(codes)[lane] = packed;
-  if ((lane % lanes_per_group) == 0) {
-    int g = lane / lanes_per_group;
-    store_f(d.v_meta, d.md_dtype, (out_row * 2 + 0) * d.value_groups + g, scale);
-    store_f(d.v_meta, d.md_dtype, (out_row * 2 + 1) * d.value_groups + g, mn);
+  for (int r = 0; r < ROWS; ++r) {
+    if (first + r >= total) break;
+    const uint32_t x01 = raw[r].x, x23 = raw[r].y;
+    const uint32_t expmask = DT == DARTKV_BF16 ? 0x7F807F80u : 0x7C007C00u;
+    bad |= ((x01 & expmask & 0xFFFFu) == (expmask & 0xFFFFu)) | ((x01 & expmask & 0xFFFF0000u) == (expmask & 0xFFFF0000u)) |
+           ((x23 & expmask & 0xFFFFu) == (expmask & 0xFFFFu)) | ((x23 & expmask & 0xFFFF0000u) == (expmask & 0xFFFF0000u));
+    uint32_t mn2 = P::min2(x01, x23), mx2 = P::max2(x01, x23);
+    for (int off = 1; off < lanes_per_group; off <<= 1) {
+      mn2 = P::min2(mn2, __shfl_xor_sync(0xffffffffu, mn2, off));
+      mx2 = P::max2(mx2, __shfl_xor_sync(0xffffffffu, mx2, off));
+    }
+    const float mn = fminf(P::lo(mn2), P::hi(mn2)), mx = fmaxf(P::lo(mx2), P::hi(mx2));
+    const float scale = scale_of<DT>(mn, mx, qmax);
+    const float inv = __frcp_rn(scale);
+    const uint32_t mnp = (uint32_t)P::bits(mn) * 0x00010001u;
+    const uint32_t c01 = pair_codes<DT, VBITS>(x01, mnp, scale, inv, cap2);
+    const uint32_t c23 = pair_codes<DT, VBITS>(x23, mnp, scale, inv, cap2);
+    const int64_t out_row = (int64_t)bh_of[r] * d.max_value_tokens + (t_of[r] - d.sink_tokens);
+    uint8_t* codes = d.v_codes + out_row * d.value_row_bytes;
+    if (VBITS == 2) {
+      codes[lane] = (uint8_t)((c01 & 3u) | ((c01 >> 14) & 0xCu) | ((c23 & 3u) << 4) | ((c23 >> 10) & 0xC0u));
+    } else if (VBITS == 4) {
+      reinterpret_cast<uint16_t*>(codes)[lane] =
+          (uint16_t)((c01 & 0xFu) | ((c01 >> 12) & 0xF0u) | ((c23 & 0xFu) << 8) | ((c23 >> 4) & 0xF000u));
+    } else {
+      reinterpret_cast<uint32_t*>(codes)[lane] =
+          (c01 & 0xFFu) | ((c01 >> 8) & 0xFF00u) | ((c23 & 0xFFu) << 16) | ((c23 << 8) & 0xFF000000u);
+    }
+    if ((lane % lanes_per_group) == 0) {
+      const int g = lane / lanes_per_group;
+      store_f(d.v_meta, d.md_dtype, (out_row * 2 + 0) * d.value_groups + g, scale);
+      store_f(d.v_meta, d.md_dtype, (out_row * 2 + 1) * d.value_groups + g, mn);
+    }
   }
   if (bad && nonfinite) *nonfinite = 1;
 }
@@ -260,7 +350,7 @@ static int launch_values(const dartkv_cache_desc& d, const dartkv_append_plan& p
                          int32_t* nonfinite, cudaStream_t stream) {
   const int count = p.value_end - p.value_begin;
   const int64_t rows = (int64_t)d.batch * d.kv_heads * count;
-  const unsigned blocks = (unsigned)((rows + 7) / 8);
+  const unsigned blocks = (unsigned)((rows + 31) / 32);   // 8 warps per block, 4 rows per warp
   const int lpg = d.value_group / 4;
   if (d.value_bits == 2)
     fast_value_rows_kernel<DT, 2><<<blocks, 256, 0, stream>>>(d, src, p.value_begin, count, lpg, nonfinite);

@@ -59,8 +59,10 @@ struct TokenSource {
 // ---------------------------------------------------------------------------- dense copies
 // grid (bh, chunk token, side); copies sink tokens into the sink rows and tail tokens into the ring.
 __global__ void copy_dense_kernel(dartkv_cache_desc d, dartkv_append_plan p, const void* keys, const void* values,
-                                  int64_t sb, int64_t sh, int64_t st, int32_t* nonfinite) {
-  int bh = blockIdx.x, j = blockIdx.y, side = blockIdx.z;
+                                  int64_t sb, int64_t sh, int64_t st, int ring_first, int32_t* nonfinite) {
+  // blockIdx.y enumerates only the chunk tokens that can need a copy: the sink part, then [ring_first, chunk end)
+  int bh = blockIdx.x, side = blockIdx.z;
+  int j = (int)blockIdx.y < p.sink_copy ? (int)blockIdx.y : ring_first + ((int)blockIdx.y - p.sink_copy);
   int t = p.chunk_start + j;
   int ring_begin = side == 0 ? p.ring_begin : p.value_end;  // values not packed by this step stay dense
   const bool to_sink = j < p.sink_copy;
@@ -461,7 +463,9 @@ extern "C" int dartkv_cache_append(const dartkv_cache_desc* desc, const dartkv_a
   }
   if (copies) {
     DARTKV_REQUIRE(p.chunk_tokens <= 65535, "append chunks longer than 65535 tokens must be split by the caller");
-    copy_dense_kernel<<<dim3(bh, p.chunk_tokens, 2), 128, 0, stream>>>(d, p, keys, values, stride_b, stride_h, stride_t, nonfinite);
+    const int ring_first = max(p.sink_copy, min(p.ring_begin, max(p.value_end, p.chunk_start)) - p.chunk_start);
+    const int rows = p.sink_copy + (p.chunk_tokens - ring_first);
+    copy_dense_kernel<<<dim3(bh, rows, 2), 128, 0, stream>>>(d, p, keys, values, stride_b, stride_h, stride_t, ring_first, nonfinite);
     DARTKV_LAUNCH_OK("copy_dense_kernel");
   }
   finalize_append_kernel<<<1, 128, 0, stream>>>(d, p);
