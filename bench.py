@@ -387,15 +387,113 @@ def gpu_arm(args, wl) -> None:
         dist.destroy_process_group()
 
 
+def qwen3_decode(args) -> None:
+    """Qwen3-8B-architecture greedy decode through DartHFCache + the fused decode hook (random bf16 weights)."""
+
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    import dartkv_b200 as dart
+    from dartkv_b200 import _lib
+    from dartkv_b200.integrations import DartHFCache, attach_dart_fused_attention
+    from dartkv_b200.integrations import qwen3 as hook
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    batch, prompt_len, new_tokens = 8, 1024, max(2, args.steps if args.steps != 20 else 256)
+    config = Qwen3Config(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
+                         num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=40960,
+                         rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False, initializer_range=0.02)
+    config._attn_implementation = "sdpa"
+    torch.manual_seed(3)
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device(device):
+        model = Qwen3ForCausalLM(config)
+    torch.set_default_dtype(torch.float32)
+    model.eval()
+    attach_dart_fused_attention(model)
+    cfg = dart.DartKVCacheConfig(bits=2, promote_ratio=0.25, page_size=128, key_group_size=128, value_group_size=64,
+                                 sink_tokens=32, hold_partial_pages=True, local_tokens=1, value_local_tokens=128,
+                                 metadata_dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, config.vocab_size, (batch, prompt_len), generator=gen).to(device)
+
+    # time spent inside the hot path (cache update + fused attention) per decode step, by CUDA events
+    spans = []
+    original = hook.fused_dart_attention
+    original_update = DartHFCache.update
+
+    def timed_attention(*a, **k):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = original(*a, **k)
+        stop.record()
+        spans.append((start, stop))
+        return out
+
+    def timed_update(self, *a, **k):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = original_update(self, *a, **k)
+        stop.record()
+        spans.append((start, stop))
+        return out
+
+    def run(measure: bool):
+        cache = DartHFCache(cfg, max_tokens=prompt_len + new_tokens + 128)
+        with torch.no_grad():
+            logits = model(prompt, past_key_values=cache, use_cache=True).logits[:, -1]
+            token = logits.argmax(-1, keepdim=True)
+            torch.cuda.synchronize(device)
+            if measure:
+                hook.fused_dart_attention = timed_attention
+                DartHFCache.update = timed_update
+            launches = _lib.LIB.dartkv_launch_count()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(new_tokens):
+                logits = model(token, past_key_values=cache, use_cache=True).logits[:, -1]
+                token = logits.argmax(-1, keepdim=True)
+            t1.record()
+            torch.cuda.synchronize(device)
+            hook.fused_dart_attention = original
+            DartHFCache.update = original_update
+        return t0.elapsed_time(t1), _lib.LIB.dartkv_launch_count() - launches, cache
+
+    run(False)                       # warm-up: allocator, cuBLAS heuristics, kernel load
+    spans.clear()
+    with ClockSampler(0) as clocks:
+        ms, launches, cache = run(True)
+    hot_ms = sum(a.elapsed_time(b) for a, b in spans)
+    line = {
+        "metric": "qwen3_8b_arch_decode_tokens_per_s", "value": batch * new_tokens / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": new_tokens, "warmup": 1, "ms_per_step": ms / new_tokens, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "config4", "model": "Qwen3-8B architecture, random-init bf16 weights (std 0.02)",
+                   "batch": batch, "prompt": prompt_len, "new_tokens": new_tokens,
+                   "cache": "2-bit + 0.25 promotion, page 128, groups 128/64, 32 sinks, local 1, value local 128, bf16 metadata"},
+        "attention_share_of_step": hot_ms / ms, "hot_path_ms_per_step": hot_ms / new_tokens,
+        "compression_ratio": cache.compression_ratio, "gpu_launches": int(launches), "clocks": clocks.summary(),
+        "e2e": {"value": batch * new_tokens / (ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0, "note": "token ids stay on the device between steps"},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=sorted(WORKLOADS), default="config5")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["config4"], default="config5")
     parser.add_argument("--skip-extras", action="store_true", help="skip the append microbench and the CPU baseline")
     args = parser.parse_args()
+    if args.workload == "config4":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "config4 needs the GPU model run; the CPU arm covers config5/config3"}))
+            return
+        qwen3_decode(args)
+        return
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
         reference_arm(args, wl)

@@ -32,6 +32,16 @@ struct RowSource {
   const void* ring;
   int64_t sb, sh, st;
   int chunk_start, ring_tokens, kv_heads;
+  // base pointers for one (batch, head): chunk rows then ring rows
+  __device__ __forceinline__ void bases(int bh, const uint16_t*& chunk_base, const uint16_t*& ring_base) const {
+    int b = bh / kv_heads, h = bh % kv_heads;
+    chunk_base = reinterpret_cast<const uint16_t*>(chunk) + (int64_t)b * sb + (int64_t)h * sh;
+    ring_base = reinterpret_cast<const uint16_t*>(ring) + (int64_t)bh * ring_tokens * kD;
+  }
+  __device__ __forceinline__ const uint16_t* row_from(const uint16_t* chunk_base, const uint16_t* ring_base, int t) const {
+    if (t >= chunk_start) return chunk_base + (int64_t)(t - chunk_start) * st;
+    return ring_base + (t % ring_tokens) * kD;
+  }
   // 16-bit elements; rows are head_dim contiguous elements
   __device__ __forceinline__ const uint16_t* row(int bh, int t) const {
     if (t >= chunk_start) {
@@ -157,10 +167,12 @@ __global__ void __launch_bounds__(128) fast_key_pages_kernel(dartkv_cache_desc d
   const int bh = blockIdx.x, pg = blockIdx.y, c = threadIdx.x;
   const int t0 = page_token_start + pg * kP;
   // stage the page: 2048 16-byte pieces, 16 per thread
+  const uint16_t *chunk_base, *ring_base;
+  src.bases(bh, chunk_base, ring_base);
   for (int i = c; i < kP * 16; i += 128) {
     int r = i >> 4, piece = i & 15;
     cp_async16(reinterpret_cast<char*>(s_page) + r * 256 + piece * 16,
-               reinterpret_cast<const char*>(src.row(bh, t0 + r)) + piece * 16);
+               reinterpret_cast<const char*>(src.row_from(chunk_base, ring_base, t0 + r)) + piece * 16);
   }
   cp_async_wait_all();
   __syncthreads();
@@ -169,7 +181,8 @@ __global__ void __launch_bounds__(128) fast_key_pages_kernel(dartkv_cache_desc d
   const uint16_t* col = s_page + c;
   // pass 1: min / max on packed pairs, sum |k| in double (order independent for 16-bit data)
   uint32_t mn2 = (uint32_t)col[0] * 0x00010001u, mx2 = mn2;
-  uint32_t exp_or = 0;
+  uint32_t exp_or = 0;   // bit 15 / 31 end up set iff some magnitude has an all-ones exponent (Inf or NaN)
+  constexpr uint32_t kExpCarry = DT == DARTKV_BF16 ? 0x00800080u : 0x04000400u;
   double asum = 0.0;
 #pragma unroll 4
   for (int t = 0; t < kP; t += 2) {
@@ -177,11 +190,10 @@ __global__ void __launch_bounds__(128) fast_key_pages_kernel(dartkv_cache_desc d
     const uint32_t x2 = lo | (hi << 16);
     mn2 = P::min2(mn2, x2);
     mx2 = P::max2(mx2, x2);
-    exp_or |= (DT == DARTKV_BF16) ? (((lo & 0x7F80u) == 0x7F80u) | ((hi & 0x7F80u) == 0x7F80u))
-                                   : (((lo & 0x7C00u) == 0x7C00u) | ((hi & 0x7C00u) == 0x7C00u));
+    exp_or |= (x2 & 0x7FFF7FFFu) + kExpCarry;
     if (KBITS == 0) asum += P::abs_double(lo) + P::abs_double(hi);
   }
-  const bool bad = exp_or != 0;   // an all-ones exponent is Inf or NaN
+  const bool bad = (exp_or & 0x80008000u) != 0;
   const float mn = fminf(P::lo(mn2), P::hi(mn2)), mx = fmaxf(P::lo(mx2), P::hi(mx2));
   int slot = -1;
   float qmax;
@@ -258,17 +270,20 @@ __global__ void __launch_bounds__(256) fast_value_rows_kernel(dartkv_cache_desc 
   using P = Pack16<DT>;
   constexpr int ROWS = 4;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  const int64_t total = (int64_t)d.batch * d.kv_heads * count;
-  const int64_t first = (int64_t)warp * ROWS;
+  const uint32_t total = (uint32_t)d.batch * d.kv_heads * count;   // checked on the host to fit 32 bits
+  const uint32_t first = (uint32_t)warp * ROWS;
   if (first >= total) return;
   uint2 raw[ROWS];
   int bh_of[ROWS], t_of[ROWS];
+  {
+    int bh = (int)(first / (uint32_t)count), j = (int)(first % (uint32_t)count);
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) {
-    const int64_t row = min(first + r, total - 1);
-    bh_of[r] = (int)(row / count);
-    t_of[r] = value_begin + (int)(row % count);
-    raw[r] = *reinterpret_cast<const uint2*>(src.row(bh_of[r], t_of[r]) + lane * 4);
+    for (int r = 0; r < ROWS; ++r) {
+      bh_of[r] = bh;
+      t_of[r] = value_begin + j;
+      raw[r] = *reinterpret_cast<const uint2*>(src.row(bh, t_of[r]) + lane * 4);
+      if (first + r + 1 < total && ++j == count) { j = 0; ++bh; }
+    }
   }
   constexpr float qmax = (float)((1 << VBITS) - 1);
   const uint32_t cap2 = cap_pair<DT>(qmax);
@@ -277,9 +292,8 @@ __global__ void __launch_bounds__(256) fast_value_rows_kernel(dartkv_cache_desc 
   for (int r = 0; r < ROWS; ++r) {
     if (first + r >= total) break;
     const uint32_t x01 = raw[r].x, x23 = raw[r].y;
-    const uint32_t expmask = DT == DARTKV_BF16 ? 0x7F807F80u : 0x7C007C00u;
-    bad |= ((x01 & expmask & 0xFFFFu) == (expmask & 0xFFFFu)) | ((x01 & expmask & 0xFFFF0000u) == (expmask & 0xFFFF0000u)) |
-           ((x23 & expmask & 0xFFFFu) == (expmask & 0xFFFFu)) | ((x23 & expmask & 0xFFFF0000u) == (expmask & 0xFFFF0000u));
+    constexpr uint32_t kExpCarry = DT == DARTKV_BF16 ? 0x00800080u : 0x04000400u;
+    bad |= ((((x01 & 0x7FFF7FFFu) + kExpCarry) | ((x23 & 0x7FFF7FFFu) + kExpCarry)) & 0x80008000u) != 0;
     uint32_t mn2 = P::min2(x01, x23), mx2 = P::max2(x01, x23);
     for (int off = 1; off < lanes_per_group; off <<= 1) {
       mn2 = P::min2(mn2, __shfl_xor_sync(0xffffffffu, mn2, off));
@@ -350,6 +364,7 @@ static int launch_values(const dartkv_cache_desc& d, const dartkv_append_plan& p
                          int32_t* nonfinite, cudaStream_t stream) {
   const int count = p.value_end - p.value_begin;
   const int64_t rows = (int64_t)d.batch * d.kv_heads * count;
+  DARTKV_REQUIRE(rows < (1ll << 31), "too many value rows in one append (limit 2^31)");
   const unsigned blocks = (unsigned)((rows + 31) / 32);   // 8 warps per block, 4 rows per warp
   const int lpg = d.value_group / 4;
   if (d.value_bits == 2)
