@@ -320,6 +320,10 @@ def gpu_arm(args, wl) -> None:
     local_bytes = step_bytes(local_batch, wl["ctx"])
     peak, peak_kind = measured_peak_gbs()
     achieved = local_bytes / (kernel_ms * 1e-3) / 1e9
+    # DRAM traffic of one decode launch from the ncu capture of config 3 (profiles/decode_fast_kernel_config3.md):
+    # 192.72 MB read + 4.59 MB written for 192.77 MB algorithmic; traffic grows with the pages processed, so
+    # other workloads scale it by their algorithmic bytes
+    traffic = int(round(local_bytes * (192.72e6 + 4.59e6) / 192774144))
 
     # end to end through host buffers: pinned query -> device, attention, output -> pinned host
     host_q = q3.cpu().pin_memory()
@@ -374,7 +378,8 @@ def gpu_arm(args, wl) -> None:
                        "l2": f"per-GPU working set {local_bytes / 1e6:.0f} MB exceeds the 126 MB L2",
                        "parallelism": f"batch sharded over {world} GPU(s), output all-gather only"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "kernel": "decode attention call (all its kernels)",
+                         "traffic": traffic, "traffic_unit": "bytes per launch (ncu, config 3 capture scaled by algorithmic bytes)",
+                         "peak_kind": peak_kind, "kernel": "decode attention call (all its kernels)",
                          "us_per_launch": kernel_ms * 1e3, "per_gpu_gbs": achieved},
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(q3.numel() * 2), "d2h_bytes_per_step": int(out.numel() * 2)},
