@@ -245,17 +245,41 @@ int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int
                               int flavour, int splits, int pages_per_split, int split_base, int total_splits,
                               float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream);
 
+static int dartkv_sm_count() {
+  static int cached = 0;
+  if (cached == 0) {
+    int device = 0, count = 0;
+    if (cudaGetDevice(&device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && count > 0)
+      cached = count;
+    else
+      cached = 148;   // B200
+  }
+  return cached;
+}
+
 static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int query_heads, int flavour, int tokens) {
   DecodeLayout L{};
   const int bh = d->batch * d->kv_heads;
   const int target_blocks = 148 * 8;   // two resident blocks per SM, about four waves
   L.fast = flavour == DARTKV_DEQUANT_PER_OP && dartkv_decode_fast_supported(d, q_dtype, query_heads);
   if (L.fast) {
+    // A block hands its pages to four warp pairs round-robin, two blocks are resident per SM.  Pick the
+    // pages per block (a multiple of four, at most 16 blocks per (batch, kv head)) that minimizes
+    // waves x (pages per pair + a fixed per-block cost of about one page).
     const int pages = max(1, (tokens - d->sink_tokens) / d->page_size);
-    const int quads = (pages + 3) / 4;                 // a block hands pages to its four warps round-robin
-    int want = max(1, (target_blocks + bh - 1) / bh);
-    want = min(want, quads);
-    L.fast_pages_per_split = 4 * ((quads + want - 1) / want);
+    const int quads = (pages + 3) / 4;
+    const int resident = 2 * dartkv_sm_count();
+    int best_q = quads;
+    double best_cost = 1e30;
+    for (int q = max(1, (quads + 15) / 16); q <= quads; ++q) {
+      const int splits = (pages + 4 * q - 1) / (4 * q);
+      const int64_t blocks = (int64_t)bh * (splits + 1);
+      const int64_t waves = (blocks + resident - 1) / resident;
+      const double cost = (double)waves * (q + 1.0);
+      if (cost < best_cost - 1e-9) { best_cost = cost; best_q = q; }
+    }
+    L.fast_pages_per_split = 4 * best_q;
     L.fast_splits = (pages + L.fast_pages_per_split - 1) / L.fast_pages_per_split;
     L.total_splits = L.fast_splits + 1;                // + one block per (batch, kv head) for the dense tokens
   } else {
@@ -283,8 +307,8 @@ extern "C" int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* d, int
   for (int dt = 0; dt < 3; ++dt)
     for (int flavour = 0; flavour < 2; ++flavour) {
       DecodeLayout L = decode_layout(d, dt, query_heads, flavour, max_tokens);
-      best = max(best, layout_bytes(d, query_heads, L));
-      L.total_splits += 1;   // slack for rounding differences at smaller token counts
+      // the tensor-core layout uses at most 16 page splits + 1 dense block whatever the token count
+      if (L.fast) L.total_splits = 17;
       best = max(best, layout_bytes(d, query_heads, L));
     }
   return best;

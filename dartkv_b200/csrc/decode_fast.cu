@@ -129,7 +129,29 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, Block
       __syncthreads();
     } else { kind = 2; seg_end = seen; }
     (void)pages;
+    // dense rows of the next token are requested before the current one is consumed
+    auto dense_row = [&](const void* sink, const void* ring, int tok) -> uint2 {
+      const uint16_t* row = tok < sink_filled
+          ? reinterpret_cast<const uint16_t*>(sink) + ((int64_t)bh * d.sink_tokens + tok) * 128
+          : reinterpret_cast<const uint16_t*>(ring) + ((int64_t)bh * d.ring_tokens + (tok % d.ring_tokens)) * 128;
+      return *reinterpret_cast<const uint2*>(row + lane * 4);
+    };
+    auto value_dense = [&](int tok) { return !(tok >= sink_filled && tok < v_end); };
+    uint2 k_next = make_uint2(0, 0), v_next = make_uint2(0, 0);
+    {
+      const int first = t + warp;
+      if (first < seg_end) {
+        if (kind != 1) k_next = dense_row(d.k_sink, d.k_ring, first);
+        if (value_dense(first)) v_next = dense_row(d.v_sink, d.v_ring, first);
+      }
+    }
     for (int tok = t + warp; tok < seg_end; tok += kWarps) {
+      const uint2 k_raw = k_next, v_raw = v_next;
+      const int nxt = tok + kWarps;
+      if (nxt < seg_end) {
+        if (kind != 1) k_next = dense_row(d.k_sink, d.k_ring, nxt);
+        if (value_dense(nxt)) v_next = dense_row(d.v_sink, d.v_ring, nxt);
+      }
       float kv[4];
       if (kind == 1) {
         const int j = tok - page_first;
@@ -144,12 +166,8 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, Block
           kv[i] = rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn((float)code, s)), z));
         }
       } else {
-        const uint16_t* row = kind == 0
-            ? reinterpret_cast<const uint16_t*>(d.k_sink) + ((int64_t)bh * d.sink_tokens + tok) * 128
-            : reinterpret_cast<const uint16_t*>(d.k_ring) + ((int64_t)bh * d.ring_tokens + (tok % d.ring_tokens)) * 128;
-        uint2 raw = *reinterpret_cast<const uint2*>(row + lane * 4);
-        kv[0] = H::to_float((uint16_t)(raw.x & 0xFFFF)); kv[1] = H::to_float((uint16_t)(raw.x >> 16));
-        kv[2] = H::to_float((uint16_t)(raw.y & 0xFFFF)); kv[3] = H::to_float((uint16_t)(raw.y >> 16));
+        kv[0] = H::to_float((uint16_t)(k_raw.x & 0xFFFF)); kv[1] = H::to_float((uint16_t)(k_raw.x >> 16));
+        kv[2] = H::to_float((uint16_t)(k_raw.y & 0xFFFF)); kv[3] = H::to_float((uint16_t)(k_raw.y >> 16));
       }
       float s[4];
 #pragma unroll
@@ -164,7 +182,7 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, Block
       }
       // value row of the same token
       float vv[4];
-      if (tok >= sink_filled && tok < v_end) {
+      if (!value_dense(tok)) {
         const int64_t row = (int64_t)bh * d.max_value_tokens + (tok - d.sink_tokens);
         const uint32_t byte = d.v_codes[row * 32 + lane];
         const int g = (lane * 4) / d.value_group;
@@ -174,12 +192,8 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, Block
         for (int i = 0; i < 4; ++i)
           vv[i] = rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn((float)((byte >> (2 * i)) & 3u), sc)), z));
       } else {
-        const uint16_t* row = tok < sink_filled
-            ? reinterpret_cast<const uint16_t*>(d.v_sink) + ((int64_t)bh * d.sink_tokens + tok) * 128
-            : reinterpret_cast<const uint16_t*>(d.v_ring) + ((int64_t)bh * d.ring_tokens + (tok % d.ring_tokens)) * 128;
-        uint2 raw = *reinterpret_cast<const uint2*>(row + lane * 4);
-        vv[0] = H::to_float((uint16_t)(raw.x & 0xFFFF)); vv[1] = H::to_float((uint16_t)(raw.x >> 16));
-        vv[2] = H::to_float((uint16_t)(raw.y & 0xFFFF)); vv[3] = H::to_float((uint16_t)(raw.y >> 16));
+        vv[0] = H::to_float((uint16_t)(v_raw.x & 0xFFFF)); vv[1] = H::to_float((uint16_t)(v_raw.x >> 16));
+        vv[2] = H::to_float((uint16_t)(v_raw.y & 0xFFFF)); vv[3] = H::to_float((uint16_t)(v_raw.y >> 16));
       }
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
