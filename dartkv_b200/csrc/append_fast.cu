@@ -156,20 +156,40 @@ __device__ __forceinline__ uint32_t cap_pair(float qmax) {
   return one * 0x00010001u;
 }
 
-// KBITS: 0 = mixed 2+2-bit keys, else uniform keys with KBITS bits
+// |x| of a 16-bit float as the high word of a double (low word 0).  Magnitudes below the smallest
+// normal are lifted to it and the lift is taken back out of the final sum (sum_bias per element).
+template <int DT>
+__device__ __forceinline__ double abs_as_double(uint32_t magnitude) {
+  constexpr uint32_t kMinNormal = DT == DARTKV_BF16 ? 0x80u : 0x400u;
+  constexpr uint32_t kShift = DT == DARTKV_BF16 ? 8192u : 1024u;
+  constexpr uint32_t kBias = DT == DARTKV_BF16 ? 0x38000000u : 0x3F000000u;
+  return __hiloint2double((int)(max(magnitude, kMinNormal) * kShift + kBias), 0);
+}
+template <int DT>
+__device__ __forceinline__ double lifted_zero() {   // what abs_as_double returns for zero / subnormal magnitudes
+  return DT == DARTKV_BF16 ? 1.1754943508222875e-38 : 6.103515625e-05;
+}
+template <int DT>
+__device__ __forceinline__ double subnormal_unit() {   // value of one unit of a subnormal magnitude
+  return DT == DARTKV_BF16 ? 9.183549615799121e-41 : 5.9604644775390625e-08;   // 2^-133, 2^-24
+}
+
+// KBITS: 0 = mixed 2+2-bit keys, else uniform keys with KBITS bits.
+// One block of 64 threads per (batch*head, page); thread p owns the adjacent channels 2p, 2p+1, which
+// travel together as one packed pair through both passes.
 template <int DT, int KBITS>
-__global__ void __launch_bounds__(128) fast_key_pages_kernel(dartkv_cache_desc d, RowSource src, int first_slot,
-                                                             int num_pages, int page_token_start,
-                                                             const int32_t* __restrict__ indices, int32_t* nonfinite) {
+__global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d, RowSource src, int first_slot,
+                                                            int num_pages, int page_token_start,
+                                                            const int32_t* __restrict__ indices, int32_t* nonfinite) {
   using P = Pack16<DT>;
-  __shared__ __align__(16) uint16_t s_page[kP * kD];
+  __shared__ __align__(16) uint32_t s_page[kP * 64];   // [token][channel pair]
   __shared__ float s_score[kD];
-  const int bh = blockIdx.x, pg = blockIdx.y, c = threadIdx.x;
+  const int bh = blockIdx.x, pg = blockIdx.y, p = threadIdx.x;
   const int t0 = page_token_start + pg * kP;
-  // stage the page: 2048 16-byte pieces, 16 per thread
   const uint16_t *chunk_base, *ring_base;
   src.bases(bh, chunk_base, ring_base);
-  for (int i = c; i < kP * 16; i += 128) {
+  // stage the page: 2048 16-byte pieces, 32 per thread
+  for (int i = p; i < kP * 16; i += 64) {
     int r = i >> 4, piece = i & 15;
     cp_async16(reinterpret_cast<char*>(s_page) + r * 256 + piece * 16,
                reinterpret_cast<const char*>(src.row_from(chunk_base, ring_base, t0 + r)) + piece * 16);
@@ -178,123 +198,168 @@ __global__ void __launch_bounds__(128) fast_key_pages_kernel(dartkv_cache_desc d
   __syncthreads();
 
   uint8_t* page = d.k_pages + ((int64_t)bh * d.max_key_pages + first_slot + pg) * d.key_page_bytes;
-  const uint16_t* col = s_page + c;
-  // pass 1: min / max on packed pairs, sum |k| in double (order independent for 16-bit data)
-  uint32_t mn2 = (uint32_t)col[0] * 0x00010001u, mx2 = mn2;
-  uint32_t exp_or = 0;   // bit 15 / 31 end up set iff some magnitude has an all-ones exponent (Inf or NaN)
+  const uint32_t* col = s_page + p;
+  // pass 1: packed min / max, Inf/NaN detection, sum |k| per channel in double (exact for 16-bit inputs)
+  uint32_t mn2 = col[0], mx2 = mn2, exp_or = 0;
   constexpr uint32_t kExpCarry = DT == DARTKV_BF16 ? 0x00800080u : 0x04000400u;
-  double asum = 0.0;
-#pragma unroll 4
-  for (int t = 0; t < kP; t += 2) {
-    const uint32_t lo = col[t * kD], hi = col[(t + 1) * kD];
-    const uint32_t x2 = lo | (hi << 16);
+  constexpr uint32_t kMinNormal = DT == DARTKV_BF16 ? 0x80u : 0x400u;
+  double sum_lo = 0.0, sum_hi = 0.0;
+  int lifted_lo = 0, lifted_hi = 0, sub_lo = 0, sub_hi = 0;   // lifted elements and their true magnitudes
+#pragma unroll 8
+  for (int t = 0; t < kP; ++t) {
+    const uint32_t x2 = col[t * 64];
     mn2 = P::min2(mn2, x2);
     mx2 = P::max2(mx2, x2);
-    exp_or |= (x2 & 0x7FFF7FFFu) + kExpCarry;
-    if (KBITS == 0) asum += P::abs_double(lo) + P::abs_double(hi);
+    const uint32_t mag2 = x2 & 0x7FFF7FFFu;
+    exp_or |= mag2 + kExpCarry;
+    if (KBITS == 0) {
+      const uint32_t m_lo = mag2 & 0xFFFFu, m_hi = mag2 >> 16;
+      sum_lo += abs_as_double<DT>(m_lo);
+      sum_hi += abs_as_double<DT>(m_hi);
+      if (m_lo < kMinNormal) { ++lifted_lo; sub_lo += (int)m_lo; }
+      if (m_hi < kMinNormal) { ++lifted_hi; sub_hi += (int)m_hi; }
+    }
   }
   const bool bad = (exp_or & 0x80008000u) != 0;
-  const float mn = fminf(P::lo(mn2), P::hi(mn2)), mx = fmaxf(P::lo(mx2), P::hi(mx2));
-  int slot = -1;
-  float qmax;
+  int slot_lo = -1, slot_hi = -1;
+  float qmax_lo, qmax_hi;
   if (KBITS == 0) {
     const int K = d.promoted;
     int32_t* idx_field = reinterpret_cast<int32_t*>(page + d.key_off_index);
+    const int c_lo = 2 * p, c_hi = 2 * p + 1;
     if (indices != nullptr) {
       const int32_t* mine = indices + ((int64_t)bh * num_pages + pg) * K;
-      for (int k = 0; k < K; ++k)
-        if (mine[k] == c) slot = k;
-      if (c < K) idx_field[c] = mine[c];
+      for (int k = 0; k < K; ++k) {
+        const int ch = mine[k];
+        if (ch == c_lo) slot_lo = k;
+        if (ch == c_hi) slot_hi = k;
+      }
+      for (int k = p; k < K; k += 64) idx_field[k] = mine[k];
     } else if (K == kD) {
-      slot = c;
-      idx_field[c] = c;
+      slot_lo = c_lo; slot_hi = c_hi;
+      idx_field[c_lo] = c_lo; idx_field[c_hi] = c_hi;
     } else if (K > 0) {
-      const float score = rnd<DT>(__fdiv_rn((float)asum, (float)kP));
-      s_score[c] = score;
+      // zero / subnormal magnitudes were lifted to the smallest normal: take the lift out, put their value in
+      const double fix = lifted_zero<DT>(), unit = subnormal_unit<DT>();
+      const float score_lo = rnd<DT>(__fdiv_rn((float)(sum_lo - fix * lifted_lo + unit * sub_lo), (float)kP));
+      const float score_hi = rnd<DT>(__fdiv_rn((float)(sum_hi - fix * lifted_hi + unit * sub_hi), (float)kP));
+      s_score[c_lo] = score_lo;
+      s_score[c_hi] = score_hi;
       __syncthreads();
-      int rank = 0;
+      int rank_lo = 0, rank_hi = 0;
 #pragma unroll 8
       for (int o = 0; o < kD; ++o) {
         const float other = s_score[o];
-        rank += (other > score) || (other == score && o < c);
+        rank_lo += (other > score_lo) || (other == score_lo && o < c_lo);
+        rank_hi += (other > score_hi) || (other == score_hi && o < c_hi);
       }
-      if (rank < K) { slot = rank; idx_field[rank] = c; }
+      if (rank_lo < K) { slot_lo = rank_lo; idx_field[rank_lo] = c_lo; }
+      if (rank_hi < K) { slot_hi = rank_hi; idx_field[rank_hi] = c_hi; }
     }
-    qmax = slot >= 0 ? 15.0f : 3.0f;
+    qmax_lo = slot_lo >= 0 ? 15.0f : 3.0f;
+    qmax_hi = slot_hi >= 0 ? 15.0f : 3.0f;
   } else {
-    qmax = (float)((1 << KBITS) - 1);
+    qmax_lo = qmax_hi = (float)((1 << KBITS) - 1);
   }
-  const float scale = scale_of<DT>(mn, mx, qmax);
-  store_f(page + d.key_off_scale, d.md_dtype, c, scale);
-  store_f(page + d.key_off_zero, d.md_dtype, c, mn);
-  const float inv = __frcp_rn(scale);
-  const uint32_t mnp = (uint32_t)P::bits(mn) * 0x00010001u;
-  const uint32_t cap2 = cap_pair<DT>(qmax);
+  const float mn_lo = P::lo(mn2), mn_hi = P::hi(mn2);
+  const float scale_lo = scale_of<DT>(mn_lo, P::lo(mx2), qmax_lo), scale_hi = scale_of<DT>(mn_hi, P::hi(mx2), qmax_hi);
+  store_f(page + d.key_off_scale, d.md_dtype, 2 * p, scale_lo);
+  store_f(page + d.key_off_scale, d.md_dtype, 2 * p + 1, scale_hi);
+  store_f(page + d.key_off_zero, d.md_dtype, 2 * p, mn_lo);
+  store_f(page + d.key_off_zero, d.md_dtype, 2 * p + 1, mn_hi);
+  const float inv_lo = __frcp_rn(scale_lo), inv_hi = __frcp_rn(scale_hi);
+  const uint32_t cap2 = (uint32_t)P::bits((DT == DARTKV_BF16 ? 128.0f : 1024.0f) + qmax_lo) |
+                        ((uint32_t)P::bits((DT == DARTKV_BF16 ? 128.0f : 1024.0f) + qmax_hi) << 16);
 
-  // pass 2: a pair is (token i, token i + step) of a 32-bit output word, so both codes fall 16 bits apart
+  // pass 2: codes of (channel 2p, channel 2p+1) for one token per step, packed into one word per channel
   constexpr int BITS = KBITS == 0 ? 2 : KBITS;      // bits per stored plane
   constexpr int CODE_BITS = KBITS == 0 ? 4 : KBITS; // bits the quantizer produces
   constexpr int PER_WORD = 32 / BITS;               // tokens per 32-bit word of a plane
-  constexpr int STEP = PER_WORD / 2;
   constexpr int WORDS = kP / PER_WORD;
-  constexpr uint32_t FIELD = ((1u << BITS) - 1u) * 0x00010001u;
-  uint32_t* low_row = reinterpret_cast<uint32_t*>(page + c * (WORDS * 4));
-  uint32_t* high_row = (KBITS == 0 && slot >= 0) ? reinterpret_cast<uint32_t*>(page + d.key_off_high + slot * (WORDS * 4)) : nullptr;
+  constexpr uint32_t FIELD = (1u << BITS) - 1u;
+  uint32_t* low_lo = reinterpret_cast<uint32_t*>(page + (2 * p) * (WORDS * 4));
+  uint32_t* low_hi = low_lo + WORDS;
+  uint32_t* high_lo = (KBITS == 0 && slot_lo >= 0) ? reinterpret_cast<uint32_t*>(page + d.key_off_high + slot_lo * (WORDS * 4)) : nullptr;
+  uint32_t* high_hi = (KBITS == 0 && slot_hi >= 0) ? reinterpret_cast<uint32_t*>(page + d.key_off_high + slot_hi * (WORDS * 4)) : nullptr;
 #pragma unroll 1
   for (int w4 = 0; w4 < WORDS; w4 += 4) {
-    uint32_t lo_words[4], hi_words[4];
+    uint32_t a_lo[4], a_hi[4], b_lo[4], b_hi[4];   // a: low plane, b: high plane
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      uint32_t lacc = 0, hacc = 0;
+      uint32_t la = 0, ha = 0, lb = 0, hb = 0;
       const int base = (w4 + q) * PER_WORD;
 #pragma unroll
-      for (int u = 0; u < STEP; ++u) {
-        const uint32_t x2 = (uint32_t)col[(base + u) * kD] | ((uint32_t)col[(base + u + STEP) * kD] << 16);
-        const uint32_t codes = pair_codes<DT, CODE_BITS>(x2, mnp, scale, inv, cap2);
-        lacc |= (codes & FIELD) << (BITS * u);
-        if (KBITS == 0) hacc |= ((codes >> 2) & FIELD) << (BITS * u);
+      for (int u = 0; u < PER_WORD; ++u) {
+        const uint32_t x2 = col[(base + u) * 64];
+        const uint32_t a2 = P::sub(x2, mn2);
+        const float q_l = P::quotient(P::lo(a2), scale_lo, inv_lo), q_h = P::quotient(P::hi(a2), scale_hi, inv_hi);
+        uint32_t codes;
+        if (DT == DARTKV_BF16 && CODE_BITS == 8) {
+          const uint32_t r2 = P::pack(q_h, q_l);
+          codes = (uint32_t)fminf(rintf(P::lo(r2)), 255.0f) | ((uint32_t)fminf(rintf(P::hi(r2)), 255.0f) << 16);
+        } else {
+          codes = P::min2(P::add(P::pack(q_h, q_l), P::kMagic), cap2);
+        }
+        la |= (codes & FIELD) << (BITS * u);
+        ha |= ((codes >> 16) & FIELD) << (BITS * u);
+        if (KBITS == 0) {
+          lb |= ((codes >> 2) & FIELD) << (BITS * u);
+          hb |= ((codes >> 18) & FIELD) << (BITS * u);
+        }
       }
-      lo_words[q] = lacc;
-      hi_words[q] = hacc;
+      a_lo[q] = la; a_hi[q] = ha; b_lo[q] = lb; b_hi[q] = hb;
     }
-    reinterpret_cast<uint4*>(low_row)[w4 / 4] = make_uint4(lo_words[0], lo_words[1], lo_words[2], lo_words[3]);
-    if (KBITS == 0 && high_row) reinterpret_cast<uint4*>(high_row)[w4 / 4] = make_uint4(hi_words[0], hi_words[1], hi_words[2], hi_words[3]);
+    reinterpret_cast<uint4*>(low_lo)[w4 / 4] = make_uint4(a_lo[0], a_lo[1], a_lo[2], a_lo[3]);
+    reinterpret_cast<uint4*>(low_hi)[w4 / 4] = make_uint4(a_hi[0], a_hi[1], a_hi[2], a_hi[3]);
+    if (KBITS == 0) {
+      if (high_lo) reinterpret_cast<uint4*>(high_lo)[w4 / 4] = make_uint4(b_lo[0], b_lo[1], b_lo[2], b_lo[3]);
+      if (high_hi) reinterpret_cast<uint4*>(high_hi)[w4 / 4] = make_uint4(b_hi[0], b_hi[1], b_hi[2], b_hi[3]);
+    }
   }
   if (bad && nonfinite) *nonfinite = 1;
 }
 
-// one warp per four token rows (loads issued together); VBITS in {2,4,8}; LPG = lanes per group
+// Values: eight lanes per token row (16 channels per lane), four rows per warp per step, two steps in
+// flight.  VBITS in {2,4,8}; LPG = lanes per value group (value_group / 16).
 template <int DT, int VBITS>
 __global__ void __launch_bounds__(256) fast_value_rows_kernel(dartkv_cache_desc d, RowSource src, int value_begin,
                                                               int count, int lanes_per_group, int32_t* nonfinite) {
   using P = Pack16<DT>;
-  constexpr int ROWS = 4;
+  constexpr int STEPS = 2;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int sub = lane >> 3, part = lane & 7;   // row within the step, 16-channel slice of the row
   const uint32_t total = (uint32_t)d.batch * d.kv_heads * count;   // checked on the host to fit 32 bits
-  const uint32_t first = (uint32_t)warp * ROWS;
+  const uint32_t first = (uint32_t)warp * (4 * STEPS);
   if (first >= total) return;
-  uint2 raw[ROWS];
-  int bh_of[ROWS], t_of[ROWS];
-  {
-    int bh = (int)(first / (uint32_t)count), j = (int)(first % (uint32_t)count);
+  uint4 raw[STEPS][2];
+  int bh_of[STEPS], t_of[STEPS];
+  bool live[STEPS];
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      bh_of[r] = bh;
-      t_of[r] = value_begin + j;
-      raw[r] = *reinterpret_cast<const uint2*>(src.row(bh, t_of[r]) + lane * 4);
-      if (first + r + 1 < total && ++j == count) { j = 0; ++bh; }
-    }
+  for (int s = 0; s < STEPS; ++s) {
+    const uint32_t row = first + 4 * s + sub;
+    live[s] = row < total;
+    const uint32_t r = live[s] ? row : total - 1;
+    bh_of[s] = (int)(r / (uint32_t)count);
+    t_of[s] = value_begin + (int)(r % (uint32_t)count);
+    const uint4* ptr = reinterpret_cast<const uint4*>(src.row(bh_of[s], t_of[s]) + part * 16);
+    raw[s][0] = ptr[0];
+    raw[s][1] = ptr[1];
   }
   constexpr float qmax = (float)((1 << VBITS) - 1);
   const uint32_t cap2 = cap_pair<DT>(qmax);
+  constexpr uint32_t kExpCarry = DT == DARTKV_BF16 ? 0x00800080u : 0x04000400u;
   bool bad = false;
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) {
-    if (first + r >= total) break;
-    const uint32_t x01 = raw[r].x, x23 = raw[r].y;
-    constexpr uint32_t kExpCarry = DT == DARTKV_BF16 ? 0x00800080u : 0x04000400u;
-    bad |= ((((x01 & 0x7FFF7FFFu) + kExpCarry) | ((x23 & 0x7FFF7FFFu) + kExpCarry)) & 0x80008000u) != 0;
-    uint32_t mn2 = P::min2(x01, x23), mx2 = P::max2(x01, x23);
+  for (int s = 0; s < STEPS; ++s) {
+    const uint32_t x[8] = {raw[s][0].x, raw[s][0].y, raw[s][0].z, raw[s][0].w, raw[s][1].x, raw[s][1].y, raw[s][1].z, raw[s][1].w};
+    uint32_t mn2 = x[0], mx2 = x[0], exp_or = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      mn2 = P::min2(mn2, x[i]);
+      mx2 = P::max2(mx2, x[i]);
+      exp_or |= (x[i] & 0x7FFF7FFFu) + kExpCarry;
+    }
+    bad |= live[s] && (exp_or & 0x80008000u) != 0;
     for (int off = 1; off < lanes_per_group; off <<= 1) {
       mn2 = P::min2(mn2, __shfl_xor_sync(0xffffffffu, mn2, off));
       mx2 = P::max2(mx2, __shfl_xor_sync(0xffffffffu, mx2, off));
@@ -303,21 +368,34 @@ __global__ void __launch_bounds__(256) fast_value_rows_kernel(dartkv_cache_desc 
     const float scale = scale_of<DT>(mn, mx, qmax);
     const float inv = __frcp_rn(scale);
     const uint32_t mnp = (uint32_t)P::bits(mn) * 0x00010001u;
-    const uint32_t c01 = pair_codes<DT, VBITS>(x01, mnp, scale, inv, cap2);
-    const uint32_t c23 = pair_codes<DT, VBITS>(x23, mnp, scale, inv, cap2);
-    const int64_t out_row = (int64_t)bh_of[r] * d.max_value_tokens + (t_of[r] - d.sink_tokens);
+    uint32_t c[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) c[i] = pair_codes<DT, VBITS>(x[i], mnp, scale, inv, cap2);
+    if (!live[s]) continue;
+    const int64_t out_row = (int64_t)bh_of[s] * d.max_value_tokens + (t_of[s] - d.sink_tokens);
     uint8_t* codes = d.v_codes + out_row * d.value_row_bytes;
     if (VBITS == 2) {
-      codes[lane] = (uint8_t)((c01 & 3u) | ((c01 >> 14) & 0xCu) | ((c23 & 3u) << 4) | ((c23 >> 10) & 0xC0u));
+      uint32_t word = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) word |= ((c[i] & 3u) | ((c[i] >> 14) & 0xCu)) << (4 * i);
+      reinterpret_cast<uint32_t*>(codes)[part] = word;
     } else if (VBITS == 4) {
-      reinterpret_cast<uint16_t*>(codes)[lane] =
-          (uint16_t)((c01 & 0xFu) | ((c01 >> 12) & 0xF0u) | ((c23 & 0xFu) << 8) | ((c23 >> 4) & 0xF000u));
+      uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        w0 |= ((c[i] & 0xFu) | ((c[i] >> 12) & 0xF0u)) << (8 * i);
+        w1 |= ((c[i + 4] & 0xFu) | ((c[i + 4] >> 12) & 0xF0u)) << (8 * i);
+      }
+      reinterpret_cast<uint2*>(codes)[part] = make_uint2(w0, w1);
     } else {
-      reinterpret_cast<uint32_t*>(codes)[lane] =
-          (c01 & 0xFFu) | ((c01 >> 8) & 0xFF00u) | ((c23 & 0xFFu) << 16) | ((c23 << 8) & 0xFF000000u);
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        w[i] = (c[2 * i] & 0xFFu) | ((c[2 * i] >> 8) & 0xFF00u) | ((c[2 * i + 1] & 0xFFu) << 16) | ((c[2 * i + 1] << 8) & 0xFF000000u);
+      reinterpret_cast<uint4*>(codes)[part] = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    if ((lane % lanes_per_group) == 0) {
-      const int g = lane / lanes_per_group;
+    if ((part % lanes_per_group) == 0) {
+      const int g = part / lanes_per_group;
       store_f(d.v_meta, d.md_dtype, (out_row * 2 + 0) * d.value_groups + g, scale);
       store_f(d.v_meta, d.md_dtype, (out_row * 2 + 1) * d.value_groups + g, mn);
     }
@@ -339,7 +417,7 @@ int dartkv_append_fast_supported(const dartkv_cache_desc* d, const dartkv_append
   if (d->page_size == kP && d->key_group == kP && (p->num_pages == 0 || p->last_page_tokens == kP) &&
       (d->key_mode == DARTKV_QUANTIZED_PAGE || d->promoted <= kD))
     ok |= 1;
-  if (d->value_group == 32 || d->value_group == 64 || d->value_group == 128) ok |= 2;
+  if (d->value_group == 16 || d->value_group == 32 || d->value_group == 64 || d->value_group == 128) ok |= 2;
   return ok;
 }
 
@@ -348,13 +426,13 @@ static int launch_keys(const dartkv_cache_desc& d, const dartkv_append_plan& p, 
                        const int32_t* indices, int32_t* nonfinite, cudaStream_t stream) {
   dim3 grid(d.batch * d.kv_heads, p.num_pages);
   if (d.key_mode == DARTKV_MIXED_PAGE)
-    fast_key_pages_kernel<DT, 0><<<grid, 128, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+    fast_key_pages_kernel<DT, 0><<<grid, 64, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
   else if (d.key_bits == 2)
-    fast_key_pages_kernel<DT, 2><<<grid, 128, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+    fast_key_pages_kernel<DT, 2><<<grid, 64, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
   else if (d.key_bits == 4)
-    fast_key_pages_kernel<DT, 4><<<grid, 128, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+    fast_key_pages_kernel<DT, 4><<<grid, 64, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
   else
-    fast_key_pages_kernel<DT, 8><<<grid, 128, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+    fast_key_pages_kernel<DT, 8><<<grid, 64, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
   DARTKV_LAUNCH_OK("fast_key_pages_kernel");
   return DARTKV_OK;
 }
@@ -365,8 +443,8 @@ static int launch_values(const dartkv_cache_desc& d, const dartkv_append_plan& p
   const int count = p.value_end - p.value_begin;
   const int64_t rows = (int64_t)d.batch * d.kv_heads * count;
   DARTKV_REQUIRE(rows < (1ll << 31), "too many value rows in one append (limit 2^31)");
-  const unsigned blocks = (unsigned)((rows + 31) / 32);   // 8 warps per block, 4 rows per warp
-  const int lpg = d.value_group / 4;
+  const unsigned blocks = (unsigned)((rows + 63) / 64);   // 8 warps per block, 8 rows per warp
+  const int lpg = d.value_group / 16;
   if (d.value_bits == 2)
     fast_value_rows_kernel<DT, 2><<<blocks, 256, 0, stream>>>(d, src, p.value_begin, count, lpg, nonfinite);
   else if (d.value_bits == 4)
