@@ -1,11 +1,12 @@
 // Page-shaped quantize+pack kernels for the common geometry: head_dim 128, 16-bit data,
 // full 128-token key pages with one 128-token key group, value groups of 32/64/128 channels.
 //
-// Keys (one block of 128 threads per (batch*head, page)): the page is staged in shared memory
-// with 16-byte async copies; thread c owns channel c: one pass for min / max / sum|k|, a
-// block-wide rank for the promoted channels, one pass that emits the codes and packs them in
-// registers, then 32-byte row stores.  Values (one warp per token row): four channels per lane,
-// group min/max by xor-shuffles, packed bytes and metadata written coalesced.
+// Keys (one block of 64 threads per (batch*head, page)): the page is staged in shared memory
+// with 16-byte async copies; thread p owns the channel pair (2p, 2p+1), which moves through both
+// passes as one packed 16-bit pair: a pass for min / max / sum|k|, a block-wide rank for the
+// promoted channels, a pass that emits the codes and packs them in registers, then 16-byte row
+// stores.  Values: eight lanes per token row (16 channels per lane), group min/max by
+// xor-shuffles, packed bytes and metadata written coalesced.
 // HBM traffic per page: 64 KiB read (K and V rows), 10.6 KiB written (2-bit, 32 promoted).
 // The arithmetic is the reference's per-op rounding in the data dtype
 // (src/dart/quantization.py:178-186, src/dart/mixed.py:200-209).
@@ -89,10 +90,10 @@ template <> struct Pack16<DARTKV_BF16> {
     uint32_t d; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
   }
   static __device__ __forceinline__ uint32_t min2(uint32_t a, uint32_t b) {
-    uint32_t d; asm("min.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+    uint32_t d; asm("min.NaN.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
   }
   static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
-    uint32_t d; asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+    uint32_t d; asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
   }
   static __device__ __forceinline__ float lo(uint32_t v) { return __uint_as_float(v << 16); }
   static __device__ __forceinline__ float hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
@@ -116,10 +117,10 @@ template <> struct Pack16<DARTKV_F16> {
     uint32_t d; asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
   }
   static __device__ __forceinline__ uint32_t min2(uint32_t a, uint32_t b) {
-    uint32_t d; asm("min.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+    uint32_t d; asm("min.NaN.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
   }
   static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
-    uint32_t d; asm("max.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+    uint32_t d; asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
   }
   static __device__ __forceinline__ float lo(uint32_t v) { return __half2float(__ushort_as_half((uint16_t)(v & 0xFFFFu))); }
   static __device__ __forceinline__ float hi(uint32_t v) { return __half2float(__ushort_as_half((uint16_t)(v >> 16))); }
@@ -156,22 +157,23 @@ __device__ __forceinline__ uint32_t cap_pair(float qmax) {
   return one * 0x00010001u;
 }
 
-// |x| of a 16-bit float as the high word of a double (low word 0).  Magnitudes below the smallest
-// normal are lifted to it and the lift is taken back out of the final sum (sum_bias per element).
+__device__ __forceinline__ uint32_t umin16x2(uint32_t a, uint32_t b) {
+  uint32_t d; asm("min.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+}
+
+// |x| of a normal 16-bit float, from its 15 magnitude bits, as the high word of a double (low word 0)
 template <int DT>
-__device__ __forceinline__ double abs_as_double(uint32_t magnitude) {
-  constexpr uint32_t kMinNormal = DT == DARTKV_BF16 ? 0x80u : 0x400u;
+__device__ __forceinline__ double normal_abs_as_double(uint32_t magnitude) {
   constexpr uint32_t kShift = DT == DARTKV_BF16 ? 8192u : 1024u;
   constexpr uint32_t kBias = DT == DARTKV_BF16 ? 0x38000000u : 0x3F000000u;
-  return __hiloint2double((int)(max(magnitude, kMinNormal) * kShift + kBias), 0);
+  return __hiloint2double((int)(magnitude * kShift + kBias), 0);
 }
+// any magnitude, zero and subnormals included
 template <int DT>
-__device__ __forceinline__ double lifted_zero() {   // what abs_as_double returns for zero / subnormal magnitudes
-  return DT == DARTKV_BF16 ? 1.1754943508222875e-38 : 6.103515625e-05;
-}
-template <int DT>
-__device__ __forceinline__ double subnormal_unit() {   // value of one unit of a subnormal magnitude
-  return DT == DARTKV_BF16 ? 9.183549615799121e-41 : 5.9604644775390625e-08;   // 2^-133, 2^-24
+__device__ __forceinline__ double any_abs_as_double(uint32_t magnitude) {
+  constexpr uint32_t kMinNormal = DT == DARTKV_BF16 ? 0x80u : 0x400u;
+  constexpr double kUnit = DT == DARTKV_BF16 ? 9.183549615799121e-41 : 5.9604644775390625e-08;   // 2^-133, 2^-24
+  return magnitude >= kMinNormal ? normal_abs_as_double<DT>(magnitude) : (double)(int)magnitude * kUnit;
 }
 
 // KBITS: 0 = mixed 2+2-bit keys, else uniform keys with KBITS bits.
@@ -183,44 +185,51 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
                                                             const int32_t* __restrict__ indices, int32_t* nonfinite) {
   using P = Pack16<DT>;
   __shared__ __align__(16) uint32_t s_page[kP * 64];   // [token][channel pair]
-  __shared__ float s_score[kD];
+  __shared__ __align__(16) uint32_t s_key[kD];
   const int bh = blockIdx.x, pg = blockIdx.y, p = threadIdx.x;
   const int t0 = page_token_start + pg * kP;
   const uint16_t *chunk_base, *ring_base;
   src.bases(bh, chunk_base, ring_base);
-  // stage the page: 2048 16-byte pieces, 32 per thread
-  for (int i = p; i < kP * 16; i += 64) {
-    int r = i >> 4, piece = i & 15;
-    cp_async16(reinterpret_cast<char*>(s_page) + r * 256 + piece * 16,
-               reinterpret_cast<const char*>(src.row_from(chunk_base, ring_base, t0 + r)) + piece * 16);
+  // stage the page: 2048 16-byte pieces, 32 per thread (thread p: piece p%16 of rows p/16, p/16+4, ...)
+  {
+    const int piece = p & 15, r0 = p >> 4;
+    char* dst = reinterpret_cast<char*>(s_page) + r0 * 256 + piece * 16;
+    if (t0 >= src.chunk_start) {
+      const char* from = reinterpret_cast<const char*>(chunk_base + (int64_t)(t0 - src.chunk_start + r0) * src.st) + piece * 16;
+      const int64_t step = src.st * 8;   // four rows, in bytes
+#pragma unroll 8
+      for (int k = 0; k < kP / 4; ++k) cp_async16(dst + k * 1024, from + k * step);
+    } else {
+      for (int k = 0; k < kP / 4; ++k)
+        cp_async16(dst + k * 1024,
+                   reinterpret_cast<const char*>(src.row_from(chunk_base, ring_base, t0 + r0 + 4 * k)) + piece * 16);
+    }
   }
   cp_async_wait_all();
   __syncthreads();
 
   uint8_t* page = d.k_pages + ((int64_t)bh * d.max_key_pages + first_slot + pg) * d.key_page_bytes;
   const uint32_t* col = s_page + p;
-  // pass 1: packed min / max, Inf/NaN detection, sum |k| per channel in double (exact for 16-bit inputs)
-  uint32_t mn2 = col[0], mx2 = mn2, exp_or = 0;
-  constexpr uint32_t kExpCarry = DT == DARTKV_BF16 ? 0x00800080u : 0x04000400u;
+  // pass 1: packed min / max (NaN-propagating, so Inf/NaN inputs surface in them) and, for mixed pages,
+  // sum |k| per channel in double (exact for 16-bit inputs).  The loop takes every magnitude for a normal
+  // number; the smallest magnitude seen says whether a channel has to be summed again with care.
+  uint32_t mn2 = col[0], mx2 = mn2, min_mag2 = 0xFFFFFFFFu;
   constexpr uint32_t kMinNormal = DT == DARTKV_BF16 ? 0x80u : 0x400u;
   double sum_lo = 0.0, sum_hi = 0.0;
-  int lifted_lo = 0, lifted_hi = 0, sub_lo = 0, sub_hi = 0;   // lifted elements and their true magnitudes
 #pragma unroll 8
   for (int t = 0; t < kP; ++t) {
     const uint32_t x2 = col[t * 64];
     mn2 = P::min2(mn2, x2);
     mx2 = P::max2(mx2, x2);
-    const uint32_t mag2 = x2 & 0x7FFF7FFFu;
-    exp_or |= mag2 + kExpCarry;
     if (KBITS == 0) {
-      const uint32_t m_lo = mag2 & 0xFFFFu, m_hi = mag2 >> 16;
-      sum_lo += abs_as_double<DT>(m_lo);
-      sum_hi += abs_as_double<DT>(m_hi);
-      if (m_lo < kMinNormal) { ++lifted_lo; sub_lo += (int)m_lo; }
-      if (m_hi < kMinNormal) { ++lifted_hi; sub_hi += (int)m_hi; }
+      const uint32_t mag2 = x2 & 0x7FFF7FFFu;
+      min_mag2 = umin16x2(min_mag2, mag2);
+      sum_lo += normal_abs_as_double<DT>(mag2 & 0xFFFFu);
+      sum_hi += normal_abs_as_double<DT>(mag2 >> 16);
     }
   }
-  const bool bad = (exp_or & 0x80008000u) != 0;
+  const float mn_lo = P::lo(mn2), mn_hi = P::hi(mn2), mx_lo = P::lo(mx2), mx_hi = P::hi(mx2);
+  const bool bad = !(isfinite(mn_lo) && isfinite(mn_hi) && isfinite(mx_lo) && isfinite(mx_hi));
   int slot_lo = -1, slot_hi = -1;
   float qmax_lo, qmax_hi;
   if (KBITS == 0) {
@@ -239,19 +248,27 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
       slot_lo = c_lo; slot_hi = c_hi;
       idx_field[c_lo] = c_lo; idx_field[c_hi] = c_hi;
     } else if (K > 0) {
-      // zero / subnormal magnitudes were lifted to the smallest normal: take the lift out, put their value in
-      const double fix = lifted_zero<DT>(), unit = subnormal_unit<DT>();
-      const float score_lo = rnd<DT>(__fdiv_rn((float)(sum_lo - fix * lifted_lo + unit * sub_lo), (float)kP));
-      const float score_hi = rnd<DT>(__fdiv_rn((float)(sum_hi - fix * lifted_hi + unit * sub_hi), (float)kP));
-      s_score[c_lo] = score_lo;
-      s_score[c_hi] = score_hi;
+      if ((min_mag2 & 0xFFFFu) < kMinNormal || (min_mag2 >> 16) < kMinNormal) {   // zeros or subnormals: sum again
+        sum_lo = 0.0; sum_hi = 0.0;
+        for (int t = 0; t < kP; ++t) {
+          const uint32_t mag2 = col[t * 64] & 0x7FFF7FFFu;
+          sum_lo += any_abs_as_double<DT>(mag2 & 0xFFFFu);
+          sum_hi += any_abs_as_double<DT>(mag2 >> 16);
+        }
+      }
+      // rank by (score descending, channel ascending): scores are non-negative 16-bit floats, so their bit
+      // patterns order like integers and one unsigned key carries both criteria
+      const uint32_t key_lo = ((uint32_t)P::bits(__fdiv_rn((float)sum_lo, (float)kP)) << 7) | (uint32_t)(kD - 1 - c_lo);
+      const uint32_t key_hi = ((uint32_t)P::bits(__fdiv_rn((float)sum_hi, (float)kP)) << 7) | (uint32_t)(kD - 1 - c_hi);
+      s_key[c_lo] = key_lo;
+      s_key[c_hi] = key_hi;
       __syncthreads();
       int rank_lo = 0, rank_hi = 0;
-#pragma unroll 8
-      for (int o = 0; o < kD; ++o) {
-        const float other = s_score[o];
-        rank_lo += (other > score_lo) || (other == score_lo && o < c_lo);
-        rank_hi += (other > score_hi) || (other == score_hi && o < c_hi);
+#pragma unroll 4
+      for (int o = 0; o < kD / 4; ++o) {
+        const uint4 k4 = reinterpret_cast<const uint4*>(s_key)[o];
+        rank_lo += (k4.x > key_lo) + (k4.y > key_lo) + (k4.z > key_lo) + (k4.w > key_lo);
+        rank_hi += (k4.x > key_hi) + (k4.y > key_hi) + (k4.z > key_hi) + (k4.w > key_hi);
       }
       if (rank_lo < K) { slot_lo = rank_lo; idx_field[rank_lo] = c_lo; }
       if (rank_hi < K) { slot_hi = rank_hi; idx_field[rank_hi] = c_hi; }
@@ -261,8 +278,7 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
   } else {
     qmax_lo = qmax_hi = (float)((1 << KBITS) - 1);
   }
-  const float mn_lo = P::lo(mn2), mn_hi = P::hi(mn2);
-  const float scale_lo = scale_of<DT>(mn_lo, P::lo(mx2), qmax_lo), scale_hi = scale_of<DT>(mn_hi, P::hi(mx2), qmax_hi);
+  const float scale_lo = scale_of<DT>(mn_lo, mx_lo, qmax_lo), scale_hi = scale_of<DT>(mn_hi, mx_hi, qmax_hi);
   store_f(page + d.key_off_scale, d.md_dtype, 2 * p, scale_lo);
   store_f(page + d.key_off_scale, d.md_dtype, 2 * p + 1, scale_hi);
   store_f(page + d.key_off_zero, d.md_dtype, 2 * p, mn_lo);
@@ -271,12 +287,14 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
   const uint32_t cap2 = (uint32_t)P::bits((DT == DARTKV_BF16 ? 128.0f : 1024.0f) + qmax_lo) |
                         ((uint32_t)P::bits((DT == DARTKV_BF16 ? 128.0f : 1024.0f) + qmax_hi) << 16);
 
-  // pass 2: codes of (channel 2p, channel 2p+1) for one token per step, packed into one word per channel
+  // pass 2: codes of (channel 2p, channel 2p+1) for one token per step.  A plane's fields of both channels
+  // gather in one register (channel 2p in the low half, 2p+1 in the high half, 16/BITS tokens each); two such
+  // registers split into one 32-bit word per channel.
   constexpr int BITS = KBITS == 0 ? 2 : KBITS;      // bits per stored plane
   constexpr int CODE_BITS = KBITS == 0 ? 4 : KBITS; // bits the quantizer produces
-  constexpr int PER_WORD = 32 / BITS;               // tokens per 32-bit word of a plane
-  constexpr int WORDS = kP / PER_WORD;
-  constexpr uint32_t FIELD = (1u << BITS) - 1u;
+  constexpr int PER_HALF = 16 / BITS;               // tokens per 16-bit half of a plane word
+  constexpr int WORDS = kP / (2 * PER_HALF);        // 32-bit words per channel and plane
+  constexpr uint32_t FIELD2 = ((1u << BITS) - 1u) * 0x00010001u;
   uint32_t* low_lo = reinterpret_cast<uint32_t*>(page + (2 * p) * (WORDS * 4));
   uint32_t* low_hi = low_lo + WORDS;
   uint32_t* high_lo = (KBITS == 0 && slot_lo >= 0) ? reinterpret_cast<uint32_t*>(page + d.key_off_high + slot_lo * (WORDS * 4)) : nullptr;
@@ -286,28 +304,35 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
     uint32_t a_lo[4], a_hi[4], b_lo[4], b_hi[4];   // a: low plane, b: high plane
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      uint32_t la = 0, ha = 0, lb = 0, hb = 0;
-      const int base = (w4 + q) * PER_WORD;
+      uint32_t acc_a[2], acc_b[2];
 #pragma unroll
-      for (int u = 0; u < PER_WORD; ++u) {
-        const uint32_t x2 = col[(base + u) * 64];
-        const uint32_t a2 = P::sub(x2, mn2);
-        const float q_l = P::quotient(P::lo(a2), scale_lo, inv_lo), q_h = P::quotient(P::hi(a2), scale_hi, inv_hi);
-        uint32_t codes;
-        if (DT == DARTKV_BF16 && CODE_BITS == 8) {
-          const uint32_t r2 = P::pack(q_h, q_l);
-          codes = (uint32_t)fminf(rintf(P::lo(r2)), 255.0f) | ((uint32_t)fminf(rintf(P::hi(r2)), 255.0f) << 16);
-        } else {
-          codes = P::min2(P::add(P::pack(q_h, q_l), P::kMagic), cap2);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t fa = 0, fb = 0;
+        const int base = ((w4 + q) * 2 + half) * PER_HALF;
+#pragma unroll
+        for (int u = 0; u < PER_HALF; ++u) {
+          const uint32_t x2 = col[(base + u) * 64];
+          const uint32_t a2 = P::sub(x2, mn2);
+          const float q_l = P::quotient(P::lo(a2), scale_lo, inv_lo), q_h = P::quotient(P::hi(a2), scale_hi, inv_hi);
+          uint32_t codes;
+          if (DT == DARTKV_BF16 && CODE_BITS == 8) {
+            const uint32_t r2 = P::pack(q_h, q_l);
+            codes = (uint32_t)fminf(rintf(P::lo(r2)), 255.0f) | ((uint32_t)fminf(rintf(P::hi(r2)), 255.0f) << 16);
+          } else {
+            codes = P::min2(P::add(P::pack(q_h, q_l), P::kMagic), cap2);
+          }
+          fa += (codes & FIELD2) << (BITS * u);
+          if (KBITS == 0) fb += ((codes >> 2) & FIELD2) << (BITS * u);
         }
-        la |= (codes & FIELD) << (BITS * u);
-        ha |= ((codes >> 16) & FIELD) << (BITS * u);
-        if (KBITS == 0) {
-          lb |= ((codes >> 2) & FIELD) << (BITS * u);
-          hb |= ((codes >> 18) & FIELD) << (BITS * u);
-        }
+        acc_a[half] = fa;
+        acc_b[half] = fb;
       }
-      a_lo[q] = la; a_hi[q] = ha; b_lo[q] = lb; b_hi[q] = hb;
+      a_lo[q] = __byte_perm(acc_a[0], acc_a[1], 0x5410);
+      a_hi[q] = __byte_perm(acc_a[0], acc_a[1], 0x7632);
+      if (KBITS == 0) {
+        b_lo[q] = __byte_perm(acc_b[0], acc_b[1], 0x5410);
+        b_hi[q] = __byte_perm(acc_b[0], acc_b[1], 0x7632);
+      }
     }
     reinterpret_cast<uint4*>(low_lo)[w4 / 4] = make_uint4(a_lo[0], a_lo[1], a_lo[2], a_lo[3]);
     reinterpret_cast<uint4*>(low_hi)[w4 / 4] = make_uint4(a_hi[0], a_hi[1], a_hi[2], a_hi[3]);
@@ -320,79 +345,76 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
 }
 
 // Values: eight lanes per token row (16 channels per lane), four rows per warp per step, two steps in
-// flight.  VBITS in {2,4,8}; LPG = lanes per value group (value_group / 16).
+// flight; grid (64-row blocks of one (batch, head), batch*head).  VBITS in {2,4,8}; lanes_per_group =
+// value_group / 16.
 template <int DT, int VBITS>
 __global__ void __launch_bounds__(256) fast_value_rows_kernel(dartkv_cache_desc d, RowSource src, int value_begin,
                                                               int count, int lanes_per_group, int32_t* nonfinite) {
   using P = Pack16<DT>;
   constexpr int STEPS = 2;
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y, lane = threadIdx.x & 31;
   const int sub = lane >> 3, part = lane & 7;   // row within the step, 16-channel slice of the row
-  const uint32_t total = (uint32_t)d.batch * d.kv_heads * count;   // checked on the host to fit 32 bits
-  const uint32_t first = (uint32_t)warp * (4 * STEPS);
-  if (first >= total) return;
+  const int first = (blockIdx.x * 8 + (threadIdx.x >> 5)) * (4 * STEPS);
+  if (first >= count) return;
+  const uint16_t *chunk_base, *ring_base;
+  src.bases(bh, chunk_base, ring_base);
   uint4 raw[STEPS][2];
-  int bh_of[STEPS], t_of[STEPS];
+  int t_of[STEPS];
   bool live[STEPS];
 #pragma unroll
   for (int s = 0; s < STEPS; ++s) {
-    const uint32_t row = first + 4 * s + sub;
-    live[s] = row < total;
-    const uint32_t r = live[s] ? row : total - 1;
-    bh_of[s] = (int)(r / (uint32_t)count);
-    t_of[s] = value_begin + (int)(r % (uint32_t)count);
-    const uint4* ptr = reinterpret_cast<const uint4*>(src.row(bh_of[s], t_of[s]) + part * 16);
+    const int row = first + 4 * s + sub;
+    live[s] = row < count;
+    t_of[s] = value_begin + (live[s] ? row : count - 1);
+    const uint4* ptr = reinterpret_cast<const uint4*>(src.row_from(chunk_base, ring_base, t_of[s]) + part * 16);
     raw[s][0] = ptr[0];
     raw[s][1] = ptr[1];
   }
   constexpr float qmax = (float)((1 << VBITS) - 1);
   const uint32_t cap2 = cap_pair<DT>(qmax);
-  constexpr uint32_t kExpCarry = DT == DARTKV_BF16 ? 0x00800080u : 0x04000400u;
   bool bad = false;
 #pragma unroll
   for (int s = 0; s < STEPS; ++s) {
     const uint32_t x[8] = {raw[s][0].x, raw[s][0].y, raw[s][0].z, raw[s][0].w, raw[s][1].x, raw[s][1].y, raw[s][1].z, raw[s][1].w};
-    uint32_t mn2 = x[0], mx2 = x[0], exp_or = 0;
+    uint32_t mn2 = x[0], mx2 = x[0];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 1; i < 8; ++i) {
       mn2 = P::min2(mn2, x[i]);
       mx2 = P::max2(mx2, x[i]);
-      exp_or |= (x[i] & 0x7FFF7FFFu) + kExpCarry;
     }
-    bad |= live[s] && (exp_or & 0x80008000u) != 0;
     for (int off = 1; off < lanes_per_group; off <<= 1) {
       mn2 = P::min2(mn2, __shfl_xor_sync(0xffffffffu, mn2, off));
       mx2 = P::max2(mx2, __shfl_xor_sync(0xffffffffu, mx2, off));
     }
-    const float mn = fminf(P::lo(mn2), P::hi(mn2)), mx = fmaxf(P::lo(mx2), P::hi(mx2));
+    // NaN-propagating min / max: any Inf or NaN of the group ends up in mn or mx
+    const uint32_t mn1 = P::min2(mn2, mn2 >> 16), mx1 = P::max2(mx2, mx2 >> 16);
+    const float mn = P::lo(mn1), mx = P::lo(mx1);
+    bad |= live[s] && !(isfinite(mn) && isfinite(mx));
     const float scale = scale_of<DT>(mn, mx, qmax);
     const float inv = __frcp_rn(scale);
-    const uint32_t mnp = (uint32_t)P::bits(mn) * 0x00010001u;
-    uint32_t c[8];
+    const uint32_t mnp = (mn1 & 0xFFFFu) * 0x00010001u;
+    // codes of 16/(2*VBITS) pairs gather in one register (even channels in the low half, odd in the high half)
+    constexpr int PAIRS = 8 / VBITS;                      // pairs per gather register
+    constexpr int GATHERS = 8 / PAIRS;
+    constexpr uint32_t LOMASK = VBITS == 2 ? 0x3333u : VBITS == 4 ? 0x0F0Fu : 0x00FFu;
+    uint32_t half_word[GATHERS];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) c[i] = pair_codes<DT, VBITS>(x[i], mnp, scale, inv, cap2);
+    for (int g = 0; g < GATHERS; ++g) {
+      uint32_t acc = 0;
+#pragma unroll
+      for (int i = 0; i < PAIRS; ++i) acc += pair_codes<DT, VBITS>(x[g * PAIRS + i], mnp, scale, inv, cap2) << (2 * VBITS * i);
+      half_word[g] = (acc & LOMASK) | ((acc >> (16 - VBITS)) & (LOMASK << VBITS));
+    }
     if (!live[s]) continue;
-    const int64_t out_row = (int64_t)bh_of[s] * d.max_value_tokens + (t_of[s] - d.sink_tokens);
+    const int64_t out_row = (int64_t)bh * d.max_value_tokens + (t_of[s] - d.sink_tokens);
     uint8_t* codes = d.v_codes + out_row * d.value_row_bytes;
     if (VBITS == 2) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) word |= ((c[i] & 3u) | ((c[i] >> 14) & 0xCu)) << (4 * i);
-      reinterpret_cast<uint32_t*>(codes)[part] = word;
+      reinterpret_cast<uint32_t*>(codes)[part] = half_word[0] | (half_word[1] << 16);
     } else if (VBITS == 4) {
-      uint32_t w0 = 0, w1 = 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        w0 |= ((c[i] & 0xFu) | ((c[i] >> 12) & 0xF0u)) << (8 * i);
-        w1 |= ((c[i + 4] & 0xFu) | ((c[i + 4] >> 12) & 0xF0u)) << (8 * i);
-      }
-      reinterpret_cast<uint2*>(codes)[part] = make_uint2(w0, w1);
+      reinterpret_cast<uint2*>(codes)[part] = make_uint2(half_word[0] | (half_word[1] << 16), half_word[2] | (half_word[3] << 16));
     } else {
-      uint32_t w[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        w[i] = (c[2 * i] & 0xFFu) | ((c[2 * i] >> 8) & 0xFF00u) | ((c[2 * i + 1] & 0xFFu) << 16) | ((c[2 * i + 1] << 8) & 0xFF000000u);
-      reinterpret_cast<uint4*>(codes)[part] = make_uint4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<uint4*>(codes)[part] = make_uint4(half_word[0] | (half_word[1] << 16), half_word[2] | (half_word[3] << 16),
+                                                         half_word[4] | (half_word[5] << 16), half_word[6] | (half_word[7] << 16));
     }
     if ((part % lanes_per_group) == 0) {
       const int g = part / lanes_per_group;
@@ -441,9 +463,8 @@ template <int DT>
 static int launch_values(const dartkv_cache_desc& d, const dartkv_append_plan& p, const RowSource& src,
                          int32_t* nonfinite, cudaStream_t stream) {
   const int count = p.value_end - p.value_begin;
-  const int64_t rows = (int64_t)d.batch * d.kv_heads * count;
-  DARTKV_REQUIRE(rows < (1ll << 31), "too many value rows in one append (limit 2^31)");
-  const unsigned blocks = (unsigned)((rows + 63) / 64);   // 8 warps per block, 8 rows per warp
+  DARTKV_REQUIRE(d.batch * d.kv_heads <= 65535, "batch * kv_heads above 65535");
+  const dim3 blocks((unsigned)((count + 63) / 64), d.batch * d.kv_heads);   // 8 warps per block, 8 rows per warp
   const int lpg = d.value_group / 16;
   if (d.value_bits == 2)
     fast_value_rows_kernel<DT, 2><<<blocks, 256, 0, stream>>>(d, src, p.value_begin, count, lpg, nonfinite);

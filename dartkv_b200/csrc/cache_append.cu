@@ -57,27 +57,71 @@ struct TokenSource {
 };
 
 // ---------------------------------------------------------------------------- dense copies
-// grid (bh, chunk token, side); copies sink tokens into the sink rows and tail tokens into the ring.
+// ---------------------------------------------------------------------------- device-side metadata
+__device__ __forceinline__ void publish_append(const dartkv_cache_desc& d, const dartkv_append_plan& p) {
+  for (int pg = threadIdx.x; pg < p.num_pages; pg += blockDim.x) {
+    d.page_start[p.first_page + pg] = p.page_token_start + pg * d.page_size;
+    d.page_tokens[p.first_page + pg] = (pg == p.num_pages - 1) ? p.last_page_tokens : d.page_size;
+  }
+  if (threadIdx.x == 0) {
+    d.state[0] = p.seen_after;
+    d.state[1] = p.key_pages_after;
+    d.state[2] = p.k_packed_end_after;
+    d.state[3] = p.v_packed_end_after;
+    d.state[4] = min(p.seen_after, d.sink_tokens);
+  }
+}
+
+// true when a 16-byte piece of `dt` elements holds an Inf or NaN
+__device__ __forceinline__ bool piece_nonfinite(uint4 v, int dt) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t flag = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (dt == DARTKV_F32) flag |= ((w[i] & 0x7FFFFFFFu) + 0x00800000u) & 0x80000000u;
+    else flag |= ((w[i] & 0x7FFF7FFFu) + (dt == DARTKV_BF16 ? 0x00800080u : 0x04000400u)) & 0x80008000u;
+  }
+  return flag != 0;
+}
+
+constexpr int kCopyRows = 8;   // rows per block of the dense copy
+
+// grid (bh, blocks of kCopyRows copy rows, side): copies sink tokens into the sink rows and tail tokens into
+// the ring; copy row r enumerates only the chunk tokens that can need a copy: the sink part, then
+// [ring_first, chunk end).  Block (0,0,0) also publishes the page table rows and the state words of the step
+// (nothing of this step reads them; later launches on the stream do).
 __global__ void copy_dense_kernel(dartkv_cache_desc d, dartkv_append_plan p, const void* keys, const void* values,
-                                  int64_t sb, int64_t sh, int64_t st, int ring_first, int32_t* nonfinite) {
-  // blockIdx.y enumerates only the chunk tokens that can need a copy: the sink part, then [ring_first, chunk end)
-  int bh = blockIdx.x, side = blockIdx.z;
-  int j = (int)blockIdx.y < p.sink_copy ? (int)blockIdx.y : ring_first + ((int)blockIdx.y - p.sink_copy);
-  int t = p.chunk_start + j;
-  int ring_begin = side == 0 ? p.ring_begin : p.value_end;  // values not packed by this step stay dense
-  const bool to_sink = j < p.sink_copy;
-  const bool to_ring = t >= ring_begin && !to_sink;
-  if (!to_sink && !to_ring) return;
+                                  int64_t sb, int64_t sh, int64_t st, int ring_first, int rows, int vector_ok,
+                                  int32_t* nonfinite) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) publish_append(d, p);
+  const int bh = blockIdx.x, side = blockIdx.z;
+  const int r_begin = blockIdx.y * kCopyRows, r_end = min(rows, r_begin + kCopyRows);
+  if (r_begin >= r_end) return;
+  const int ring_begin = side == 0 ? p.ring_begin : p.value_end;  // values not packed by this step stay dense
   const void* src = side == 0 ? keys : values;
-  void* dst = to_sink ? (side == 0 ? d.k_sink : d.v_sink) : (side == 0 ? d.k_ring : d.v_ring);
-  int64_t drow = to_sink ? ((int64_t)bh * d.sink_tokens + t) : ((int64_t)bh * d.ring_tokens + (t % d.ring_tokens));
-  int b = bh / d.kv_heads, h = bh % d.kv_heads;
-  int64_t sbase = (int64_t)b * sb + (int64_t)h * sh + (int64_t)j * st;
+  const int b = bh / d.kv_heads, h = bh % d.kv_heads;
+  const int64_t src_base = (int64_t)b * sb + (int64_t)h * sh;
+  const int esize = dartkv_dtype_size(d.dtype);
+  const int pieces = vector_ok ? d.head_dim * esize / 16 : d.head_dim;   // units per row: 16-byte pieces or elements
   bool bad = false;
-  for (int c = threadIdx.x; c < d.head_dim; c += blockDim.x) {
-    float v = load_f(src, d.dtype, sbase + c);
-    bad |= !isfinite(v);
-    store_f(dst, d.dtype, drow * d.head_dim + c, v);
+  for (int i = threadIdx.x; i < (r_end - r_begin) * pieces; i += blockDim.x) {
+    const int r = r_begin + i / pieces, c = i % pieces;
+    const int j = r < p.sink_copy ? r : ring_first + (r - p.sink_copy);
+    const int t = p.chunk_start + j;
+    const bool to_sink = j < p.sink_copy;
+    if (!to_sink && t < ring_begin) continue;
+    void* dst = to_sink ? (side == 0 ? d.k_sink : d.v_sink) : (side == 0 ? d.k_ring : d.v_ring);
+    const int64_t drow = to_sink ? ((int64_t)bh * d.sink_tokens + t) : ((int64_t)bh * d.ring_tokens + (t % d.ring_tokens));
+    const int64_t srow = src_base + (int64_t)j * st;
+    if (vector_ok) {
+      const uint4 v = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(src) + srow * esize)[c];
+      bad |= piece_nonfinite(v, d.dtype);
+      reinterpret_cast<uint4*>(reinterpret_cast<char*>(dst) + drow * d.head_dim * esize)[c] = v;
+    } else {
+      const float v = load_f(src, d.dtype, srow + c);
+      bad |= !isfinite(v);
+      store_f(dst, d.dtype, drow * d.head_dim + c, v);
+    }
   }
   if (bad && nonfinite) *nonfinite = 1;
 }
@@ -252,21 +296,6 @@ __global__ void value_rows_kernel(dartkv_cache_desc d, TokenSource src, int valu
   }
   if (filled) *out = (uint8_t)acc;
   if (bad && nonfinite) *nonfinite = 1;
-}
-
-// ---------------------------------------------------------------------------- device-side metadata
-__global__ void finalize_append_kernel(dartkv_cache_desc d, dartkv_append_plan p) {
-  for (int pg = threadIdx.x; pg < p.num_pages; pg += blockDim.x) {
-    d.page_start[p.first_page + pg] = p.page_token_start + pg * d.page_size;
-    d.page_tokens[p.first_page + pg] = (pg == p.num_pages - 1) ? p.last_page_tokens : d.page_size;
-  }
-  if (threadIdx.x == 0) {
-    d.state[0] = p.seen_after;
-    d.state[1] = p.key_pages_after;
-    d.state[2] = p.k_packed_end_after;
-    d.state[3] = p.v_packed_end_after;
-    d.state[4] = min(p.seen_after, d.sink_tokens);
-  }
 }
 
 // ---------------------------------------------------------------------------- element access
@@ -461,15 +490,22 @@ extern "C" int dartkv_cache_append(const dartkv_cache_desc* desc, const dartkv_a
       DARTKV_LAUNCH_OK("value_rows_kernel");
     }
   }
-  if (copies) {
-    DARTKV_REQUIRE(p.chunk_tokens <= 65535, "append chunks longer than 65535 tokens must be split by the caller");
-    const int ring_first = max(p.sink_copy, min(p.ring_begin, max(p.value_end, p.chunk_start)) - p.chunk_start);
-    const int rows = p.sink_copy + (p.chunk_tokens - ring_first);
-    copy_dense_kernel<<<dim3(bh, rows, 2), 128, 0, stream>>>(d, p, keys, values, stride_b, stride_h, stride_t, ring_first, nonfinite);
+  {
+    // dense copies of the step (possibly none) and the step's metadata, one launch
+    int ring_first = p.chunk_tokens, rows = 0;
+    if (copies) {
+      ring_first = max(p.sink_copy, min(p.ring_begin, max(p.value_end, p.chunk_start)) - p.chunk_start);
+      rows = p.sink_copy + (p.chunk_tokens - ring_first);
+    }
+    const int row_blocks = max(1, ceil_div(rows, kCopyRows));
+    DARTKV_REQUIRE(row_blocks <= 65535, "append chunks this long must be split by the caller");
+    const int esize = dartkv_dtype_size(d.dtype);
+    const int vector_ok = (d.head_dim * esize) % 16 == 0 && (stride_b * esize) % 16 == 0 && (stride_h * esize) % 16 == 0 &&
+                          (stride_t * esize) % 16 == 0 && ((uintptr_t)keys | (uintptr_t)values) % 16 == 0;
+    copy_dense_kernel<<<dim3(rows > 0 ? bh : 1, row_blocks, rows > 0 ? 2 : 1), 128, 0, stream>>>(
+        d, p, keys, values, stride_b, stride_h, stride_t, ring_first, rows, vector_ok, nonfinite);
     DARTKV_LAUNCH_OK("copy_dense_kernel");
   }
-  finalize_append_kernel<<<1, 128, 0, stream>>>(d, p);
-  DARTKV_LAUNCH_OK("finalize_append_kernel");
   return DARTKV_OK;
 }
 

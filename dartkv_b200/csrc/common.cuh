@@ -40,6 +40,7 @@ void dartkv_count_launch();
   } while (0)
 
 static inline bool dartkv_valid_dtype(int dt) { return dt == DARTKV_F32 || dt == DARTKV_F16 || dt == DARTKV_BF16; }
+__host__ __device__ __forceinline__ int dartkv_dtype_size(int dt) { return dt == DARTKV_F32 ? 4 : 2; }
 static inline int dartkv_dtype_bytes(int dt) { return dt == DARTKV_F32 ? 4 : 2; }
 static inline bool dartkv_valid_bits(int bits) { return bits == 2 || bits == 4 || bits == 8; }
 
