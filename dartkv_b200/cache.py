@@ -20,7 +20,7 @@ from typing import TYPE_CHECKING, List, Optional, Tuple, Union
 import torch
 
 from . import _lib
-from ._lib import LIB, AppendPlan, CacheDesc, check, ptr, require_cuda, stream_ptr
+from ._lib import LIB, AppendPlan, CacheDesc, check, ptr, require_cuda, stream_ptr, device_guard
 from .lifecycle import (LifecycleState, key_segment_list, plan_append, regular_pages, ring_rows, segment_table,
                         value_segment_list)
 from .mixed import MixedQuantizedKey, promoted_count
@@ -50,6 +50,9 @@ class DartPageMetadata:
     token_count: int
     key: DartSegmentLayout
     value: DartSegmentLayout
+
+
+_PLAN_FIELDS = tuple(name for name, _ in AppendPlan._fields_ if name != "reserved")
 
 
 @dataclass(frozen=True)
@@ -143,6 +146,7 @@ class DartKVCache:
         self._page_table_cache: dict = {}
         self._page_run_cache: dict = {}
         self._forced_indices: Optional[torch.Tensor] = None
+        self._plan = AppendPlan()
 
     # ------------------------------------------------------------------ simple accessors
     @property
@@ -197,7 +201,7 @@ class DartKVCache:
         d.max_value_tokens = 1
         check(LIB.dartkv_cache_geometry(ctypes.byref(d)))
         self._desc = d
-        with torch.cuda.device(device):
+        with device_guard(device):
             self._pools = {
                 "k_sink": torch.empty((batch, heads, max(1, cfg.sink_tokens), head_dim), dtype=dtype, device=device),
                 "v_sink": torch.empty((batch, heads, max(1, cfg.sink_tokens), head_dim), dtype=dtype, device=device),
@@ -215,7 +219,7 @@ class DartKVCache:
         cfg, d, device = self.config, self._desc, self._device
         b, h = d.batch, d.kv_heads
         old = self._pools
-        with torch.cuda.device(device):
+        with device_guard(device):
             if "k_pages" not in old or need_pages > d.max_key_pages:
                 pages = max(1, need_pages)
                 k_pages = torch.empty((b, h, pages, d.key_page_bytes), dtype=torch.uint8, device=device)
@@ -284,7 +288,9 @@ class DartKVCache:
             # pools grow by doubling; the old contents are copied on the current stream
             self._ensure_capacity(2 * len(life.pages) if len(life.pages) > d.max_key_pages else d.max_key_pages,
                                   2 * rows_needed if rows_needed > d.max_value_tokens else d.max_value_tokens)
-        plan = AppendPlan(**{name: getattr(fields, name) for name, _ in AppendPlan._fields_ if name != "reserved"})
+        plan = self._plan
+        for name in _PLAN_FIELDS:
+            setattr(plan, name, getattr(fields, name))
         idx = None
         if channel_indices is not None and d.promoted:
             expected = fields.num_pages + fields.requantize_last_page
@@ -294,7 +300,7 @@ class DartKVCache:
             if fields.requantize_last_page:
                 idx = torch.cat((idx[:, :1].reshape(-1), idx[:, 1:].reshape(-1)))
             idx = idx.contiguous()
-        with torch.cuda.device(device):
+        with device_guard(device):
             check(LIB.dartkv_cache_append(
                 ctypes.byref(d), ctypes.byref(plan), ptr(keys), ptr(values), keys.stride(0), keys.stride(1),
                 keys.stride(2), ptr(idx), ptr(self._pools["nonfinite"]), stream_ptr(device)))
@@ -342,7 +348,7 @@ class DartKVCache:
     def _materialize(self, side: int, start: int, stop: int, flavour: int = _lib.DEQUANT_PER_OP) -> torch.Tensor:
         b, h, d = self._shape
         out = torch.empty((b, h, stop - start, d), dtype=self._dtype, device=self._device)
-        with torch.cuda.device(self._device):
+        with device_guard(self._device):
             for lo in range(start, stop, 32768):
                 hi = min(stop, lo + 32768)
                 piece = out if (lo == start and hi == stop) else torch.empty(
@@ -617,7 +623,7 @@ class DartKVCache:
         key = (query_heads, capacity)
         if self._workspace is None or self._workspace[0] != key:
             nbytes = LIB.dartkv_decode_workspace_bytes(ctypes.byref(d), query_heads, capacity)
-            with torch.cuda.device(self._device):
+            with device_guard(self._device):
                 buf = torch.zeros(max(16, nbytes), dtype=torch.uint8, device=self._device)
             self._workspace = (key, buf)
         return self._workspace[1], capacity
@@ -628,7 +634,7 @@ class DartKVCache:
         if self._workspace is None:
             return 0
         status = ctypes.c_int(0)
-        with torch.cuda.device(self._device):
+        with device_guard(self._device):
             check(LIB.dartkv_decode_status(ptr(self._workspace[1]), ctypes.byref(status), stream_ptr(self._device)))
         return status.value
 

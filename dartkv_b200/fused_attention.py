@@ -14,7 +14,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import LIB, check, ptr, require_cuda, stream_ptr
+from ._lib import LIB, check, ptr, require_cuda, stream_ptr, device_guard
 from .cache import DartKVCache
 from .page_table import DartPageRun, DartPageTable
 
@@ -40,7 +40,7 @@ def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional
         out = torch.empty_like(q)
     factor = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     workspace, capacity = cache.decode_workspace(q.shape[1])
-    with torch.cuda.device(device):
+    with device_guard(device):
         check(LIB.dartkv_decode_attention(
             ctypes.byref(cache.descriptor), ptr(q), _lib.DTYPE_CODE[q.dtype], q.shape[1], float(factor), flavour,
             seen, ptr(workspace), workspace.numel(), ptr(out), stream_ptr(device)))

@@ -16,7 +16,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import LIB, check, ptr, require_cuda, stream_ptr
+from ._lib import LIB, check, ptr, require_cuda, stream_ptr, device_guard
 
 
 @dataclass
@@ -83,7 +83,7 @@ class MixedQuantizedKey:
         idx = self.channel_indices.to(torch.int32).contiguous()
         scale = self.scale.contiguous()
         zero = self.zero_point.contiguous()
-        with torch.cuda.device(device):
+        with device_guard(device):
             check(LIB.dartkv_dequantize_key_mixed(
                 ptr(low), ptr(high) if self.promoted_channels else 0, ptr(idx) if self.promoted_channels else 0,
                 ptr(scale), ptr(zero), _lib.DTYPE_CODE[scale.dtype], b * h, t, d, self.group_size,
@@ -116,7 +116,7 @@ def channel_scores(key_states: torch.Tensor, *, strategy: str = "magnitude") -> 
     keys = key_states.detach().contiguous()
     b, h, t, d = keys.shape
     scores = torch.empty((b, h, d), dtype=keys.dtype, device=device)
-    with torch.cuda.device(device):
+    with device_guard(device):
         check(LIB.dartkv_channel_scores(
             ptr(keys), _lib.DTYPE_CODE[keys.dtype], b * h, t, d, t * d, d,
             _lib.SCORE_MAGNITUDE if strategy == "magnitude" else _lib.SCORE_VARIANCE, ptr(scores), stream_ptr(device)))
@@ -158,7 +158,7 @@ def select_key_channels(
         return mask, indices
     scores = channel_scores(key_states, strategy=strategy)
     idx32 = torch.empty((batch, heads, count), dtype=torch.int32, device=device)
-    with torch.cuda.device(device):
+    with device_guard(device):
         check(LIB.dartkv_select_channels(ptr(scores), _lib.DTYPE_CODE[scores.dtype], batch * heads, head_dim, count,
                                          ptr(idx32), stream_ptr(device)))
     indices = idx32.long()
@@ -212,7 +212,7 @@ def quantize_key_mixed(
     scale = torch.empty((batch, heads, head_dim, groups), dtype=meta_dtype, device=device)
     zero = torch.empty_like(scale)
     flag = torch.zeros(1, dtype=torch.int32, device=device) if check_finite else None
-    with torch.cuda.device(device):
+    with device_guard(device):
         check(LIB.dartkv_quantize_key_mixed(
             ptr(keys), _lib.DTYPE_CODE[keys.dtype], batch * heads, tokens, head_dim, tokens * head_dim, head_dim,
             group_size, ptr(idx32) if promoted else 0, promoted, _lib.DTYPE_CODE[meta_dtype], ptr(low),

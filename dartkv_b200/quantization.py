@@ -13,7 +13,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import LIB, check, ptr, require_cuda, stream_ptr
+from ._lib import LIB, check, ptr, require_cuda, stream_ptr, device_guard
 
 _SUPPORTED_BITS = (2, 4, 8)
 
@@ -55,11 +55,11 @@ def _pack(values: torch.Tensor, bits: int, packed_dim: int) -> torch.Tensor:
         out.zero_()
         view = out.reshape(-1, packed_dim // vpb)[:, : (n + vpb - 1) // vpb]
         tmp = torch.empty((flat.shape[0], (n + vpb - 1) // vpb), dtype=torch.uint8, device=device)
-        with torch.cuda.device(device):
+        with device_guard(device):
             check(LIB.dartkv_pack(ptr(flat), flat.shape[0], n, bits, ptr(tmp), stream_ptr(device)))
         view.copy_(tmp)
         return out
-    with torch.cuda.device(device):
+    with device_guard(device):
         check(LIB.dartkv_pack(ptr(flat), flat.shape[0], n, bits, ptr(out), stream_ptr(device)))
     return out
 
@@ -71,7 +71,7 @@ def _unpack(packed: torch.Tensor, bits: int, packed_dim: int) -> torch.Tensor:
     device = require_cuda(packed)
     flat = packed.contiguous().reshape(-1, packed.shape[-1])
     out = torch.empty((*packed.shape[:-1], packed_dim), dtype=torch.uint8, device=device)
-    with torch.cuda.device(device):
+    with device_guard(device):
         check(LIB.dartkv_unpack(ptr(flat), flat.shape[0], flat.shape[1], bits, packed_dim, ptr(out), stream_ptr(device)))
     return out
 
@@ -132,7 +132,7 @@ class QuantizedTensor:
         values = self.values.contiguous()
         scale = self.scale.contiguous()
         zero = self.zero_point.contiguous()
-        with torch.cuda.device(device):
+        with device_guard(device):
             check(LIB.dartkv_dequantize(
                 ptr(values), ptr(scale), ptr(zero), _lib.DTYPE_CODE[scale.dtype], outer, n, inner, self.bits,
                 self.group_size, flavour, ptr(out), _lib.DTYPE_CODE[out_dtype], n * inner, inner, 1,
@@ -199,7 +199,7 @@ def quantize(
     scale = torch.empty((*moved_shape, groups), dtype=meta_dtype, device=device)
     zero = torch.empty((*moved_shape, groups), dtype=meta_dtype, device=device)
     flag = torch.zeros(1, dtype=torch.int32, device=device) if check_finite else None
-    with torch.cuda.device(device):
+    with device_guard(device):
         check(LIB.dartkv_quantize(
             ptr(data), _lib.DTYPE_CODE[data.dtype], outer, n, inner, n * inner, inner, 1, bits, group_size,
             _lib.DTYPE_CODE[meta_dtype], _lib.DIV_TRUE if division == "true" else _lib.DIV_RECIPROCAL,
