@@ -272,8 +272,10 @@ def gpu_arm(args, wl) -> None:
     gathered = torch.empty((world * local_batch, hq, d), dtype=torch.bfloat16, device=device) if world > 1 else None
     q3 = query[:, :, 0].contiguous()
 
+    flavour = _lib.DEQUANT_FUSED if args.flavour == "fused" else _lib.DEQUANT_PER_OP
+
     def step():
-        dart.decode_attention(q3, cache, out=out)
+        dart.decode_attention(q3, cache, out=out, flavour=flavour)
         if world > 1:
             dist.all_gather_into_tensor(gathered, out)  # the only cross-GPU traffic: final output gather
 
@@ -313,7 +315,7 @@ def gpu_arm(args, wl) -> None:
     barrier()
     start_evt.record()
     for _ in range(args.steps):
-        dart.decode_attention(q3, cache, out=out)
+        dart.decode_attention(q3, cache, out=out, flavour=flavour)
     stop_evt.record()
     torch.cuda.synchronize(device)
     kernel_ms = start_evt.elapsed_time(stop_evt) / args.steps
@@ -332,7 +334,7 @@ def gpu_arm(args, wl) -> None:
 
     def e2e_step():
         dev_q.copy_(host_q, non_blocking=True)
-        dart.decode_attention(dev_q, cache, out=out)
+        dart.decode_attention(dev_q, cache, out=out, flavour=flavour)
         if world > 1:
             dist.all_gather_into_tensor(gathered, out)
             host_out.copy_(gathered[rank * local_batch:(rank + 1) * local_batch], non_blocking=True)
@@ -357,6 +359,22 @@ def gpu_arm(args, wl) -> None:
     extra = {}
     if rank == 0 and world == 1 and not args.skip_extras:
         del gathered
+        if args.flavour == "per_op":
+            # the same call with the arithmetic of the reference's Triton kernels (dequantized values never rounded)
+            for _ in range(3):
+                dart.decode_attention(q3, cache, out=out, flavour=_lib.DEQUANT_FUSED)
+            torch.cuda.synchronize(device)
+            start_evt.record()
+            for _ in range(args.steps):
+                dart.decode_attention(q3, cache, out=out, flavour=_lib.DEQUANT_FUSED)
+            stop_evt.record()
+            torch.cuda.synchronize(device)
+            fused_ms = start_evt.elapsed_time(stop_evt) / args.steps
+            fused_gbs = local_bytes / (fused_ms * 1e-3) / 1e9
+            extra["unrounded_fp32_variant"] = {
+                "value": fused_gbs, "unit": "GB/s", "us_per_launch": fused_ms * 1e3, "frac": fused_gbs / peak,
+                "note": "flavour DEQUANT_FUSED: code*scale+zero kept in fp32 like the reference's Triton kernels; "
+                        "not the pinned oracle's arithmetic, so it is reported beside the headline, not as it"}
         extra["append"] = append_microbench(device, steps=3, warmup=1)
         rows = 1
         step_s, append_s = cpu_oracle_decode(wl["ctx"], wl["seed"], rows, 1)
@@ -375,6 +393,8 @@ def gpu_arm(args, wl) -> None:
                        "query_heads": hq, "kv_heads": GEOM["kv_heads"], "head_dim": d, "page": GEOM["page"],
                        "bits": "2-bit + 0.25 promotion", "key_group": GEOM["key_group"], "value_group": GEOM["value_group"],
                        "sinks": GEOM["sinks"], "metadata": "bf16", "bytes_per_step": total_bytes,
+                       "dequant": "per-op rounded (reference streamed path)" if args.flavour == "per_op"
+                       else "unrounded fp32 (reference Triton kernels)",
                        "l2": f"per-GPU working set {local_bytes / 1e6:.0f} MB exceeds the 126 MB L2",
                        "parallelism": f"batch sharded over {world} GPU(s), output all-gather only"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -492,6 +512,8 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["config4"], default="config5")
     parser.add_argument("--skip-extras", action="store_true", help="skip the append microbench and the CPU baseline")
+    parser.add_argument("--flavour", choices=("per_op", "fused"), default="per_op",
+                        help="dequantization arithmetic of the timed decode call (default: the pinned per-op rounding)")
     args = parser.parse_args()
     if args.workload == "config4":
         if args.impl == "reference":

@@ -4,6 +4,7 @@ The public names are the reference package's (``src/dart/__init__.py:11-34``), s
 against ``dart`` runs against this package by changing the import.
 """
 
+from ._lib import DEQUANT_FP32, DEQUANT_FUSED, DEQUANT_PER_OP
 from .cache import DartKVCache, DartKVCacheConfig, DartPageMetadata, DartSegmentLayout
 from .attention import dense_attention, streamed_dart_attention
 from .fused_attention import decode_attention, fused_dart_attention
@@ -20,6 +21,9 @@ __all__ = [
     "dense_attention",
     "fused_dart_attention",
     "decode_attention",
+    "DEQUANT_PER_OP",
+    "DEQUANT_FP32",
+    "DEQUANT_FUSED",
     "DENSE_PAGE",
     "MIXED_PAGE",
     "QUANTIZED_PAGE",

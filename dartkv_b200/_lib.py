@@ -17,7 +17,7 @@ from .build import LIB_PATH
 F32, F16, BF16 = 0, 1, 2
 DENSE_PAGE, QUANTIZED_PAGE, MIXED_PAGE = 0, 1, 2
 DIV_TRUE, DIV_RECIPROCAL = 0, 1
-DEQUANT_PER_OP, DEQUANT_FP32 = 0, 1
+DEQUANT_PER_OP, DEQUANT_FP32, DEQUANT_FUSED = 0, 1, 2
 SCORE_MAGNITUDE, SCORE_VARIANCE = 0, 1
 
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}

@@ -95,6 +95,7 @@ __device__ __forceinline__ uint32_t group_code(float x, float mn, float scale, f
 // dequantized element in the output dtype, as float
 __device__ __forceinline__ float affine_restore(float code, float scale, float zero, int md, int out_dt, int flavour) {
   float v;
+  if (flavour == DARTKV_DEQUANT_FUSED) return __fmaf_rn(code, scale, zero);   // attention-only: nothing is rounded
   if (flavour == DARTKV_DEQUANT_FP32) {
     v = __fmaf_rn(code, scale, zero);
   } else {

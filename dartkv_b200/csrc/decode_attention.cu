@@ -235,7 +235,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_m, const floa
 // ---------------------------------------------------------------------------- host side
 struct DecodeLayout {
   int generic_splits, generic_chunk;   // generic kernel over the whole range (fallback)
-  int fast;                            // 1: tensor-core kernel handles the packed pages
+  int fast;                            // tensor-core kernel for the packed pages: 1 per-op rounded, 2 unrounded fp32
   int fast_splits, fast_pages_per_split;
   int total_splits;
 };
@@ -244,6 +244,10 @@ int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int qu
 int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
                               int flavour, int splits, int pages_per_split, int split_base, int total_splits,
                               float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream);
+int dartkv_decode_fused32_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
+int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
+                                 int flavour, int splits, int pages_per_split, int split_base, int total_splits,
+                                 float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream);
 
 static int dartkv_sm_count() {
   static int cached = 0;
@@ -262,7 +266,9 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
   DecodeLayout L{};
   const int bh = d->batch * d->kv_heads;
   const int target_blocks = 148 * 8;   // two resident blocks per SM, about four waves
-  L.fast = flavour == DARTKV_DEQUANT_PER_OP && dartkv_decode_fast_supported(d, q_dtype, query_heads);
+  L.fast = 0;
+  if (flavour == DARTKV_DEQUANT_PER_OP && dartkv_decode_fast_supported(d, q_dtype, query_heads)) L.fast = 1;
+  if (flavour == DARTKV_DEQUANT_FUSED && dartkv_decode_fused32_supported(d, q_dtype, query_heads)) L.fast = 2;
   if (L.fast) {
     // A block hands its pages to four warp pairs round-robin, two blocks are resident per SM.  Pick the
     // pages per block (a multiple of four, at most 16 blocks per (batch, kv head)) that minimizes
@@ -305,7 +311,7 @@ extern "C" int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* d, int
   // the split count is non-decreasing in the token count for both layouts
   int64_t best = 0;
   for (int dt = 0; dt < 3; ++dt)
-    for (int flavour = 0; flavour < 2; ++flavour) {
+    for (int flavour = 0; flavour < 3; ++flavour) {
       DecodeLayout L = decode_layout(d, dt, query_heads, flavour, max_tokens);
       // the tensor-core layout uses at most 16 page splits + 1 dense block whatever the token count
       if (L.fast) L.total_splits = 17;
@@ -329,7 +335,7 @@ extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* q
   DARTKV_REQUIRE(dartkv_valid_dtype(q_dtype), "query must be f32, f16 or bf16");
   DARTKV_REQUIRE(query_heads > 0 && query_heads % d->kv_heads == 0, "query heads must be divisible by cache KV heads");
   DARTKV_REQUIRE(tokens > 0, "cache is empty");
-  DARTKV_REQUIRE(flavour == DARTKV_DEQUANT_PER_OP || flavour == DARTKV_DEQUANT_FP32, "unknown dequant flavour %d", flavour);
+  DARTKV_REQUIRE(flavour >= DARTKV_DEQUANT_PER_OP && flavour <= DARTKV_DEQUANT_FUSED, "unknown dequant flavour %d", flavour);
   const int rep = query_heads / d->kv_heads;
   DARTKV_REQUIRE(rep <= GEN_MAX_REP, "at most %d query heads per KV head are supported", GEN_MAX_REP);
   DARTKV_REQUIRE(d->head_dim <= GEN_MAX_D, "decode attention supports head_dim up to %d", GEN_MAX_D);
@@ -345,8 +351,9 @@ extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* q
   const int bh = d->batch * d->kv_heads;
   const int D = d->head_dim;
   if (L.fast) {
-    int rc = dartkv_decode_fast_launch(d, query, q_dtype, query_heads, scale, flavour, L.fast_splits,
-                                       L.fast_pages_per_split, 0, L.total_splits, part_m, part_l, part_acc, status, stream);
+    int rc = (L.fast == 2 ? dartkv_decode_fused32_launch : dartkv_decode_fast_launch)(
+        d, query, q_dtype, query_heads, scale, flavour, L.fast_splits, L.fast_pages_per_split, 0, L.total_splits, part_m,
+        part_l, part_acc, status, stream);
     if (rc) return rc;
   } else {
     size_t smem = ((size_t)rep * D + (size_t)GEN_TILE * (D + 1) + (size_t)rep * GEN_TILE + 3 * rep) * sizeof(float) +
@@ -407,7 +414,7 @@ extern "C" int dartkv_decode_attention_builtin_scratch(const dartkv_cache_desc* 
   DARTKV_REQUIRE(dartkv_valid_dtype(q_dtype), "query must be f32, f16 or bf16");
   DARTKV_REQUIRE(query_heads > 0 && query_heads % d->kv_heads == 0, "query heads must be divisible by cache KV heads");
   DARTKV_REQUIRE(tokens > 0, "cache is empty");
-  DARTKV_REQUIRE(flavour == DARTKV_DEQUANT_PER_OP || flavour == DARTKV_DEQUANT_FP32, "unknown dequant flavour %d", flavour);
+  DARTKV_REQUIRE(flavour >= DARTKV_DEQUANT_PER_OP && flavour <= DARTKV_DEQUANT_FUSED, "unknown dequant flavour %d", flavour);
   const DecodeLayout L = decode_layout(d, q_dtype, query_heads, flavour, tokens);
   const int64_t need = layout_bytes(d, query_heads, L);
   if (need > DARTKV_BUILTIN_SCRATCH_BYTES) {

@@ -1,0 +1,226 @@
+// Pieces shared by the tensor-core decode kernels (decode_fast.cu: per-op rounded dequantization;
+// decode_fused32.cu: unrounded fp32 dequantization): block geometry, the staged page layout, the block
+// that handles dense tokens, and the block-level merge of the warps' online-softmax states.
+#pragma once
+
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+namespace {
+
+constexpr int kPairs = 4;
+constexpr int kWarps = 2 * kPairs;
+constexpr int kThreads = kWarps * 32;
+constexpr int kPageBytesK = 5760;
+constexpr int kValueCodes = 4096;
+constexpr int kStageBytes = 10880;            // key blob (<= 5760) | value codes 4096 | value metadata (<= 1024)
+constexpr int kOffVCodes = kPageBytesK;       // 5760
+constexpr int kOffVMeta = kPageBytesK + kValueCodes;  // 9856
+constexpr int kPStride = 72;                  // 16-bit elements per (plane, head) row of a warp's probability tile
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ void pair_barrier(int pair) {
+  asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
+}
+
+struct FastArgs {
+  const void* q;
+  int query_heads;
+  float scale;
+  int flavour;
+  int splits, pages_per_split, split_base, total_splits;
+  float* part_m;
+  float* part_l;
+  float* part_acc;
+  int* status;
+};
+
+__host__ __device__ __forceinline__ int fast_range_end(int sink_tokens, int page_size, int k_end, int v_end,
+                                                       int sink_filled) {
+  int packed = min(k_end, v_end);
+  if (packed <= sink_tokens) return sink_filled;
+  return sink_tokens + (packed - sink_tokens) / page_size * page_size;
+}
+
+template <int DT>
+__device__ __forceinline__ float rnd16(float x) { return Half2Ops<DT>::to_float(Half2Ops<DT>::from_float(x)); }
+
+// ------------------------------------------------------------------------------------------------
+// dense tokens (sink prefix, unpacked tail, and tokens packed on one side only): one warp per token,
+// four channels per lane, fp32 math
+// BS: the kernel's block-level shared struct (needs slot_map[128], merge_m / merge_l [kWarps][4])
+template <int DT, class BS>
+__device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& bs, float* warp_out, int bh) {
+  using H = Half2Ops<DT>;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rep = a.query_heads / d.kv_heads;
+  const int seen = d.state[0], pages = d.state[1], k_end = d.state[2], v_end = d.state[3], sink_filled = d.state[4];
+  const int fast_end = fast_range_end(d.sink_tokens, d.page_size, k_end, v_end, sink_filled);
+  const int b = bh / d.kv_heads, h = bh % d.kv_heads;
+  float q[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      q[r][i] = r < rep ? load_f(a.q, d.dtype, ((int64_t)b * a.query_heads + h * rep + r) * 128 + lane * 4 + i) : 0.0f;
+  float m[4], l[4], acc[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[r][i] = 0.0f;
+  }
+  const float scale2 = a.scale * kLog2e;
+  const bool fused = a.flavour == DARTKV_DEQUANT_FUSED;
+  // segments: [0, sink_filled) then [fast_end, seen) cut at key page boundaries
+  int t = 0;
+  while (t < seen) {
+    if (t >= sink_filled && t < fast_end) { t = fast_end; continue; }
+    int seg_end, kind;
+    const uint8_t* page = nullptr;
+    int page_first = 0;
+    if (t < sink_filled) { kind = 0; seg_end = sink_filled; }
+    else if (t < k_end) {
+      kind = 1;
+      int pg = (t - d.sink_tokens) / d.page_size;   // pages are regular on this path
+      page_first = d.sink_tokens + pg * d.page_size;
+      seg_end = min(seen, page_first + d.page_size);
+      page = d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes;
+      __syncthreads();
+      if (tid < 128) bs.slot_map[tid] = -1;
+      __syncthreads();
+      if (d.key_mode == DARTKV_MIXED_PAGE && tid < d.promoted) {
+        int ch = reinterpret_cast<const int32_t*>(page + d.key_off_index)[tid];
+        if (ch >= 0 && ch < 128) bs.slot_map[ch] = tid;
+      }
+      __syncthreads();
+    } else { kind = 2; seg_end = seen; }
+    (void)pages;
+    // dense rows of the next token are requested before the current one is consumed
+    auto dense_row = [&](const void* sink, const void* ring, int tok) -> uint2 {
+      const uint16_t* row = tok < sink_filled
+          ? reinterpret_cast<const uint16_t*>(sink) + ((int64_t)bh * d.sink_tokens + tok) * 128
+          : reinterpret_cast<const uint16_t*>(ring) + ((int64_t)bh * d.ring_tokens + (tok % d.ring_tokens)) * 128;
+      return *reinterpret_cast<const uint2*>(row + lane * 4);
+    };
+    auto value_dense = [&](int tok) { return !(tok >= sink_filled && tok < v_end); };
+    uint2 k_next = make_uint2(0, 0), v_next = make_uint2(0, 0);
+    {
+      const int first = t + warp;
+      if (first < seg_end) {
+        if (kind != 1) k_next = dense_row(d.k_sink, d.k_ring, first);
+        if (value_dense(first)) v_next = dense_row(d.v_sink, d.v_ring, first);
+      }
+    }
+    for (int tok = t + warp; tok < seg_end; tok += kWarps) {
+      const uint2 k_raw = k_next, v_raw = v_next;
+      const int nxt = tok + kWarps;
+      if (nxt < seg_end) {
+        if (kind != 1) k_next = dense_row(d.k_sink, d.k_ring, nxt);
+        if (value_dense(nxt)) v_next = dense_row(d.v_sink, d.v_ring, nxt);
+      }
+      float kv[4];
+      if (kind == 1) {
+        const int j = tok - page_first;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int ch = lane * 4 + i;
+          uint32_t code = (page[ch * 32 + j / 4] >> ((j % 4) * 2)) & 3u;
+          const int slot = bs.slot_map[ch];
+          if (slot >= 0) code |= ((page[d.key_off_high + slot * 32 + j / 4] >> ((j % 4) * 2)) & 3u) << 2;
+          const float s = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_scale)[ch]);
+          const float z = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_zero)[ch]);
+          kv[i] = fused ? __fmaf_rn((float)code, s, z) : rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn((float)code, s)), z));
+        }
+      } else {
+        kv[0] = H::to_float((uint16_t)(k_raw.x & 0xFFFF)); kv[1] = H::to_float((uint16_t)(k_raw.x >> 16));
+        kv[2] = H::to_float((uint16_t)(k_raw.y & 0xFFFF)); kv[3] = H::to_float((uint16_t)(k_raw.y >> 16));
+      }
+      float s[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        float dot = q[r][0] * kv[0];
+        dot = fmaf(q[r][1], kv[1], dot);
+        dot = fmaf(q[r][2], kv[2], dot);
+        dot = fmaf(q[r][3], kv[3], dot);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+        s[r] = dot * scale2;
+      }
+      // value row of the same token
+      float vv[4];
+      if (!value_dense(tok)) {
+        const int64_t row = (int64_t)bh * d.max_value_tokens + (tok - d.sink_tokens);
+        const uint32_t byte = d.v_codes[row * 32 + lane];
+        const int g = (lane * 4) / d.value_group;
+        const uint16_t* meta = reinterpret_cast<const uint16_t*>(d.v_meta) + row * 2 * d.value_groups;
+        const float sc = H::to_float(meta[g]), z = H::to_float(meta[d.value_groups + g]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          vv[i] = fused ? __fmaf_rn((float)((byte >> (2 * i)) & 3u), sc, z)
+                        : rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn((float)((byte >> (2 * i)) & 3u), sc)), z));
+      } else {
+        vv[0] = H::to_float((uint16_t)(v_raw.x & 0xFFFF)); vv[1] = H::to_float((uint16_t)(v_raw.x >> 16));
+        vv[2] = H::to_float((uint16_t)(v_raw.y & 0xFFFF)); vv[3] = H::to_float((uint16_t)(v_raw.y >> 16));
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float m_new = fmaxf(m[r], s[r]);
+        const float alpha = fast_exp2(m[r] - m_new);
+        const float p = fast_exp2(s[r] - m_new);
+        m[r] = m_new;
+        l[r] = l[r] * alpha + p;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[r][i] = acc[r][i] * alpha + p * vv[i];
+      }
+    }
+    t = seg_end;
+  }
+  // hand the warp state to the block merge: acc in channel order
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    if (lane == 0) { bs.merge_m[warp][r] = m[r]; bs.merge_l[warp][r] = l[r]; }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) warp_out[(warp * 4 + r) * 128 + lane * 4 + i] = acc[r][i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
+// Block merge of the eight warp states: thread = (channel, head parity); partials leave in natural-log units.
+template <class BS>
+__device__ __forceinline__ void block_merge(const FastArgs& a, const BS& bs, const float* warp_out, int b, int hkv, int rep,
+                                            int split) {
+  const int tid = threadIdx.x;
+  const int slot = a.split_base + split;
+  const int ch = tid & 127;
+  for (int r = tid >> 7; r < rep; r += kThreads / 128) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) m = fmaxf(m, bs.merge_m[w][r]);
+    float l = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float mw = bs.merge_m[w][r];
+      if (mw != -INFINITY) {
+        const float wgt = fast_exp2(mw - m);
+        l += bs.merge_l[w][r] * wgt;
+        acc += warp_out[(w * 4 + r) * 128 + ch] * wgt;
+      }
+    }
+    const int64_t row = ((int64_t)b * a.query_heads + hkv * rep + r) * a.total_splits + slot;
+    if (ch == 0) {
+      a.part_m[row] = m == -INFINITY ? -INFINITY : m * 0.6931471805599453f;
+      a.part_l[row] = l;
+    }
+    a.part_acc[row * 128 + ch] = acc;
+  }
+}
+
+}  // namespace

@@ -55,8 +55,14 @@ def fused_dart_attention(
     fallback: bool = True,
     page_table: Optional[DartPageTable] = None,
     page_runs: Optional[Sequence[DartPageRun]] = None,
+    flavour: int = _lib.DEQUANT_PER_OP,
 ) -> torch.Tensor:
     """Single-token page attention, ``query [B, Hq, 1, D] -> [B, Hq, 1, D]``.
+
+    ``flavour`` picks the dequantization arithmetic: ``DEQUANT_PER_OP`` (default) reproduces the
+    reference's streamed path, whose pages are dequantized with the multiply and the add each
+    rounded to the metadata dtype; ``DEQUANT_FUSED`` reproduces the reference's Triton kernels
+    (``fused_attention.py:149-262``), which keep ``code * scale + zero`` in fp32.
 
     ``fallback`` only decides what happens for more than one query token (the streamed
     per-token path, as in the reference); there is no CPU fallback.  ``page_table`` and
@@ -96,7 +102,7 @@ def fused_dart_attention(
             if run.first_page_index < 0 or run.first_page_index + run.page_count > total:
                 raise ValueError("page_run is outside the current cache page range")
             starts.add(run.first_page_index)
-    return decode_attention(query[:, :, 0], cache, scale=scale).unsqueeze(2)
+    return decode_attention(query[:, :, 0], cache, scale=scale, flavour=flavour).unsqueeze(2)
 
 
 __all__ = ["fused_dart_attention", "decode_attention"]

@@ -27,8 +27,10 @@ enum { DARTKV_DENSE_PAGE = 0, DARTKV_QUANTIZED_PAGE = 1, DARTKV_MIXED_PAGE = 2 }
 enum { DARTKV_DIV_TRUE = 0, DARTKV_DIV_RECIPROCAL = 1 };
 /* dequantization arithmetic: multiply and add each rounded to the metadata dtype
  * (src/dart/quantization.py:103-106, src/dart/mixed.py:91-94), or one fp32 multiply-add
- * rounded once to the output dtype (src/dart/triton_ops.py:59,110,201) */
-enum { DARTKV_DEQUANT_PER_OP = 0, DARTKV_DEQUANT_FP32 = 1 };
+ * rounded once to the output dtype (src/dart/triton_ops.py:59,110,201), or -- decode attention only -- one
+ * fp32 multiply-add that is never rounded to the cache dtype, the arithmetic of the reference's Triton
+ * attention kernels (src/dart/fused_attention.py:149-262) */
+enum { DARTKV_DEQUANT_PER_OP = 0, DARTKV_DEQUANT_FP32 = 1, DARTKV_DEQUANT_FUSED = 2 };
 /* channel scoring, src/dart/mixed.py:154-162 */
 enum { DARTKV_SCORE_MAGNITUDE = 0, DARTKV_SCORE_VARIANCE = 1 };
 

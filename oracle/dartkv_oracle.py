@@ -235,7 +235,11 @@ def _affine_restore(codes_f32: np.ndarray, scale, zero, md: str, out_dt: str, fl
         # triton_ops.py:59,110,201: fp32 multiply-add, one rounding to the output dtype
         fused = (codes_f32.astype(np.float64) * scale.astype(np.float64) + zero.astype(np.float64)).astype(np.float32)
         return round_to(fused, out_dt)
-    raise ValueError("flavour must be 'cpu' or 'fp32'")
+    if flavour == "fused":
+        # fused_attention.py:159,209,241: the Triton attention kernels keep code * scale + zero in fp32 and never
+        # round it to the cache dtype
+        return (codes_f32.astype(np.float64) * scale.astype(np.float64) + zero.astype(np.float64)).astype(np.float32)
+    raise ValueError("flavour must be 'cpu', 'fp32' or 'fused'")
 
 
 def dequantize(q: QTensor, *, out_dt: Optional[str] = None, flavour: str = "cpu") -> np.ndarray:
