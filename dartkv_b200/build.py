@@ -28,8 +28,8 @@ def _stale(sources) -> bool:
     if not os.path.exists(LIB_PATH):
         return True
     built = os.path.getmtime(LIB_PATH)
-    deps = list(sources) + [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "mma_utils.cuh"),
-                            os.path.join(PACKAGE_DIR, "..", "include", "dartkv_b200.h")]
+    headers = [os.path.join(CSRC, name) for name in os.listdir(CSRC) if name.endswith(".cuh")]
+    deps = list(sources) + headers + [os.path.join(PACKAGE_DIR, "..", "include", "dartkv_b200.h")]
     return any(os.path.exists(p) and os.path.getmtime(p) > built for p in deps)
 
 
@@ -46,7 +46,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in sources:
         obj = os.path.join(build_dir, os.path.basename(src) + ".o")
         objects.append(obj)
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj]
+        cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("DARTKV_NVCC_FLAGS", "").split(), "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -271,18 +271,23 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
   if (flavour == DARTKV_DEQUANT_FUSED && dartkv_decode_fused32_supported(d, q_dtype, query_heads)) L.fast = 2;
   if (L.fast) {
     // A block hands its pages to four warp pairs round-robin, two blocks are resident per SM.  Pick the
-    // pages per block (a multiple of four, at most 16 blocks per (batch, kv head)) that minimizes
-    // waves x (pages per pair + a fixed per-block cost of about one page).
+    // pages per block (a multiple of four, at most 16 blocks per (batch, kv head)) that minimizes the modelled
+    // time in units of one page per pair: a block costs its pages per pair plus a fixed 1.75 (query load,
+    // first-page latency, merge of its eight warps), the dense block of a (batch, kv head) about 2; blocks run
+    // in waves of `resident`.  Constants fitted to B200 timings at batch 32 / 8K and batch 128 / 32K context.
     const int pages = max(1, (tokens - d->sink_tokens) / d->page_size);
     const int quads = (pages + 3) / 4;
     const int resident = 2 * dartkv_sm_count();
+    const double block_fixed = 1.75, dense_cost = 2.0;
     int best_q = quads;
     double best_cost = 1e30;
     for (int q = max(1, (quads + 15) / 16); q <= quads; ++q) {
       const int splits = (pages + 4 * q - 1) / (4 * q);
-      const int64_t blocks = (int64_t)bh * (splits + 1);
+      const int64_t blocks = (int64_t)bh * splits;
       const int64_t waves = (blocks + resident - 1) / resident;
-      const double cost = (double)waves * (q + 1.0);
+      const double by_waves = (double)waves * (q + block_fixed);
+      const double by_work = (double)bh * (splits * (q + block_fixed) + dense_cost) / resident;
+      const double cost = by_waves > by_work ? by_waves : by_work;
       if (cost < best_cost - 1e-9) { best_cost = cost; best_q = q; }
     }
     L.fast_pages_per_split = 4 * best_q;

@@ -233,22 +233,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     const int p_begin = split * a.pages_per_split;
     const int p_end = min(p_begin + a.pages_per_split, total_pages);
 
-    // query, pre-shifted for the block-diagonal operand
-    for (int i = tid; i < 4 * 128; i += kThreads) {
-      const int r = i >> 7, ch = i & 127;
-      uint32_t v = 0;
-      if (r < rep) v = reinterpret_cast<const uint16_t*>(a.q)[((int64_t)b * a.query_heads + hkv * rep + r) * 128 + ch];
-      bs.q32[ch][2 * r] = v;
-      bs.q32[ch][2 * r + 1] = v << 16;
-    }
+    // the first two pages of this pair are requested before anything else, so their latency overlaps the
+    // query load below
     const bool issuer = hf == 0 && lane == 0;
-    if (issuer) {
-      mbar_init(&ps.bar[0], 1);
-      mbar_init(&ps.bar[1], 1);
-      mbar_fence_init();
-    }
-    __syncthreads();
-
     const int vmeta_page_bytes = 128 * 2 * d.value_groups * 2;
     const uint32_t stage_tx = d.key_page_bytes + kValueCodes + vmeta_page_bytes;
     auto issue = [&](int pg, int stage) {
@@ -260,6 +247,25 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       bulk_copy_g2s(ps.stage[stage] + kOffVMeta,
                     reinterpret_cast<const uint8_t*>(d.v_meta) + vrow * (2 * d.value_groups * 2), vmeta_page_bytes, &ps.bar[stage]);
     };
+    const int pg0 = p_begin + pair;
+    if (issuer) {
+      mbar_init(&ps.bar[0], 1);
+      mbar_init(&ps.bar[1], 1);
+      mbar_fence_init();
+      if (pg0 < p_end) issue(pg0, 0);
+      if (pg0 + kPairs < p_end) issue(pg0 + kPairs, 1);
+    }
+
+    // query, pre-shifted for the block-diagonal operand
+    for (int i = tid; i < 4 * 128; i += kThreads) {
+      const int r = i >> 7, ch = i & 127;
+      uint32_t v = 0;
+      if (r < rep) v = reinterpret_cast<const uint16_t*>(a.q)[((int64_t)b * a.query_heads + hkv * rep + r) * 128 + ch];
+      bs.q32[ch][2 * r] = v;
+      bs.q32[ch][2 * r + 1] = v << 16;
+    }
+    __syncthreads();
+
 
     float o_acc[4][4];   // [m-tile][c-reg]: head c, channel 16g + 2mt + r + 8j'
 #pragma unroll
@@ -277,11 +283,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     CodeConsts<DT> cc;
     cc.init();
 
-    const int pg0 = p_begin + pair;
-    if (issuer) {
-      if (pg0 < p_end) issue(pg0, 0);
-      if (pg0 + kPairs < p_end) issue(pg0 + kPairs, 1);
-    }
     int iter = 0;
     for (int pg = pg0; pg < p_end; pg += kPairs, ++iter) {
       const int stage = iter & 1;

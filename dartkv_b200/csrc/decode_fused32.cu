@@ -107,6 +107,7 @@ __device__ __forceinline__ void fused_page_half(const dartkv_cache_desc& d, Fuse
   {
     const uint8_t* low_thread = blob + 4 * g + 32 * c;                               // + 256 * step (+128)
     const uint8_t* w_thread = reinterpret_cast<const uint8_t*>(ps.w_low) + 8 * c + 4 * (g >> 2);   // + 64 * step (+32)
+#ifndef FUSED_SKIP_QK
 #pragma unroll 4
     for (int ks = 0; ks < 16; ++ks) {
       uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + 256 * ks);
@@ -133,6 +134,7 @@ __device__ __forceinline__ void fused_page_half(const dartkv_cache_desc& d, Fuse
         mma_f16(s_acc[mt], w0 & (0x00030003u << (4 * mt)), w0 & (0x000C000Cu << (4 * mt)), w1 & (0x00030003u << (4 * mt)),
                 w1 & (0x000C000Cu << (4 * mt)), b0, b1);
     }
+#endif
   }
 
   // ---- online softmax for head c over this warp's 64 tokens (this thread: 8 of them)
@@ -237,6 +239,7 @@ __device__ __forceinline__ void fused_page_half(const dartkv_cache_desc& d, Fuse
     const uint32_t sel_v = (g >> 2) ? 0x7632u : 0x5410u;
     const uint8_t* vthread = blob + kOffVCodes + 32 * (4 * HF + c) + 4 * wi;   // + 512 * ks (+256 for the second token)
     const uint32_t* uthread = utab + c * 4 + (g >> 1);                         // + kUStride * ks (+16 for the second)
+#ifndef FUSED_SKIP_PV
 #pragma unroll 2
     for (int ks = 0; ks < 8; ++ks) {
       const uint32_t x0 = prmt(*reinterpret_cast<const uint32_t*>(vthread + 512 * ks),
@@ -251,6 +254,7 @@ __device__ __forceinline__ void fused_page_half(const dartkv_cache_desc& d, Fuse
       mma_f16(st.o_acc[2], x0 & 0x03000300u, y0 & 0x00030003u, x1 & 0x03000300u, y1 & 0x00030003u, b0, b1);
       mma_f16(st.o_acc[3], y0 & 0x000C000Cu, y0 & 0x00300030u, y1 & 0x000C000Cu, y1 & 0x00300030u, b0, b1);
     }
+#endif
   }
 }
 
@@ -279,6 +283,29 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
     const int p_begin = split * a.pages_per_split;
     const int p_end = min(p_begin + a.pages_per_split, total_pages);
 
+    // the first two pages of this pair are requested before anything else, so their latency overlaps the
+    // query load below
+    const bool issuer = hf == 0 && lane == 0;
+    const int vmeta_page_bytes = 128 * 2 * d.value_groups * 2;
+    const uint32_t stage_tx = d.key_page_bytes + kValueCodes + vmeta_page_bytes;
+    auto issue = [&](int pg, int stage) {
+      // one lane starts the three bulk copies of a page; the barrier completes when all bytes landed
+      mbar_expect_tx(&ps.bar[stage], stage_tx);
+      const int64_t vrow = (int64_t)bh * d.max_value_tokens + (int64_t)pg * 128;
+      bulk_copy_g2s(ps.stage[stage], d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes, d.key_page_bytes, &ps.bar[stage]);
+      bulk_copy_g2s(ps.stage[stage] + kOffVCodes, d.v_codes + vrow * 32, kValueCodes, &ps.bar[stage]);
+      bulk_copy_g2s(ps.stage[stage] + kOffVMeta,
+                    reinterpret_cast<const uint8_t*>(d.v_meta) + vrow * (2 * d.value_groups * 2), vmeta_page_bytes, &ps.bar[stage]);
+    };
+    const int pg0 = p_begin + pair;
+    if (issuer) {
+      mbar_init(&ps.bar[0], 1);
+      mbar_init(&ps.bar[1], 1);
+      mbar_fence_init();
+      if (pg0 < p_end) issue(pg0, 0);
+      if (pg0 + kPairs < p_end) issue(pg0 + kPairs, 1);
+    }
+
     // query as fp32 and its largest magnitude (bounds the page weights q*s)
     {
       float amax = 0.0f;
@@ -294,12 +321,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
       for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
       if (lane == 0) bs.merge_m[warp][0] = amax;   // scratch use before the merge
     }
-    const bool issuer = hf == 0 && lane == 0;
-    if (issuer) {
-      mbar_init(&ps.bar[0], 1);
-      mbar_init(&ps.bar[1], 1);
-      mbar_fence_init();
-    }
     __syncthreads();
     if (tid == 0) {
       float amax = 0.0f;
@@ -309,17 +330,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
     __syncthreads();
     const float q_absmax = bs.q_absmax;
 
-    const int vmeta_page_bytes = 128 * 2 * d.value_groups * 2;
-    const uint32_t stage_tx = d.key_page_bytes + kValueCodes + vmeta_page_bytes;
-    auto issue = [&](int pg, int stage) {
-      // one lane starts the three bulk copies of a page; the barrier completes when all bytes landed
-      mbar_expect_tx(&ps.bar[stage], stage_tx);
-      const int64_t vrow = (int64_t)bh * d.max_value_tokens + (int64_t)pg * 128;
-      bulk_copy_g2s(ps.stage[stage], d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes, d.key_page_bytes, &ps.bar[stage]);
-      bulk_copy_g2s(ps.stage[stage] + kOffVCodes, d.v_codes + vrow * 32, kValueCodes, &ps.bar[stage]);
-      bulk_copy_g2s(ps.stage[stage] + kOffVMeta,
-                    reinterpret_cast<const uint8_t*>(d.v_meta) + vrow * (2 * d.value_groups * 2), vmeta_page_bytes, &ps.bar[stage]);
-    };
 
     WarpState st;
 #pragma unroll
@@ -339,11 +349,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
     uint32_t* utab = ps.u[hf];
     bool ok = true;
 
-    const int pg0 = p_begin + pair;
-    if (issuer) {
-      if (pg0 < p_end) issue(pg0, 0);
-      if (pg0 + kPairs < p_end) issue(pg0 + kPairs, 1);
-    }
     int iter = 0;
     for (int pg = pg0; pg < p_end; pg += kPairs, ++iter) {
       const int stage = iter & 1;
@@ -352,7 +357,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
       const uint8_t* blob = ps.stage[stage];
 
       // ---- per-page setup by the 64 threads of the pair: thread tp owns channels 2tp, 2tp+1
-      float f, f_inv;
+      float f = 1.0f, f_inv = 1.0f;
+#ifndef FUSED_SKIP_SETUP
       {
         const uint32_t* kscale2 = reinterpret_cast<const uint32_t*>(blob + d.key_off_scale);
         const uint32_t* kzero2 = reinterpret_cast<const uint32_t*>(blob + d.key_off_zero);
@@ -397,6 +403,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
           ps.w_high[lane] = wh;
         }
       }
+#endif
       pair_barrier(pair);
 
       if (d.value_groups == 2) {
