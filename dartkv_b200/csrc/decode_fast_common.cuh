@@ -75,6 +75,9 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
   const bool fused = a.flavour == DARTKV_DEQUANT_FUSED;
   // segments: [0, sink_filled) then [fast_end, seen) cut at key page boundaries
   int t = 0;
+#ifdef DENSE_SKIP
+  t = seen;
+#endif
   while (t < seen) {
     if (t >= sink_filled && t < fast_end) { t = fast_end; continue; }
     int seg_end, kind;

@@ -26,6 +26,14 @@
 
 namespace {
 
+#ifndef FUSED_QK_UNROLL
+#define FUSED_QK_UNROLL 16
+#endif
+#ifndef FUSED_PV_UNROLL
+#define FUSED_PV_UNROLL 4
+#endif
+
+constexpr int kQkUnroll = FUSED_QK_UNROLL, kPvUnroll = FUSED_PV_UNROLL;
 constexpr int kUStride = 36;   // 32-bit words per group of 8 local tokens in a warp's weight table (4 pad)
 
 struct FusedPairSmem {
@@ -108,7 +116,7 @@ __device__ __forceinline__ void fused_page_half(const dartkv_cache_desc& d, Fuse
     const uint8_t* low_thread = blob + 4 * g + 32 * c;                               // + 256 * step (+128)
     const uint8_t* w_thread = reinterpret_cast<const uint8_t*>(ps.w_low) + 8 * c + 4 * (g >> 2);   // + 64 * step (+32)
 #ifndef FUSED_SKIP_QK
-#pragma unroll 4
+#pragma unroll kQkUnroll
     for (int ks = 0; ks < 16; ++ks) {
       uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + 256 * ks);
       uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + 256 * ks + 128);
@@ -240,7 +248,7 @@ __device__ __forceinline__ void fused_page_half(const dartkv_cache_desc& d, Fuse
     const uint8_t* vthread = blob + kOffVCodes + 32 * (4 * HF + c) + 4 * wi;   // + 512 * ks (+256 for the second token)
     const uint32_t* uthread = utab + c * 4 + (g >> 1);                         // + kUStride * ks (+16 for the second)
 #ifndef FUSED_SKIP_PV
-#pragma unroll 2
+#pragma unroll kPvUnroll
     for (int ks = 0; ks < 8; ++ks) {
       const uint32_t x0 = prmt(*reinterpret_cast<const uint32_t*>(vthread + 512 * ks),
                                *reinterpret_cast<const uint32_t*>(vthread + 512 * ks + 16), sel_v);
