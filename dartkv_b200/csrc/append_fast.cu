@@ -59,11 +59,24 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
+// range / qmax rounded to the data dtype.  For bf16 the quotient of two 8-bit significands is never within
+// 2^-17 of a rounding boundary (see below), so a multiply by the fp32 reciprocal rounds to the same bf16.
 template <int DT>
 __device__ __forceinline__ float scale_of(float mn, float mx, float qmax) {
   float range = rnd<DT>(__fsub_rn(mx, mn));
   range = fmaxf(range, rnd<DT>(1e-4f));
+  // qmax is one of 3, 15, 255: correctly rounded fp32 reciprocals as constants
+  const float inv_qmax = qmax == 3.0f ? 0.3333333432674408f : (qmax == 15.0f ? 0.06666667014360428f : 0.003921568859368563f);
+  if (DT == DARTKV_BF16) return rnd<DT>(__fmul_rn(range, inv_qmax));
   return rnd<DT>(__fdiv_rn(range, qmax));
+}
+// 1 / scale for the reciprocal-multiply quotient (bf16 only): the approximate reciprocal is within 2^-22
+template <int DT>
+__device__ __forceinline__ float inverse_scale(float scale) {
+  if (DT != DARTKV_BF16) return 0.0f;   // fp16 takes the true division
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(scale));
+  return r;
 }
 
 // ---- packed code computation -------------------------------------------------------------------
@@ -283,7 +296,7 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
   store_f(page + d.key_off_scale, d.md_dtype, 2 * p + 1, scale_hi);
   store_f(page + d.key_off_zero, d.md_dtype, 2 * p, mn_lo);
   store_f(page + d.key_off_zero, d.md_dtype, 2 * p + 1, mn_hi);
-  const float inv_lo = __frcp_rn(scale_lo), inv_hi = __frcp_rn(scale_hi);
+  const float inv_lo = inverse_scale<DT>(scale_lo), inv_hi = inverse_scale<DT>(scale_hi);
   const uint32_t cap2 = (uint32_t)P::bits((DT == DARTKV_BF16 ? 128.0f : 1024.0f) + qmax_lo) |
                         ((uint32_t)P::bits((DT == DARTKV_BF16 ? 128.0f : 1024.0f) + qmax_hi) << 16);
 
@@ -391,7 +404,7 @@ __global__ void __launch_bounds__(256) fast_value_rows_kernel(dartkv_cache_desc 
     const float mn = P::lo(mn1), mx = P::lo(mx1);
     bad |= live[s] && !(isfinite(mn) && isfinite(mx));
     const float scale = scale_of<DT>(mn, mx, qmax);
-    const float inv = __frcp_rn(scale);
+    const float inv = inverse_scale<DT>(scale);
     const uint32_t mnp = (mn1 & 0xFFFFu) * 0x00010001u;
     // codes of 16/(2*VBITS) pairs gather in one register (even channels in the low half, odd in the high half)
     constexpr int PAIRS = 8 / VBITS;                      // pairs per gather register
