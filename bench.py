@@ -514,6 +514,8 @@ def main() -> None:
     parser.add_argument("--skip-extras", action="store_true", help="skip the append microbench and the CPU baseline")
     parser.add_argument("--flavour", choices=("per_op", "fused"), default="per_op",
                         help="dequantization arithmetic of the timed decode call (default: the pinned per-op rounding)")
+    parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (e.g. one rank's share)")
+    parser.add_argument("--context", type=int, default=0, help="override the workload's context length")
     args = parser.parse_args()
     if args.workload == "config4":
         if args.impl == "reference":
@@ -521,7 +523,11 @@ def main() -> None:
             return
         qwen3_decode(args)
         return
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        wl["batch"] = args.batch
+    if args.context > 0:
+        wl["ctx"] = args.context
     if args.impl == "reference":
         reference_arm(args, wl)
     else:

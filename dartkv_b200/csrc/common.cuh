@@ -107,4 +107,12 @@ __device__ __forceinline__ float affine_restore(float code, float scale, float z
 __host__ __device__ __forceinline__ int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Balanced split of `units` work units over `blocks` blocks: block j owns [j*units/blocks, (j+1)*units/blocks).
+// Returns the block that owns unit x.
+__host__ __device__ __forceinline__ int dartkv_block_of_unit(int64_t x, int blocks, int64_t units) {
+  int64_t j = x * blocks / units;
+  if ((j + 1) * units / blocks <= x) ++j;
+  return (int)j;
+}
+
 static inline int dartkv_gcd(int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; }

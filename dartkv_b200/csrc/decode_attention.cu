@@ -211,9 +211,22 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cach
 }
 
 // one block per (batch, query head): combine split partials, normalize, cast
+// With stream_blocks > 0 (tensor-core layouts) a row's valid slots are its dense slot 0 plus one per stream block
+// that touched its (batch, kv head); the remaining slots of the row hold stale data and are skipped.
 __global__ void decode_merge_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
-                                    const float* __restrict__ part_acc, int splits, int D, void* out, int out_dt) {
+                                    const float* __restrict__ part_acc, int total_splits, int D, void* out, int out_dt,
+                                    int stream_blocks, int64_t units, int quads, int query_heads, int kv_heads) {
   int64_t row = blockIdx.x;
+  int splits = total_splits;
+  if (stream_blocks > 0) {
+    const int rep = query_heads / kv_heads;
+    const int64_t bh = (row / query_heads) * kv_heads + (row % query_heads) / rep;
+    splits = 2 + dartkv_block_of_unit(bh * quads + quads - 1, stream_blocks, units) -
+             dartkv_block_of_unit(bh * quads, stream_blocks, units);
+  }
+  part_m += row * (total_splits - splits);   // rows are total_splits slots apart, the loops below index row * splits
+  part_l += row * (total_splits - splits);
+  part_acc += row * (total_splits - splits) * D;
   float m = -INFINITY;
   for (int s = 0; s < splits; ++s) m = fmaxf(m, part_m[row * splits + s]);
   float l = 0.0f;
@@ -236,17 +249,18 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_m, const floa
 struct DecodeLayout {
   int generic_splits, generic_chunk;   // generic kernel over the whole range (fallback)
   int fast;                            // tensor-core kernel for the packed pages: 1 per-op rounded, 2 unrounded fp32
-  int fast_splits, fast_pages_per_split;
+  int quads, stream_blocks;            // tensor-core layouts: four-page units per (batch, kv head), stream blocks
+  long long units;
   int total_splits;
 };
 
 int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
 int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
-                              int flavour, int splits, int pages_per_split, int split_base, int total_splits,
+                              int flavour, int quads, int stream_blocks, long long units, int total_splits,
                               float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream);
 int dartkv_decode_fused32_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
 int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
-                                 int flavour, int splits, int pages_per_split, int split_base, int total_splits,
+                                 int flavour, int quads, int stream_blocks, long long units, int total_splits,
                                  float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream);
 
 static int dartkv_sm_count() {
@@ -270,29 +284,46 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
   if (flavour == DARTKV_DEQUANT_PER_OP && dartkv_decode_fast_supported(d, q_dtype, query_heads)) L.fast = 1;
   if (flavour == DARTKV_DEQUANT_FUSED && dartkv_decode_fused32_supported(d, q_dtype, query_heads)) L.fast = 2;
   if (L.fast) {
-    // A block hands its pages to four warp pairs round-robin, two blocks are resident per SM.  Pick the
-    // pages per block (a multiple of four, at most 16 blocks per (batch, kv head)) that minimizes the modelled
-    // time in units of one page per pair: a block costs its pages per pair plus a fixed 1.75 (query load,
-    // first-page latency, merge of its eight warps), the dense block of a (batch, kv head) about 2; blocks run
-    // in waves of `resident`.  Constants fitted to B200 timings at batch 32 / 8K and batch 128 / 32K context.
+    // One unit = four consecutive pages of a (batch, kv head) (a block hands them to its four warp pairs).  The
+    // units of all rows are dealt out evenly to `stream_blocks` blocks.  Two families of splits are compared with a
+    // cost model in units of one page per pair (a block costs its pages per pair plus 1.75 per row it touches:
+    // query load, first-page latency, merge of its eight warps; the dense block of a row about 2; blocks run in
+    // waves of two per SM; constants fitted to B200 timings):
+    //   aligned    rows * s blocks, s = 1..16 pieces per row;
+    //   unaligned  one block per resident slot, a block may finish one row and start the next (at most 16 blocks
+    //              touch a row); measured ~8 % slower per unit than aligned blocks, which start staggered.
     const int pages = max(1, (tokens - d->sink_tokens) / d->page_size);
-    const int quads = (pages + 3) / 4;
+    L.quads = (pages + 3) / 4;
+    L.units = (long long)bh * L.quads;
     const int resident = 2 * dartkv_sm_count();
     const double block_fixed = 1.75, dense_cost = 2.0;
-    int best_q = quads;
+    int best_pieces = 1;
     double best_cost = 1e30;
-    for (int q = max(1, (quads + 15) / 16); q <= quads; ++q) {
-      const int splits = (pages + 4 * q - 1) / (4 * q);
-      const int64_t blocks = (int64_t)bh * splits;
-      const int64_t waves = (blocks + resident - 1) / resident;
+    for (int q = max(1, (L.quads + 15) / 16); q <= L.quads; ++q) {
+      const int pieces = (L.quads + q - 1) / q;
+      const long long blocks = (long long)bh * pieces;
+      const long long waves = (blocks + resident - 1) / resident;
       const double by_waves = (double)waves * (q + block_fixed);
-      const double by_work = (double)bh * (splits * (q + block_fixed) + dense_cost) / resident;
+      const double by_work = (double)bh * (pieces * (q + block_fixed) + dense_cost) / resident;
       const double cost = by_waves > by_work ? by_waves : by_work;
-      if (cost < best_cost - 1e-9) { best_cost = cost; best_q = q; }
+      if (cost < best_cost - 1e-9) { best_cost = cost; best_pieces = pieces; }
     }
-    L.fast_pages_per_split = 4 * best_q;
-    L.fast_splits = (pages + L.fast_pages_per_split - 1) / L.fast_pages_per_split;
-    L.total_splits = L.fast_splits + 1;                // + one block per (batch, kv head) for the dense tokens
+    L.stream_blocks = bh * best_pieces;
+    L.total_splits = best_pieces + 1;
+    {
+      const long long min_share = (L.quads + 14) / 15;
+      long long blocks = resident;
+      if (blocks > L.units / min_share) blocks = L.units / min_share;
+      if (blocks >= 1 && blocks < (long long)bh * best_pieces) {
+        const double share = (double)L.units / blocks;
+        const double cost = 1.08 * (share + block_fixed * (share / L.quads + 1.0)) + (double)bh * dense_cost / resident;
+        if (cost < best_cost) {
+          const long long w = L.units / blocks;   // smallest share of a block
+          L.stream_blocks = (int)blocks;
+          L.total_splits = (int)((L.quads + w - 2) / w + 1) + 1;
+        }
+      }
+    }
   } else {
     int max_splits = max(1, (tokens + 63) / 64);
     int want = max(1, (148 * 4 + bh - 1) / bh);
@@ -318,7 +349,7 @@ extern "C" int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* d, int
   for (int dt = 0; dt < 3; ++dt)
     for (int flavour = 0; flavour < 3; ++flavour) {
       DecodeLayout L = decode_layout(d, dt, query_heads, flavour, max_tokens);
-      // the tensor-core layout uses at most 16 page splits + 1 dense block whatever the token count
+      // the tensor-core layouts use at most 16 stream slots + 1 dense slot per row whatever the token count
       if (L.fast) L.total_splits = 17;
       best = max(best, layout_bytes(d, query_heads, L));
     }
@@ -357,7 +388,7 @@ extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* q
   const int D = d->head_dim;
   if (L.fast) {
     int rc = (L.fast == 2 ? dartkv_decode_fused32_launch : dartkv_decode_fast_launch)(
-        d, query, q_dtype, query_heads, scale, flavour, L.fast_splits, L.fast_pages_per_split, 0, L.total_splits, part_m,
+        d, query, q_dtype, query_heads, scale, flavour, L.quads, L.stream_blocks, L.units, L.total_splits, part_m,
         part_l, part_acc, status, stream);
     if (rc) return rc;
   } else {
@@ -373,8 +404,9 @@ extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* q
     decode_generic_kernel<<<dim3(bh, L.generic_splits), GEN_THREADS, smem, stream>>>(*d, a);
     DARTKV_LAUNCH_OK("decode_generic_kernel");
   }
-  decode_merge_kernel<<<(unsigned)((int64_t)d->batch * query_heads), 128, 0, stream>>>(part_m, part_l, part_acc,
-                                                                                        L.total_splits, D, out, q_dtype);
+  decode_merge_kernel<<<(unsigned)((int64_t)d->batch * query_heads), 128, 0, stream>>>(
+      part_m, part_l, part_acc, L.total_splits, D, out, q_dtype, L.fast ? L.stream_blocks : 0, L.units, L.quads, query_heads,
+      d->kv_heads);
   DARTKV_LAUNCH_OK("decode_merge_kernel");
   return DARTKV_OK;
 }

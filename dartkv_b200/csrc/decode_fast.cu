@@ -217,43 +217,74 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
-  const int bh = blockIdx.x, split = blockIdx.y;
-  const int b = bh / d.kv_heads, hkv = bh % d.kv_heads;
   const int rep = a.query_heads / d.kv_heads;
-  const bool dense = split == a.splits;
+  const int rows = d.batch * d.kv_heads;
 
-  if (dense) {
+  if ((int)blockIdx.x >= a.stream_blocks) {
+    // dense tokens of one (batch, kv head): partial slot 0.  These short blocks come last in launch order and fill
+    // the slots the stream blocks leave.
+    const int bh = blockIdx.x - a.stream_blocks;
     dense_block<DT>(d, a, bs, warp_out, bh);
-  } else {
-    const int pair = warp >> 1, hf = warp & 1;
-    PairSmem& ps = psm_all[pair];
-    const int k_end = d.state[2], v_end = d.state[3], sink_filled = d.state[4];
-    const int fast_end = fast_range_end(d.sink_tokens, d.page_size, k_end, v_end, sink_filled);
-    const int total_pages = fast_end > d.sink_tokens ? (fast_end - d.sink_tokens) / 128 : 0;
-    const int p_begin = split * a.pages_per_split;
-    const int p_end = min(p_begin + a.pages_per_split, total_pages);
+    __syncthreads();
+    block_merge(a, bs, warp_out, bh / d.kv_heads, bh % d.kv_heads, rep, 0);
+    return;
+  }
+
+  // ---- stream block: an even share of all (row, four-page unit) work, possibly spanning several rows
+  const int sb = blockIdx.x;
+  int64_t unit = (int64_t)sb * a.units / a.stream_blocks;
+  const int64_t unit_end = (int64_t)(sb + 1) * a.units / a.stream_blocks;
+  const int pair = warp >> 1, hf = warp & 1;
+  PairSmem& ps = psm_all[pair];
+  const int k_end = d.state[2], v_end = d.state[3], sink_filled = d.state[4];
+  const int fast_end = fast_range_end(d.sink_tokens, d.page_size, k_end, v_end, sink_filled);
+  const int total_pages = fast_end > d.sink_tokens ? (fast_end - d.sink_tokens) / 128 : 0;
+  const bool issuer = hf == 0 && lane == 0;
+  const int vmeta_page_bytes = 128 * 2 * d.value_groups * 2;
+  const uint32_t stage_tx = d.key_page_bytes + kValueCodes + vmeta_page_bytes;
+  int bh = 0;
+  auto issue = [&](int pg, int stage) {
+    // one lane starts the three bulk copies of a page; the barrier completes when all bytes landed
+    mbar_expect_tx(&ps.bar[stage], stage_tx);
+    const int64_t vrow = (int64_t)bh * d.max_value_tokens + (int64_t)pg * 128;
+    bulk_copy_g2s(ps.stage[stage], d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes, d.key_page_bytes, &ps.bar[stage]);
+    bulk_copy_g2s(ps.stage[stage] + kOffVCodes, d.v_codes + vrow * 32, kValueCodes, &ps.bar[stage]);
+    bulk_copy_g2s(ps.stage[stage] + kOffVMeta,
+                  reinterpret_cast<const uint8_t*>(d.v_meta) + vrow * (2 * d.value_groups * 2), vmeta_page_bytes, &ps.bar[stage]);
+  };
+  if (issuer) {
+    mbar_init(&ps.bar[0], 1);
+    mbar_init(&ps.bar[1], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const int K = d.key_mode == DARTKV_MIXED_PAGE ? d.promoted : 0;
+  const int prom_steps = (K + 7) >> 3;
+  const int jp = g & 1, hq = g >> 1;
+  const uint8_t* q_thread = reinterpret_cast<const uint8_t*>(&bs.q32[0][g]);   // + 32 * channel
+  const float scale2 = a.scale * kLog2e;
+  const int gv = (16 * g) / d.value_group;
+  bool ok = true;
+  CodeConsts<DT> cc;
+  cc.init();
+  int iter = 0;   // pages this pair has consumed so far: stage and barrier parity carry over from row to row
+
+  while (unit < unit_end) {
+    bh = (int)(unit / a.quads);
+    const int quad_begin = (int)(unit - (int64_t)bh * a.quads);
+    const int quad_count = (int)min((int64_t)(a.quads - quad_begin), unit_end - unit);
+    unit += quad_count;
+    const int b = bh / d.kv_heads, hkv = bh % d.kv_heads;
+    const int slot = 1 + sb - dartkv_block_of_unit((int64_t)bh * a.quads, a.stream_blocks, a.units);
+    const int p_begin = 4 * quad_begin;
+    const int p_end = min(4 * (quad_begin + quad_count), total_pages);
 
     // the first two pages of this pair are requested before anything else, so their latency overlaps the
     // query load below
-    const bool issuer = hf == 0 && lane == 0;
-    const int vmeta_page_bytes = 128 * 2 * d.value_groups * 2;
-    const uint32_t stage_tx = d.key_page_bytes + kValueCodes + vmeta_page_bytes;
-    auto issue = [&](int pg, int stage) {
-      // one lane starts the three bulk copies of a page; the barrier completes when all bytes landed
-      mbar_expect_tx(&ps.bar[stage], stage_tx);
-      const int64_t vrow = (int64_t)bh * d.max_value_tokens + (int64_t)pg * 128;
-      bulk_copy_g2s(ps.stage[stage], d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes, d.key_page_bytes, &ps.bar[stage]);
-      bulk_copy_g2s(ps.stage[stage] + kOffVCodes, d.v_codes + vrow * 32, kValueCodes, &ps.bar[stage]);
-      bulk_copy_g2s(ps.stage[stage] + kOffVMeta,
-                    reinterpret_cast<const uint8_t*>(d.v_meta) + vrow * (2 * d.value_groups * 2), vmeta_page_bytes, &ps.bar[stage]);
-    };
     const int pg0 = p_begin + pair;
     if (issuer) {
-      mbar_init(&ps.bar[0], 1);
-      mbar_init(&ps.bar[1], 1);
-      mbar_fence_init();
-      if (pg0 < p_end) issue(pg0, 0);
-      if (pg0 + kPairs < p_end) issue(pg0 + kPairs, 1);
+      if (pg0 < p_end) issue(pg0, iter & 1);
+      if (pg0 + kPairs < p_end) issue(pg0 + kPairs, (iter + 1) & 1);
     }
 
     // query, pre-shifted for the block-diagonal operand
@@ -266,24 +297,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     }
     __syncthreads();
 
-
     float o_acc[4][4];   // [m-tile][c-reg]: head c, channel 16g + 2mt + r + 8j'
 #pragma unroll
     for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) o_acc[mt][i] = 0.0f;
     float m_run = -INFINITY, l_run = 0.0f;   // head c, log2 domain
-    const int K = d.key_mode == DARTKV_MIXED_PAGE ? d.promoted : 0;
-    const int prom_steps = (K + 7) >> 3;
-    const int jp = g & 1, hq = g >> 1;
-    const uint8_t* q_thread = reinterpret_cast<const uint8_t*>(&bs.q32[0][g]);   // + 32 * channel
-    const float scale2 = a.scale * kLog2e;
-    const int gv = (16 * g) / d.value_group;
-    bool ok = true;
-    CodeConsts<DT> cc;
-    cc.init();
-
-    int iter = 0;
     for (int pg = pg0; pg < p_end; pg += kPairs, ++iter) {
       const int stage = iter & 1;
       const uint32_t parity = (iter >> 1) & 1;
@@ -349,7 +368,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       // the stage is free again: prefetch the page two iterations ahead
       if (issuer && pg + 2 * kPairs < p_end) issue(pg + 2 * kPairs, stage);
     }
-    if (!ok && lane == 0) atomicExch(a.status, 1);
 
     // ---- hand the warp state to the block merge
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 4);
@@ -364,10 +382,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
         const int ch = 16 * g + 2 * mt + (i >> 1) + 8 * (i & 1);
         warp_out[(warp * 4 + c) * 128 + ch] = o_acc[mt][i];
       }
+    __syncthreads();
+    block_merge(a, bs, warp_out, b, hkv, rep, slot);
+    __syncthreads();   // the merge buffer is staging memory again, the query table may be overwritten
   }
-  __syncthreads();
-
-  block_merge(a, bs, warp_out, b, hkv, rep, split);
+  if (!ok && lane == 0) atomicExch(a.status, 1);
 }
 
 constexpr size_t kSmemBytes = sizeof(PairSmem) * kPairs + sizeof(BlockSmem);
@@ -388,11 +407,11 @@ int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int qu
 }
 
 int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
-                              int flavour, int splits, int pages_per_split, int split_base, int total_splits,
+                              int flavour, int quads, int stream_blocks, long long units, int total_splits,
                               float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream) {
   (void)q_dtype;
-  FastArgs a{query, query_heads, scale, flavour, splits, pages_per_split, split_base, total_splits, part_m, part_l, part_acc, status};
-  dim3 grid(d->batch * d->kv_heads, splits + 1);
+  FastArgs a{query, query_heads, scale, flavour, quads, stream_blocks, units, total_splits, part_m, part_l, part_acc, status};
+  dim3 grid(stream_blocks + d->batch * d->kv_heads);
   if (d->dtype == DARTKV_BF16) {
     DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fast_kernel<DARTKV_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
     decode_fast_kernel<DARTKV_BF16><<<grid, kThreads, kSmemBytes, stream>>>(*d, a);

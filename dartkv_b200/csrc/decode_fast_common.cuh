@@ -28,7 +28,13 @@ struct FastArgs {
   int query_heads;
   float scale;
   int flavour;
-  int splits, pages_per_split, split_base, total_splits;
+  // Work split: one unit = four consecutive pages of one (batch, kv head) (one page per warp pair); the units of
+  // all (batch, kv head) rows, `quads` each, are dealt out evenly to `stream_blocks` blocks, so a block may finish
+  // one row and start the next.  Partial slot 0 of a row belongs to its dense-token block, slot 1 + k to the
+  // k-th stream block that touches the row.
+  int quads, stream_blocks;
+  long long units;
+  int total_splits;
   float* part_m;
   float* part_l;
   float* part_acc;
@@ -199,9 +205,8 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 // Block merge of the eight warp states: thread = (channel, head parity); partials leave in natural-log units.
 template <class BS>
 __device__ __forceinline__ void block_merge(const FastArgs& a, const BS& bs, const float* warp_out, int b, int hkv, int rep,
-                                            int split) {
+                                            int slot) {
   const int tid = threadIdx.x;
-  const int slot = a.split_base + split;
   const int ch = tid & 127;
   for (int r = tid >> 7; r < rep; r += kThreads / 128) {
     float m = -INFINITY;
