@@ -9,6 +9,9 @@
 // This file holds the generic kernel (any page geometry, bit width, dtype; CUDA-core fp32 math)
 // and the merge; the tensor-core kernel for the headline geometry is in decode_fast.cu.
 
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 
 #define GEN_THREADS 128
@@ -314,10 +317,18 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
       const long long min_share = (L.quads + 14) / 15;
       long long blocks = resident;
       if (blocks > L.units / min_share) blocks = L.units / min_share;
-      if (blocks >= 1 && blocks < (long long)bh * best_pieces) {
+      // DARTKV_DECODE_SPLIT=aligned | unaligned | unaligned:<blocks> overrides the model (tests exercise both
+      // families, and blocks that span several rows, with it)
+      const char* force = getenv("DARTKV_DECODE_SPLIT");
+      const bool force_unaligned = force && force[0] == 'u', force_aligned = force && force[0] == 'a';
+      if (force_unaligned && strchr(force, ':')) {
+        const long long wanted = atoll(strchr(force, ':') + 1);
+        if (wanted >= 1 && wanted < blocks) blocks = wanted;
+      }
+      if (blocks >= 1 && (blocks < (long long)bh * best_pieces || force_unaligned) && !force_aligned) {
         const double share = (double)L.units / blocks;
         const double cost = 1.08 * (share + block_fixed * (share / L.quads + 1.0)) + (double)bh * dense_cost / resident;
-        if (cost < best_cost) {
+        if (cost < best_cost || force_unaligned) {
           const long long w = L.units / blocks;   // smallest share of a block
           L.stream_blocks = (int)blocks;
           L.total_splits = (int)((L.quads + w - 2) / w + 1) + 1;

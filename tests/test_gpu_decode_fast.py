@@ -123,3 +123,10 @@ def test_full_context_properties():
     assert torch.all((got - expect.unsqueeze(2)).abs() <= expect.abs().unsqueeze(2) * 2.0 ** -7 + 1e-3)
     generic = dart.fused_dart_attention(query.float().cuda(), cache, fallback=False)
     assert torch.all((out.float() - generic).abs() <= generic.abs() * 2.0 ** -8 + 2e-5)
+
+
+@pytest.mark.parametrize("split", ["aligned", "unaligned", "unaligned:7", "unaligned:5"])
+def test_both_split_families_and_blocks_that_span_rows(split, monkeypatch):
+    # 6 (batch, kv head) rows x 3 four-page units: with 7 or 5 blocks every block's share crosses a row boundary
+    monkeypatch.setenv("DARTKV_DECODE_SPLIT", split)
+    run_case(torch.bfloat16, seed=9, batch=3, heads=2, hq=8, tokens=32 + 11 * 128 + 9, promote_ratio=0.25)

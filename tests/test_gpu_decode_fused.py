@@ -110,3 +110,9 @@ def test_unknown_flavour_is_rejected():
     cache.append(keys.cuda(), values.cuda())
     with pytest.raises(ValueError, match="unknown dequant flavour"):
         dart.fused_dart_attention(query.cuda(), cache, fallback=False, flavour=7)
+
+
+@pytest.mark.parametrize("split", ["aligned", "unaligned:7"])
+def test_both_split_families(split, monkeypatch):
+    monkeypatch.setenv("DARTKV_DECODE_SPLIT", split)
+    run_case(torch.bfloat16, seed=9, batch=3, heads=2, hq=8, tokens=32 + 11 * 128 + 9, promote_ratio=0.25)
