@@ -286,6 +286,8 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
   L.fast = 0;
   if (flavour == DARTKV_DEQUANT_PER_OP && dartkv_decode_fast_supported(d, q_dtype, query_heads)) L.fast = 1;
   if (flavour == DARTKV_DEQUANT_FUSED && dartkv_decode_fused32_supported(d, q_dtype, query_heads)) L.fast = 2;
+  // the tensor-core kernels index (row, four-page unit) pairs with 32 bits
+  if (L.fast && (long long)bh * ((max(1, (tokens - d->sink_tokens) / d->page_size) + 3) / 4) >= (1ll << 31)) L.fast = 0;
   if (L.fast) {
     // One unit = four consecutive pages of a (batch, kv head) (a block hands them to its four warp pairs).  The
     // units of all rows are dealt out evenly to `stream_blocks` blocks.  Two families of splits are compared with a

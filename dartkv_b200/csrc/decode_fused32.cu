@@ -290,8 +290,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
 
   // ---- stream block: an even share of all (row, four-page unit) work, possibly spanning several rows
   const int sb = blockIdx.x;
-  int64_t unit = (int64_t)sb * a.units / a.stream_blocks;
-  const int64_t unit_end = (int64_t)(sb + 1) * a.units / a.stream_blocks;
+  int unit = (int)((int64_t)sb * a.units / a.stream_blocks);   // the host keeps the unit count below 2^31
+  const int unit_end = (int)((int64_t)(sb + 1) * a.units / a.stream_blocks);
   const int pair = warp >> 1, hf = warp & 1;
   FusedPairSmem& ps = psm_all[pair];
   const int k_end = d.state[2], v_end = d.state[3], sink_filled = d.state[4];
@@ -329,12 +329,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
   int iter = 0;   // pages this pair has consumed so far: stage and barrier parity carry over from row to row
 
   while (unit < unit_end) {
-    bh = (int)(unit / a.quads);
-    const int quad_begin = (int)(unit - (int64_t)bh * a.quads);
-    const int quad_count = (int)min((int64_t)(a.quads - quad_begin), unit_end - unit);
+    bh = unit / a.quads;
+    const int quad_begin = unit - bh * a.quads;
+    const int quad_count = min(a.quads - quad_begin, unit_end - unit);
     unit += quad_count;
-    const int b = bh / d.kv_heads, hkv = bh % d.kv_heads;
-    const int slot = 1 + sb - dartkv_block_of_unit((int64_t)bh * a.quads, a.stream_blocks, a.units);
     const int p_begin = 4 * quad_begin;
     const int p_end = min(4 * (quad_begin + quad_count), total_pages);
 
@@ -348,6 +346,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
 
     // query as fp32 and its largest magnitude (bounds the page weights q*s)
     {
+      const int b = bh / d.kv_heads, hkv = bh % d.kv_heads;
       float amax = 0.0f;
       for (int i = tid; i < 4 * 128; i += kThreads) {
         const int r = i >> 7, ch = i & 127;
@@ -470,7 +469,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
         }
     }
     __syncthreads();
-    block_merge(a, bs, warp_out, b, hkv, rep, slot);
+    block_merge(a, bs, warp_out, bh / d.kv_heads, bh % d.kv_heads, rep,
+                1 + sb - dartkv_block_of_unit((int64_t)bh * a.quads, a.stream_blocks, a.units));
     __syncthreads();   // the merge buffer is staging memory again, the query table may be overwritten
   }
   if (!ok && lane == 0) atomicExch(a.status, 1);
