@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import ctypes
 from dataclasses import dataclass
-from typing import TYPE_CHECKING, List, Optional, Tuple, Union
+from typing import TYPE_CHECKING, List, Optional, Sequence, Tuple, Union
 
 import torch
 
@@ -580,6 +580,34 @@ class DartKVCache:
                          "page_tokens", "state"):
                 setattr(self._desc, name, self._pools[name].data_ptr())
             self._workspace = None
+        self._layout_version += 1
+        self._invalidate_page_descriptors()
+        return self
+
+    def reorder_batch(self, batch_indices: torch.Tensor | Sequence[int]) -> "DartKVCache":
+        """Select / permute batch rows in place: ``row i <- row batch_indices[i]`` (beam search reorder).
+
+        Every pool is indexed along its batch dimension on the device; packed pages, scales and
+        zero points move as bytes, so nothing is dequantized or quantized again (the reference's
+        ``DartPageTable.reorder`` describes the same permutation, ``page_table.py:148-165``).
+        The number of rows may change; page metadata is shared by all rows and stays as it is.
+        """
+
+        if self._desc is None:
+            return self
+        indices = torch.as_tensor(batch_indices, dtype=torch.long, device=self._device).reshape(-1)
+        if indices.numel() == 0:
+            raise ValueError("batch_indices must not be empty")
+        batch = self._desc.batch
+        if int(indices.min()) < 0 or int(indices.max()) >= batch:
+            raise IndexError(f"batch_indices must lie in [0, {batch})")
+        with device_guard(self._device):
+            for name in ("k_sink", "v_sink", "k_ring", "v_ring", "k_pages", "v_codes", "v_meta"):
+                self._pools[name] = self._pools[name].index_select(0, indices)
+                setattr(self._desc, name, self._pools[name].data_ptr())
+        self._desc.batch = int(indices.numel())
+        self._shape = (self._desc.batch, self._shape[1], self._shape[2])
+        self._workspace = None
         self._layout_version += 1
         self._invalidate_page_descriptors()
         return self

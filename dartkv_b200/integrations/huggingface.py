@@ -105,9 +105,16 @@ class DartHFCache(Cache):
         layer = self._layers.get(layer_idx)
         return layer.page_runs(device=device, rebuild=rebuild) if layer is not None else None
 
-    def reorder_cache(self, beam_idx: torch.LongTensor) -> "DartHFCache":
-        """Rebuild the selected beams from the dequantized contents (reference huggingface.py:117-127)."""
+    def reorder_cache(self, beam_idx: torch.LongTensor, *, requantize: bool = True) -> "DartHFCache":
+        """Select beams.  ``requantize=True`` (default) rebuilds them from the dequantized contents like the
+        reference (huggingface.py:117-127); ``requantize=False`` permutes the packed pools on the device
+        instead, which keeps every packed byte and costs one gather per pool."""
 
+        if not requantize:
+            for layer in self._layers.values():
+                layer.reorder_batch(beam_idx)
+            self._last_update_prefill.clear()
+            return self
         for layer_idx, layer in list(self._layers.items()):
             keys, values = layer.get()
             indices = beam_idx.to(keys.device)

@@ -352,3 +352,77 @@ def test_pools_grow_without_changing_contents():
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
     q = torch.randn(1, 4, 1, 16, dtype=torch.float16).cuda()
     assert torch.equal(dart.fused_dart_attention(q, small), dart.fused_dart_attention(q, big))
+
+
+def test_reorder_batch_moves_packed_rows_without_requantizing():
+    """Beam reorder on the device pools: bytes of the selected rows are unchanged, attention follows the rows."""
+    import dartkv_b200 as dart
+    from dartkv_b200.synthetic import make_kvq
+
+    keys, values, query = make_kvq(21, 3, 2, 32 + 3 * 128 + 17, 128, query_heads=8, dtype=torch.bfloat16)
+    cfg = dart.DartKVCacheConfig(bits=2, promote_ratio=0.25, page_size=128, key_group_size=128, value_group_size=64,
+                                 sink_tokens=32, hold_partial_pages=True, metadata_dtype=torch.bfloat16)
+    cache = dart.DartKVCache(cfg)
+    cache.append(keys.cuda(), values.cuda())
+    before = dart.fused_dart_attention(query.cuda(), cache, fallback=False)
+    k_before, v_before = cache.get()
+    order = [2, 0, 2, 1]
+    cache.reorder_batch(order)
+    assert cache.shape[0] == 4
+    k_after, v_after = cache.get()
+    index = torch.tensor(order, device="cuda")
+    assert torch.equal(k_after, k_before.index_select(0, index))
+    assert torch.equal(v_after, v_before.index_select(0, index))
+    after = dart.fused_dart_attention(query.cuda().index_select(0, index), cache, fallback=False)
+    assert torch.equal(after, before.index_select(0, index))
+    # appends keep working on the reordered rows
+    more_k, more_v, _ = make_kvq(22, 4, 2, 130, 128, query_heads=8, dtype=torch.bfloat16)
+    cache.append(more_k.cuda(), more_v.cuda())
+    assert cache.seen_tokens == 32 + 3 * 128 + 17 + 130
+    with pytest.raises(IndexError):
+        cache.reorder_batch([0, 7])
+
+
+def test_append_reads_projection_layout_without_a_copy():
+    """Keys/values that live as [B, T, H, D] (projection output) are appended through a transposed view."""
+    import dartkv_b200 as dart
+
+    torch.manual_seed(5)
+    b, t, h, d = 2, 32 + 2 * 128 + 40, 4, 128
+    k_bthd = torch.randn(b, t, h, d, device="cuda", dtype=torch.bfloat16)
+    v_bthd = torch.randn(b, t, h, d, device="cuda", dtype=torch.bfloat16)
+    cfg = dart.DartKVCacheConfig(bits=2, promote_ratio=0.25, page_size=128, key_group_size=128, value_group_size=64,
+                                 sink_tokens=32, hold_partial_pages=True, metadata_dtype=torch.bfloat16)
+    strided, dense = dart.DartKVCache(cfg), dart.DartKVCache(cfg)
+    k_view, v_view = k_bthd.transpose(1, 2), v_bthd.transpose(1, 2)
+    assert not k_view.is_contiguous()
+    strided.append(k_view, v_view)
+    dense.append(k_view.contiguous(), v_view.contiguous())
+    for (ks, vs), (kd, vd) in zip(strided.iter_segments(), dense.iter_segments()):
+        for a, c in ((ks, kd), (vs, vd)):
+            if isinstance(a, torch.Tensor):
+                assert torch.equal(a, c)
+            else:
+                assert torch.equal(a.scale, c.scale) and torch.equal(a.zero_point, c.zero_point)
+                fields = ("low_values", "high_values", "channel_indices") if hasattr(a, "low_values") else ("values",)
+                for name in fields:
+                    assert torch.equal(getattr(a, name), getattr(c, name))
+
+
+def test_hf_cache_reorder_without_requantizing():
+    import dartkv_b200 as dart
+    from dartkv_b200.integrations import DartHFCache
+
+    torch.manual_seed(6)
+    cfg = dart.DartKVCacheConfig(bits=2, promote_ratio=0.25, page_size=128, key_group_size=128, value_group_size=64,
+                                 sink_tokens=32, hold_partial_pages=True, metadata_dtype=torch.bfloat16)
+    hf = DartHFCache(cfg)
+    k = torch.randn(3, 2, 300, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn_like(k)
+    hf.update(k, v, 0)
+    keys_before, values_before = hf._layers[0].get()
+    hf.reorder_cache(torch.tensor([1, 1, 0], device="cuda"), requantize=False)
+    keys_after, values_after = hf._layers[0].get()
+    index = torch.tensor([1, 1, 0], device="cuda")
+    assert torch.equal(keys_after, keys_before.index_select(0, index))
+    assert torch.equal(values_after, values_before.index_select(0, index))
