@@ -3,15 +3,17 @@
 // 32 promoted 2+2-bit channels), 16-bit data whose metadata has the same dtype, up to 4 query heads
 // per KV head.  Everything else takes the generic kernel in decode_attention.cu.
 //
-// Work split: grid (batch*kv_heads, splits + 1).  A block of 8 warps (4 warp pairs) owns a run of
-// consecutive packed pages; page p of the run goes to pair p % 4.  A pair streams its pages through a
-// two-stage shared-memory ring filled by 1-D bulk async copies (one key blob of up to 5760 bytes,
-// 4096 bytes of value codes and up to 1024 bytes of value metadata per page, completion on an
-// mbarrier).  The two warps of a pair split the page's tokens (codes 0-3 / 4-7 of every packed
-// 16-bit half, i.e. 64 tokens each) and keep private online-softmax states, so they only meet at two
-// named barriers per page; the block merges all eight states at the end.  The extra block
-// (blockIdx.y == splits) handles the dense tokens: the sink prefix and everything after the last
-// page that is packed on both the key and the value side.
+// Work split: one unit = four consecutive pages of a (batch, kv head) row.  The units of all rows are dealt out
+// evenly to the stream blocks (aligned to rows, or one block per resident slot whose share may run from one
+// row into the next; the host chooses).  A block of 8 warps (4 warp pairs) hands page p of its run to pair
+// p % 4.  A pair streams its pages through a two-stage shared-memory ring filled by 1-D bulk async copies
+// (one key blob of up to 5760 bytes, 4096 bytes of value codes and up to 1024 bytes of value metadata per
+// page, completion on an mbarrier).  The two warps of a pair split the page's tokens (codes 0-3 / 4-7 of
+// every packed 16-bit half, i.e. 64 tokens each) and keep private online-softmax states, so they only meet
+// at two named barriers per page; the block merges all eight states when it leaves a row and writes one
+// partial per row it touched.  One more short block per row, launched after the stream blocks, handles the
+// dense tokens: the sink prefix and everything after the last page that is packed on both the key and the
+// value side.
 //
 // Per page a warp never materializes K or V: packed 2-bit codes are turned into exactly rounded
 // 16-bit operands with one logic op and two packed fma/add per pair (mma_utils.cuh) and fed straight
