@@ -52,8 +52,10 @@ template <int DT>
 __device__ __forceinline__ float rnd16(float x) { return Half2Ops<DT>::to_float(Half2Ops<DT>::from_float(x)); }
 
 // ------------------------------------------------------------------------------------------------
-// dense tokens (sink prefix, unpacked tail, and tokens packed on one side only): one warp per token,
-// four channels per lane, fp32 math
+// dense tokens (sink prefix, unpacked tail, and tokens packed on one side only).  Tokens whose key and value rows
+// are both dense go through 16-token tiles: logits by m16n8k16 MMAs straight from the rows, probabilities
+// through a small shared table, P.V on CUDA cores with four channels per lane.  Tokens packed on one side only
+// (Kitty lifecycle) take one warp per token, four channels per lane, fp32 math.
 // BS: the kernel's block-level shared struct (needs slot_map[128], merge_m / merge_l [kWarps][4])
 template <int DT, class BS>
 __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& bs, float* warp_out, int bh) {
@@ -79,6 +81,18 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
   }
   const float scale2 = a.scale * kLog2e;
   const bool fused = a.flavour == DARTKV_DEQUANT_FUSED;
+  // MMA operand of the tiles: column n = g is query head g (zero past the last head), two channels per register
+  const int g = lane >> 2, c = lane & 3;
+  uint32_t qb[8][2];
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      qb[ks][j] = g < rep ? *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(a.q) +
+                                ((int64_t)b * a.query_heads + h * rep + g) * 128 + 16 * ks + 8 * j + 2 * c)
+                          : 0u;
+  int tile_counter = 0;
+  float* ptab = warp_out + 4096 + warp * 64;   // this warp's [16 tokens][4 heads] probabilities, beyond the merge buffer
   // segments: [0, sink_filled) then [fast_end, seen) cut at key page boundaries
   int t = 0;
 #ifdef DENSE_SKIP
@@ -107,13 +121,85 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
     } else { kind = 2; seg_end = seen; }
     (void)pages;
     // dense rows of the next token are requested before the current one is consumed
-    auto dense_row = [&](const void* sink, const void* ring, int tok) -> uint2 {
-      const uint16_t* row = tok < sink_filled
+    auto dense_ptr = [&](const void* sink, const void* ring, int tok) -> const uint16_t* {
+      return tok < sink_filled
           ? reinterpret_cast<const uint16_t*>(sink) + ((int64_t)bh * d.sink_tokens + tok) * 128
           : reinterpret_cast<const uint16_t*>(ring) + ((int64_t)bh * d.ring_tokens + (tok % d.ring_tokens)) * 128;
-      return *reinterpret_cast<const uint2*>(row + lane * 4);
+    };
+    auto dense_row = [&](const void* sink, const void* ring, int tok) -> uint2 {
+      return *reinterpret_cast<const uint2*>(dense_ptr(sink, ring, tok) + lane * 4);
     };
     auto value_dense = [&](int tok) { return !(tok >= sink_filled && tok < v_end); };
+    // [tile_from, seg_end): key and value rows both dense -> tiles; [t, tile_from): per-token path below
+    const int tile_from = kind == 1 ? seg_end : (kind == 0 ? t : min(seg_end, max(t, v_end)));
+    for (int tile = tile_from; tile < seg_end; tile += 16) {
+      if ((tile_counter++ & (kWarps - 1)) != warp) continue;   // tiles of all segments go round the warps
+      const int last = seg_end - 1;
+      const uint8_t* k0 = reinterpret_cast<const uint8_t*>(dense_ptr(d.k_sink, d.k_ring, min(tile + g, last))) + 4 * c;
+      const uint8_t* k1 = reinterpret_cast<const uint8_t*>(dense_ptr(d.k_sink, d.k_ring, min(tile + g + 8, last))) + 4 * c;
+      float s_acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        H::mma(s_acc, *reinterpret_cast<const uint32_t*>(k0 + 32 * ks), *reinterpret_cast<const uint32_t*>(k1 + 32 * ks),
+               *reinterpret_cast<const uint32_t*>(k0 + 32 * ks + 16), *reinterpret_cast<const uint32_t*>(k1 + 32 * ks + 16),
+               qb[ks][0], qb[ks][1]);
+      // the value rows of the whole tile are requested now; the softmax below hides their latency
+      uint2 v_rows[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v_rows[j] = dense_row(d.v_sink, d.v_ring, min(tile + j, last));
+      // s_acc: tokens tile+g (0,1) and tile+g+8 (2,3), heads 2c and 2c+1
+      const bool live0 = tile + g < seg_end, live1 = tile + g + 8 < seg_end;
+      float sv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sv[i] = ((i < 2) ? live0 : live1) ? s_acc[i] * scale2 : -INFINITY;
+      float mt0 = fmaxf(sv[0], sv[2]), mt1 = fmaxf(sv[1], sv[3]);
+#pragma unroll
+      for (int off = 4; off < 32; off <<= 1) {
+        mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, off));
+        mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, off));
+      }
+      // every lane needs the tile maxima of heads 0..3: heads 0,1 sit in lanes c = 0, heads 2,3 in lanes c = 1
+      float m_tile[4];
+      m_tile[0] = __shfl_sync(0xffffffffu, mt0, 0); m_tile[1] = __shfl_sync(0xffffffffu, mt1, 0);
+      m_tile[2] = __shfl_sync(0xffffffffu, mt0, 1); m_tile[3] = __shfl_sync(0xffffffffu, mt1, 1);
+      float alpha[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float m_new = fmaxf(m[r], m_tile[r]);
+        alpha[r] = fast_exp2(m[r] - m_new);
+        m[r] = m_new;
+      }
+      if (c < 2) {
+        const float ma = c == 0 ? m[0] : m[2], mb = c == 0 ? m[1] : m[3];
+        *reinterpret_cast<float2*>(ptab + 4 * g + 2 * c) = make_float2(fast_exp2(sv[0] - ma), fast_exp2(sv[1] - mb));
+        *reinterpret_cast<float2*>(ptab + 4 * (g + 8) + 2 * c) = make_float2(fast_exp2(sv[2] - ma), fast_exp2(sv[3] - mb));
+      }
+      __syncwarp();
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        l[r] *= alpha[r];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[r][i] *= alpha[r];
+      }
+      // tokens past the end of the segment have probability zero
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const uint2 v_raw = v_rows[j];
+        const float4 pj = *reinterpret_cast<const float4*>(ptab + 4 * j);
+        const float vv[4] = {H::to_float((uint16_t)(v_raw.x & 0xFFFF)), H::to_float((uint16_t)(v_raw.x >> 16)),
+                             H::to_float((uint16_t)(v_raw.y & 0xFFFF)), H::to_float((uint16_t)(v_raw.y >> 16))};
+        const float pr[4] = {pj.x, pj.y, pj.z, pj.w};
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          l[r] += pr[r];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[r][i] = fmaf(pr[r], vv[i], acc[r][i]);
+        }
+      }
+      __syncwarp();   // the table is rewritten by the next tile
+    }
+    const int seg_stop = seg_end;
+    seg_end = tile_from;   // what is left for the per-token path
     uint2 k_next = make_uint2(0, 0), v_next = make_uint2(0, 0);
     {
       const int first = t + warp;
@@ -184,7 +270,7 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
         for (int i = 0; i < 4; ++i) acc[r][i] = acc[r][i] * alpha + p * vv[i];
       }
     }
-    t = seg_end;
+    t = seg_stop;
   }
   // hand the warp state to the block merge: acc in channel order
 #pragma unroll

@@ -499,11 +499,20 @@ int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, 
   (void)q_dtype;
   FastArgs a{query, query_heads, scale, flavour, quads, stream_blocks, units, total_splits, part_m, part_l, part_acc, status};
   dim3 grid(stream_blocks + d->batch * d->kv_heads);
+  {
+    // the shared-memory opt-in is per device and per kernel: ask once
+    static bool ready[64] = {};
+    int device = 0;
+    DARTKV_CUDA_OK(cudaGetDevice(&device));
+    if (device < 0 || device >= 64 || !ready[device]) {
+      DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fused32_kernel<DARTKV_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmemBytes));
+      DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fused32_kernel<DARTKV_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmemBytes));
+      if (device >= 0 && device < 64) ready[device] = true;
+    }
+  }
   if (d->dtype == DARTKV_BF16) {
-    DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fused32_kernel<DARTKV_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmemBytes));
     decode_fused32_kernel<DARTKV_BF16><<<grid, kThreads, kFusedSmemBytes, stream>>>(*d, a);
   } else {
-    DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fused32_kernel<DARTKV_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmemBytes));
     decode_fused32_kernel<DARTKV_F16><<<grid, kThreads, kFusedSmemBytes, stream>>>(*d, a);
   }
   DARTKV_LAUNCH_OK("decode_fused32_kernel");
