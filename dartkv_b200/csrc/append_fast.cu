@@ -18,16 +18,6 @@ namespace {
 constexpr int kD = 128;
 constexpr int kP = 128;
 
-template <int DT> struct Elem;
-template <> struct Elem<DARTKV_F16> {
-  using type = __half;
-  static __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
-};
-template <> struct Elem<DARTKV_BF16> {
-  using type = __nv_bfloat16;
-  static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
-};
-
 struct RowSource {
   const void* chunk;
   const void* ring;
@@ -42,14 +32,6 @@ struct RowSource {
   __device__ __forceinline__ const uint16_t* row_from(const uint16_t* chunk_base, const uint16_t* ring_base, int t) const {
     if (t >= chunk_start) return chunk_base + (int64_t)(t - chunk_start) * st;
     return ring_base + (t % ring_tokens) * kD;
-  }
-  // 16-bit elements; rows are head_dim contiguous elements
-  __device__ __forceinline__ const uint16_t* row(int bh, int t) const {
-    if (t >= chunk_start) {
-      int b = bh / kv_heads, h = bh % kv_heads;
-      return reinterpret_cast<const uint16_t*>(chunk) + (int64_t)b * sb + (int64_t)h * sh + (int64_t)(t - chunk_start) * st;
-    }
-    return reinterpret_cast<const uint16_t*>(ring) + ((int64_t)bh * ring_tokens + (t % ring_tokens)) * kD;
   }
 };
 

@@ -282,7 +282,6 @@ static int dartkv_sm_count() {
 static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int query_heads, int flavour, int tokens) {
   DecodeLayout L{};
   const int bh = d->batch * d->kv_heads;
-  const int target_blocks = 148 * 8;   // two resident blocks per SM, about four waves
   L.fast = 0;
   if (flavour == DARTKV_DEQUANT_PER_OP && dartkv_decode_fast_supported(d, q_dtype, query_heads)) L.fast = 1;
   if (flavour == DARTKV_DEQUANT_FUSED && dartkv_decode_fused32_supported(d, q_dtype, query_heads)) L.fast = 2;

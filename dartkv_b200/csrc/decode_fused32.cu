@@ -276,7 +276,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
   const int rep = a.query_heads / d.kv_heads;
-  const int rows = d.batch * d.kv_heads;
 
   if ((int)blockIdx.x >= a.stream_blocks) {
     // dense tokens of one (batch, kv head): partial slot 0.  These short blocks come last in launch order and fill
