@@ -219,6 +219,9 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cach
 __global__ void decode_merge_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
                                     const float* __restrict__ part_acc, int total_splits, int D, void* out, int out_dt,
                                     int stream_blocks, int64_t units, int quads, int query_heads, int kv_heads) {
+  // launched with programmatic stream serialization: the grid may become resident while the kernel before it
+  // drains, and waits here until that kernel's memory is visible
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   int64_t row = blockIdx.x;
   int splits = total_splits;
   if (stream_blocks > 0) {
@@ -416,9 +419,20 @@ extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* q
     decode_generic_kernel<<<dim3(bh, L.generic_splits), GEN_THREADS, smem, stream>>>(*d, a);
     DARTKV_LAUNCH_OK("decode_generic_kernel");
   }
-  decode_merge_kernel<<<(unsigned)((int64_t)d->batch * query_heads), 128, 0, stream>>>(
-      part_m, part_l, part_acc, L.total_splits, D, out, q_dtype, L.fast ? L.stream_blocks : 0, L.units, L.quads, query_heads,
-      d->kv_heads);
+  {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)((int64_t)d->batch * query_heads));
+    config.blockDim = dim3(128);
+    config.stream = stream;
+    cudaLaunchAttribute attribute = {};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    DARTKV_CUDA_OK(cudaLaunchKernelEx(&config, decode_merge_kernel, (const float*)part_m, (const float*)part_l,
+                                      (const float*)part_acc, L.total_splits, D, out, q_dtype,
+                                      L.fast ? L.stream_blocks : 0, (int64_t)L.units, L.quads, query_heads, d->kv_heads));
+  }
   DARTKV_LAUNCH_OK("decode_merge_kernel");
   return DARTKV_OK;
 }
