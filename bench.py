@@ -323,9 +323,9 @@ def gpu_arm(args, wl) -> None:
     peak, peak_kind = measured_peak_gbs()
     achieved = local_bytes / (kernel_ms * 1e-3) / 1e9
     # DRAM traffic of one decode launch from the ncu capture of config 3 (profiles/decode_fast_kernel_config3.md):
-    # 192.72 MB read + 4.59 MB written for 192.77 MB algorithmic; traffic grows with the pages processed, so
+    # 192.72 MB read + 6.54 MB written for 192.77 MB algorithmic; traffic grows with the pages processed, so
     # other workloads scale it by their algorithmic bytes
-    traffic = int(round(local_bytes * (192.72e6 + 4.59e6) / 192774144))
+    traffic = int(round(local_bytes * (192.72e6 + 6.54e6) / 192774144))
 
     # end to end through host buffers: pinned query -> device, attention, output -> pinned host
     host_q = q3.cpu().pin_memory()
