@@ -100,8 +100,8 @@ struct WarpState {
 
 // One warp's share of a staged page.  HF: which four codes of every 16-bit half this warp owns;
 // GN: value groups per token (1 or 2).
-template <int DT, int HF, int GN>
-__device__ __forceinline__ void fused_page_half(const dartkv_cache_desc& d, FusedPairSmem& ps, const uint8_t* blob,
+template <int DT, int GN>
+__device__ __forceinline__ void fused_page_half(const int HF, const dartkv_cache_desc& d, FusedPairSmem& ps, const uint8_t* blob,
                                                 uint32_t* utab, int prom_steps, float scale2, float f_inv, int g, int c,
                                                 uint32_t sel_w, uint32_t mask_u, WarpState& st) {
   // ---- logits: S[token pair][(head, j')] over the doubled contraction (channel, j).  Row g of m-tile mt
@@ -120,7 +120,7 @@ __device__ __forceinline__ void fused_page_half(const dartkv_cache_desc& d, Fuse
     for (int ks = 0; ks < 16; ++ks) {
       uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + 256 * ks);
       uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + 256 * ks + 128);
-      if (HF == 1) { w0 >>= 8; w1 >>= 8; }
+      w0 >>= 8 * HF; w1 >>= 8 * HF;   // HF is a run-time value: one copy of this code serves both warps of a pair
       const uint32_t b0 = prmt(*reinterpret_cast<const uint32_t*>(w_thread + 64 * ks), 0u, sel_w);
       const uint32_t b1 = prmt(*reinterpret_cast<const uint32_t*>(w_thread + 64 * ks + 32), 0u, sel_w);
 #pragma unroll
@@ -134,7 +134,7 @@ __device__ __forceinline__ void fused_page_half(const dartkv_cache_desc& d, Fuse
     for (int ks = 0; ks < prom_steps; ++ks) {
       uint32_t w0 = *reinterpret_cast<const uint32_t*>(high_thread + 256 * ks);
       uint32_t w1 = *reinterpret_cast<const uint32_t*>(high_thread + 256 * ks + 128);
-      if (HF == 1) { w0 >>= 8; w1 >>= 8; }
+      w0 >>= 8 * HF; w1 >>= 8 * HF;   // HF is a run-time value: one copy of this code serves both warps of a pair
       const uint32_t b0 = prmt(*reinterpret_cast<const uint32_t*>(wh_thread + 64 * ks), 0u, sel_w);
       const uint32_t b1 = prmt(*reinterpret_cast<const uint32_t*>(wh_thread + 64 * ks + 32), 0u, sel_w);
 #pragma unroll
@@ -432,11 +432,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
       pair_barrier(pair);
 
       if (d.value_groups == 2) {
-        if (hf == 0) fused_page_half<DT, 0, 2>(d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
-        else fused_page_half<DT, 1, 2>(d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
+        fused_page_half<DT, 2>(hf, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
       } else {
-        if (hf == 0) fused_page_half<DT, 0, 1>(d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
-        else fused_page_half<DT, 1, 1>(d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
+        fused_page_half<DT, 1>(hf, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
       }
 
       pair_barrier(pair);
