@@ -46,12 +46,15 @@ struct BlockSmem {
 
 // One warp's share of a staged page: QK over its 64 tokens, online softmax, PV over the same tokens.
 // GN = value groups per token (1 or 2).
-template <int DT, int HF, int GN>
-__device__ __forceinline__ void page_half(const dartkv_cache_desc& d, PairSmem& ps, const uint8_t* blob, uint16_t* prob,
+template <int DT, int GN>
+__device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc& d, PairSmem& ps, const uint8_t* blob, uint16_t* prob,
                                           const uint8_t* q_thread, const CodeConsts<DT>& cc, int K, int prom_steps,
                                           float scale2, int g, int c, int jp, int hq, int gv, float (&o_acc)[4][4],
                                           float& m_run, float& l_run) {
   using H = Half2Ops<DT>;
+  // HF is a run-time value, so one copy of this code serves both warps of a pair: the second warp shifts its four
+  // codes of every half-word down into the place of the first warp's
+  const int half_shift = 8 * HF;
   const uint8_t* low_thread = blob + 4 * g;   // + 32 * channel = this thread's word of the channel row
   const uint32_t* high = reinterpret_cast<const uint32_t*>(blob + d.key_off_high);
 
@@ -74,8 +77,8 @@ __device__ __forceinline__ void page_half(const dartkv_cache_desc& d, PairSmem& 
     const uint32_t h0 = s0 < K ? high[s0 * 8 + g] : 0u;
     const uint32_t h1 = s1 < K ? high[s1 * 8 + g] : 0u;
     uint32_t r0[4], r1[4];
-    dequant_half4<DT, HF>(cc, w0, h0, a0.x, a0.y, a0.z, a0.w, r0);
-    dequant_half4<DT, HF>(cc, w1, h1, a1.x, a1.y, a1.z, a1.w, r1);
+    dequant_half4<DT, 0>(cc, w0 >> half_shift, h0 >> half_shift, a0.x, a0.y, a0.z, a0.w, r0);
+    dequant_half4<DT, 0>(cc, w1 >> half_shift, h1 >> half_shift, a1.x, a1.y, a1.z, a1.w, r1);
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
     if (ks & 1) {
@@ -95,8 +98,8 @@ __device__ __forceinline__ void page_half(const dartkv_cache_desc& d, PairSmem& 
     const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
     const uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + o1.y);
     uint32_t r0[4], r1[4];
-    dequant_half2<DT, HF>(cc, w0, a0.x, a0.y, a0.z, a0.w, o0.x, r0);
-    dequant_half2<DT, HF>(cc, w1, a1.x, a1.y, a1.z, a1.w, o1.x, r1);
+    dequant_half2<DT, 0>(cc, w0 >> half_shift, a0.x, a0.y, a0.z, a0.w, o0.x, r0);
+    dequant_half2<DT, 0>(cc, w1 >> half_shift, a1.x, a1.y, a1.z, a1.w, o1.x, r1);
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
 #pragma unroll
@@ -112,8 +115,8 @@ __device__ __forceinline__ void page_half(const dartkv_cache_desc& d, PairSmem& 
       const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
       const uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + o1.y);
       uint32_t r0[4], r1[4];
-      dequant_half2<DT, HF>(cc, w0, a0.x, a0.y, a0.z, a0.w, o0.x, r0);
-      dequant_half2<DT, HF>(cc, w1, a1.x, a1.y, a1.z, a1.w, o1.x, r1);
+      dequant_half2<DT, 0>(cc, w0 >> half_shift, a0.x, a0.y, a0.z, a0.w, o0.x, r0);
+      dequant_half2<DT, 0>(cc, w1 >> half_shift, a1.x, a1.y, a1.z, a1.w, o1.x, r1);
       const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
       const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
 #pragma unroll
@@ -353,15 +356,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       pair_barrier(pair);
 
       if (d.value_groups == 2) {
-        if (hf == 0)
-          page_half<DT, 0, 2>(d, ps, blob, ps.prob[0], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
-        else
-          page_half<DT, 1, 2>(d, ps, blob, ps.prob[1], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
+        page_half<DT, 2>(hf, d, ps, blob, ps.prob[hf], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
       } else {
-        if (hf == 0)
-          page_half<DT, 0, 1>(d, ps, blob, ps.prob[0], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
-        else
-          page_half<DT, 1, 1>(d, ps, blob, ps.prob[1], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
+        page_half<DT, 1>(hf, d, ps, blob, ps.prob[hf], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
       }
 
       pair_barrier(pair);
