@@ -27,6 +27,14 @@
 
 namespace {
 
+#ifndef PEROP_QK_UNROLL
+#define PEROP_QK_UNROLL 2
+#endif
+#ifndef PEROP_PV_UNROLL
+#define PEROP_PV_UNROLL 2
+#endif
+constexpr int kQkUnroll = PEROP_QK_UNROLL, kPvUnroll = PEROP_PV_UNROLL;
+
 struct PairSmem {
   uint8_t stage[2][kStageBytes];
   uint4 kpar_a[128];      // by contraction position: (s,s) (z,z) -magic0*s -magic1*s of that position's channel
@@ -81,18 +89,18 @@ __device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc&
     dequant_half4<DT, 0>(cc, w1 >> half_shift, h1 >> half_shift, a1.x, a1.y, a1.z, a1.w, r1);
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
+#ifndef PEROP_SINGLE_ACC
     if (ks & 1) {
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[1][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
-    } else {
+    } else
+#endif
+    {
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[0][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
     }
   }
-  // one plain step, if needed, to put the unrolled loop on an even step index
-  const int first_plain = prom_steps + (prom_steps & 1);
-#pragma unroll 1
-  for (int ks = prom_steps; ks < first_plain && ks < 16; ++ks) {
+  auto plain_step = [&](int ks, float (&acc)[2][4]) {
     const uint4 a0 = ps.kpar_a[8 * ks + c], a1 = ps.kpar_a[8 * ks + c + 4];
     const uint2 o0 = ps.kpar_b[8 * ks + c], o1 = ps.kpar_b[8 * ks + c + 4];
     const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
@@ -103,26 +111,21 @@ __device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc&
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[1][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
-  }
-#pragma unroll 2
+    for (int mt = 0; mt < 2; ++mt) H::mma(acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+  };
+#ifdef PEROP_SINGLE_ACC
+#pragma unroll kQkUnroll
+  for (int ks = prom_steps; ks < 16; ++ks) plain_step(ks, s_acc[0]);
+#else
+  // one plain step, if needed, to put the unrolled loop on an even step index
+  const int first_plain = prom_steps + (prom_steps & 1);
+  if (first_plain != prom_steps && prom_steps < 16) plain_step(prom_steps, s_acc[1]);
+#pragma unroll kQkUnroll
   for (int kp = first_plain; kp < 16; kp += 2) {
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int ks = kp + e;
-      const uint4 a0 = ps.kpar_a[8 * ks + c], a1 = ps.kpar_a[8 * ks + c + 4];
-      const uint2 o0 = ps.kpar_b[8 * ks + c], o1 = ps.kpar_b[8 * ks + c + 4];
-      const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
-      const uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + o1.y);
-      uint32_t r0[4], r1[4];
-      dequant_half2<DT, 0>(cc, w0 >> half_shift, a0.x, a0.y, a0.z, a0.w, o0.x, r0);
-      dequant_half2<DT, 0>(cc, w1 >> half_shift, a1.x, a1.y, a1.z, a1.w, o1.x, r1);
-      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
-      const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[e][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
-    }
+    plain_step(kp, s_acc[0]);
+    plain_step(kp + 1, s_acc[1]);
   }
+#endif
 
   // ---- online softmax for head c over this warp's 64 tokens (this thread: 8 of them)
   float mx = -INFINITY;
@@ -182,7 +185,7 @@ __device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc&
   // byte selectors that duplicate the scale / zero of this thread's value group into both halves
   const uint32_t sel_s = GN == 2 ? (gv ? 0x3232u : 0x1010u) : 0x1010u;
   const uint32_t sel_z = GN == 2 ? (gv ? 0x3232u : 0x1010u) : 0x3232u;
-#pragma unroll 2
+#pragma unroll kPvUnroll
   for (int ks = 0; ks < 8; ++ks) {
     const int t0 = 16 * ks + 4 * HF + c, t1 = t0 + 8;
     const uint32_t w0 = vcodes[t0 * 8], w1 = vcodes[t1 * 8];
