@@ -261,6 +261,9 @@ def gpu_arm(args, wl) -> None:
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     if world > 1:
+        # the only collective is a gather of [B/N, Hq, D] outputs (1 MB in total): in-switch reduction buys nothing
+        # here and its set-up dominates communicator creation on 8 GPUs
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=device)
     from dartkv_b200.sharding import shard_rows
 
