@@ -38,10 +38,12 @@ constexpr int kUStride = 36;   // 32-bit words per group of 8 local tokens in a 
 
 struct FusedPairSmem {
   uint8_t stage[2][kStageBytes];
-  uint2 w_low[128];              // per channel: fp16 q*s*f of heads (0,1) and (2,3)
-  uint2 w_high[32];              // per promoted slot: fp16 4*q*s*f of its channel, zero past the last slot
+  // per-page tables, double-buffered like the stages so that one warp of the pair may set up the next page while
+  // the other still reads this page's
+  uint2 w_low[2][128];           // per channel: fp16 q*s*f of heads (0,1) and (2,3)
+  uint2 w_high[2][32];           // per promoted slot: fp16 4*q*s*f of its channel, zero past the last slot
   uint32_t u[2][8 * kUStride];   // per warp: [local token][head] = fp16 p*s*fv of (value group 0 | group 1 << 16)
-  float bias_part[2][4];         // per warp: partial sum_ch q*z per head
+  float bias_part[2][2][4];      // [table][warp]: partial sum_ch q*z per head
   uint64_t bar[2];
 };
 
@@ -101,7 +103,7 @@ struct WarpState {
 // One warp's share of a staged page.  HF: which four codes of every 16-bit half this warp owns;
 // GN: value groups per token (1 or 2).
 template <int DT, int GN>
-__device__ __forceinline__ void fused_page_half(const int HF, const dartkv_cache_desc& d, FusedPairSmem& ps, const uint8_t* blob,
+__device__ __forceinline__ void fused_page_half(const int HF, const int tb, const dartkv_cache_desc& d, FusedPairSmem& ps, const uint8_t* blob,
                                                 uint32_t* utab, int prom_steps, float scale2, float f_inv, int g, int c,
                                                 uint32_t sel_w, uint32_t mask_u, WarpState& st) {
   // ---- logits: S[token pair][(head, j')] over the doubled contraction (channel, j).  Row g of m-tile mt
@@ -114,7 +116,7 @@ __device__ __forceinline__ void fused_page_half(const int HF, const dartkv_cache
     for (int i = 0; i < 4; ++i) s_acc[mt][i] = s_odd[mt][i] = 0.0f;
   {
     const uint8_t* low_thread = blob + 4 * g + 32 * c;                               // + 256 * step (+128)
-    const uint8_t* w_thread = reinterpret_cast<const uint8_t*>(ps.w_low) + 8 * c + 4 * (g >> 2);   // + 64 * step (+32)
+    const uint8_t* w_thread = reinterpret_cast<const uint8_t*>(ps.w_low[tb]) + 8 * c + 4 * (g >> 2);   // + 64 * step (+32)
 #ifndef FUSED_SKIP_QK
 #pragma unroll kQkUnroll
     for (int ks = 0; ks < 16; ++ks) {
@@ -130,7 +132,7 @@ __device__ __forceinline__ void fused_page_half(const int HF, const dartkv_cache
     }
     // high plane of the promoted slots
     const uint8_t* high_thread = blob + d.key_off_high + 4 * g + 32 * c;
-    const uint8_t* wh_thread = reinterpret_cast<const uint8_t*>(ps.w_high) + 8 * c + 4 * (g >> 2);
+    const uint8_t* wh_thread = reinterpret_cast<const uint8_t*>(ps.w_high[tb]) + 8 * c + 4 * (g >> 2);
     for (int ks = 0; ks < prom_steps; ++ks) {
       uint32_t w0 = *reinterpret_cast<const uint32_t*>(high_thread + 256 * ks);
       uint32_t w1 = *reinterpret_cast<const uint32_t*>(high_thread + 256 * ks + 128);
@@ -146,7 +148,7 @@ __device__ __forceinline__ void fused_page_half(const int HF, const dartkv_cache
   }
 
   // ---- online softmax for head c over this warp's 64 tokens (this thread: 8 of them)
-  const float bias = (ps.bias_part[0][c] + ps.bias_part[1][c]) * scale2;
+  const float bias = (ps.bias_part[tb][0][c] + ps.bias_part[tb][1][c]) * scale2;
   float cm[4];   // scale2 / f * 2^(24 - 2p)
   {
     const float base = scale2 * f_inv;
@@ -401,8 +403,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
         const float4 qa = *reinterpret_cast<const float4*>(bs.qf[2 * tp]);
         const float4 qb = *reinterpret_cast<const float4*>(bs.qf[2 * tp + 1]);
         const float sa = s0 * f, sb = s1 * f;
-        ps.w_low[2 * tp] = make_uint2(pack_f16x2(qa.x * sa, qa.y * sa), pack_f16x2(qa.z * sa, qa.w * sa));
-        ps.w_low[2 * tp + 1] = make_uint2(pack_f16x2(qb.x * sb, qb.y * sb), pack_f16x2(qb.z * sb, qb.w * sb));
+        ps.w_low[stage][2 * tp] = make_uint2(pack_f16x2(qa.x * sa, qa.y * sa), pack_f16x2(qa.z * sa, qa.w * sa));
+        ps.w_low[stage][2 * tp + 1] = make_uint2(pack_f16x2(qb.x * sb, qb.y * sb), pack_f16x2(qb.z * sb, qb.w * sb));
         // sum_ch q*z per head, reduced over the warp
         float bz[4] = {fmaf(qa.x, z0, qb.x * z1), fmaf(qa.y, z0, qb.y * z1), fmaf(qa.z, z0, qb.z * z1), fmaf(qa.w, z0, qb.w * z1)};
         // four sums over 32 lanes in 6 shuffles: halve the number of sums a lane carries at the first two levels
@@ -414,7 +416,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
           k += __shfl_xor_sync(0xffffffffu, k, 4);
           k += __shfl_xor_sync(0xffffffffu, k, 2);
           k += __shfl_xor_sync(0xffffffffu, k, 1);
-          if ((lane & 7) == 0) ps.bias_part[hf][lane >> 3] = k;
+          if ((lane & 7) == 0) ps.bias_part[stage][hf][lane >> 3] = k;
         }
         // promoted slots: warp 1 of the pair, lane = slot
         if (hf == 1 && prom_steps > 0) {
@@ -425,21 +427,21 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
             const float4 qh = *reinterpret_cast<const float4*>(bs.qf[ch]);
             wh = make_uint2(pack_f16x2(qh.x * s4, qh.y * s4), pack_f16x2(qh.z * s4, qh.w * s4));
           }
-          ps.w_high[lane] = wh;
+          ps.w_high[stage][lane] = wh;
         }
       }
 #endif
+      // the only meeting point of the pair per page: the tables of this page are complete and both warps are done
+      // with the page before, whose stage can take the page after this one
       pair_barrier(pair);
+      if (issuer && pg != pg0 && pg + kPairs < p_end) issue(pg + kPairs, stage ^ 1);
 
       if (d.value_groups == 2) {
-        fused_page_half<DT, 2>(hf, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
+        fused_page_half<DT, 2>(hf, stage, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
       } else {
-        fused_page_half<DT, 1>(hf, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
+        fused_page_half<DT, 1>(hf, stage, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
       }
 
-      pair_barrier(pair);
-      // the stage is free again: prefetch the page two iterations ahead
-      if (issuer && pg + 2 * kPairs < p_end) issue(pg + 2 * kPairs, stage);
     }
 
     // ---- hand the warp state to the block merge: sums over the lanes that share head c
