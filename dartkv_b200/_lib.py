@@ -28,7 +28,7 @@ EXPORTS = (
     "dartkv_last_error", "dartkv_version", "dartkv_launch_count", "dartkv_pack", "dartkv_unpack", "dartkv_quantize", "dartkv_dequantize",
     "dartkv_channel_scores", "dartkv_select_channels", "dartkv_quantize_key_mixed", "dartkv_dequantize_key_mixed",
     "dartkv_cache_geometry", "dartkv_cache_append", "dartkv_cache_materialize", "dartkv_decode_workspace_bytes",
-    "dartkv_decode_attention", "dartkv_decode_status", "dartkv_builtin_scratch_bytes",
+    "dartkv_decode_attention", "dartkv_decode_plan", "dartkv_decode_status", "dartkv_builtin_scratch_bytes",
     "dartkv_decode_attention_builtin_scratch",
 )
 
@@ -50,6 +50,15 @@ class CacheDesc(Structure):
         ("k_sink", c_void_p), ("v_sink", c_void_p), ("k_ring", c_void_p), ("v_ring", c_void_p),
         ("k_pages", c_void_p), ("v_codes", c_void_p), ("v_meta", c_void_p),
         ("page_start", c_void_p), ("page_tokens", c_void_p), ("state", c_void_p),
+    ]
+
+
+class DecodePlanInfo(Structure):
+    """Mirror of ``dartkv_decode_plan_info``."""
+
+    _fields_ = [
+        ("kernel", c_int32), ("quads", c_int32), ("stream_blocks", c_int32), ("total_splits", c_int32),
+        ("units", c_int64), ("generic_splits", c_int32), ("generic_chunk", c_int32),
     ]
 
 
@@ -92,6 +101,7 @@ def _load() -> ctypes.CDLL:
     lib.dartkv_decode_workspace_bytes.restype = c_int64
     lib.dartkv_decode_attention.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, i64, p, p]
     lib.dartkv_decode_status.argtypes = [p, POINTER(c_int), p]
+    lib.dartkv_decode_plan.argtypes = [POINTER(CacheDesc), i32, i32, i32, i32, POINTER(DecodePlanInfo)]
     lib.dartkv_builtin_scratch_bytes.restype = c_int64
     lib.dartkv_decode_attention_builtin_scratch.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, p]
     for name in EXPORTS:

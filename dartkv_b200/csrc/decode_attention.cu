@@ -371,6 +371,24 @@ extern "C" int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* d, int
   return best;
 }
 
+extern "C" int dartkv_decode_plan(const dartkv_cache_desc* d, int q_dtype, int query_heads, int flavour, int tokens,
+                                  dartkv_decode_plan_info* out) {
+  DARTKV_REQUIRE(d != nullptr && out != nullptr, "decode_plan received a null pointer");
+  DARTKV_REQUIRE(dartkv_valid_dtype(q_dtype), "query must be f32, f16 or bf16");
+  DARTKV_REQUIRE(query_heads > 0 && query_heads % d->kv_heads == 0, "query heads must be divisible by cache KV heads");
+  DARTKV_REQUIRE(tokens > 0, "cache is empty");
+  DARTKV_REQUIRE(flavour >= DARTKV_DEQUANT_PER_OP && flavour <= DARTKV_DEQUANT_FUSED, "unknown dequant flavour %d", flavour);
+  const DecodeLayout L = decode_layout(d, q_dtype, query_heads, flavour, tokens);
+  out->kernel = L.fast;
+  out->quads = L.fast ? L.quads : 0;
+  out->stream_blocks = L.fast ? L.stream_blocks : 0;
+  out->total_splits = L.total_splits;
+  out->units = L.fast ? L.units : 0;
+  out->generic_splits = L.fast ? 0 : L.generic_splits;
+  out->generic_chunk = L.fast ? 0 : L.generic_chunk;
+  return DARTKV_OK;
+}
+
 extern "C" int dartkv_decode_status(const void* workspace, int* status_out, void* stream) {
   DARTKV_REQUIRE(workspace && status_out, "decode_status received a null pointer");
   DARTKV_CUDA_OK(cudaMemcpyAsync(status_out, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));

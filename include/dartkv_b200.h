@@ -183,6 +183,22 @@ int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* desc, int query_h
 int dartkv_decode_attention(const dartkv_cache_desc* desc, const void* query, int q_dtype, int query_heads,
                             float scale, int flavour, int tokens, void* workspace, int64_t workspace_bytes,
                             void* out, void* stream);
+/* How dartkv_decode_attention would split a call; host arithmetic only, nothing is launched (no counterpart in
+ * the reference: it exists so that integrators and tests can see the plan).  kernel: 0 generic, 1 tensor-core
+ * per-op flavour, 2 tensor-core unrounded flavour.  On the tensor-core layouts one unit is four consecutive pages
+ * of a (batch, kv head) row; block j of `stream_blocks` owns units [j*units/stream_blocks, (j+1)*units/stream_blocks)
+ * and every row is touched by at most total_splits - 1 of them (plus its dense-token block). */
+typedef struct {
+  int32_t kernel;
+  int32_t quads;          /* units per row */
+  int32_t stream_blocks;
+  int32_t total_splits;   /* partial slots per (batch, query head) row of the workspace */
+  int64_t units;          /* rows * quads */
+  int32_t generic_splits; /* generic kernel only */
+  int32_t generic_chunk;
+} dartkv_decode_plan_info;
+int dartkv_decode_plan(const dartkv_cache_desc* desc, int q_dtype, int query_heads, int flavour, int tokens,
+                       dartkv_decode_plan_info* out);
 /* Copies the workspace status word to the host (synchronizes the stream): 0 = no bounded wait expired. */
 int dartkv_decode_status(const void* workspace, int* status_out, void* stream);
 
