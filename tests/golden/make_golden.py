@@ -195,7 +195,9 @@ def cache_cases(dart, out: dict) -> None:
 
 
 def main() -> None:
-    reference = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference project>")
+    reference = sys.argv[1]
     sys.path.insert(0, os.path.join(reference, "src"))
     import dart  # the reference package, unmodified
 
