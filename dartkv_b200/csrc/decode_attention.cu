@@ -298,7 +298,7 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
     // waves of two per SM; constants fitted to B200 timings):
     //   aligned    rows * s blocks, s = 1..16 pieces per row;
     //   unaligned  one block per resident slot, a block may finish one row and start the next (at most 16 blocks
-    //              touch a row); measured ~8 % slower per unit than aligned blocks, which start staggered.
+    //              touch a row); measured a few % slower per unit than aligned blocks.
     const int pages = max(1, (tokens - d->sink_tokens) / d->page_size);
     L.quads = (pages + 3) / 4;
     L.units = (long long)bh * L.quads;
@@ -331,7 +331,7 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
       }
       if (blocks >= 1 && (blocks < (long long)bh * best_pieces || force_unaligned) && !force_aligned) {
         const double share = (double)L.units / blocks;
-        const double cost = 1.08 * (share + block_fixed * (share / L.quads + 1.0)) + (double)bh * dense_cost / resident;
+        const double cost = 1.04 * (share + block_fixed * (share / L.quads + 1.0)) + (double)bh * dense_cost / resident;
         if (cost < best_cost || force_unaligned) {
           const long long w = L.units / blocks;   // smallest share of a block
           L.stream_blocks = (int)blocks;
