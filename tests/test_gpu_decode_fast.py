@@ -130,3 +130,15 @@ def test_both_split_families_and_blocks_that_span_rows(split, monkeypatch):
     # 6 (batch, kv head) rows x 3 four-page units: with 7 or 5 blocks every block's share crosses a row boundary
     monkeypatch.setenv("DARTKV_DECODE_SPLIT", split)
     run_case(torch.bfloat16, seed=9, batch=3, heads=2, hq=8, tokens=32 + 11 * 128 + 9, promote_ratio=0.25)
+
+
+@pytest.mark.parametrize("tokens", [1, 5, 31, 32, 33, 100, 159, 160, 161, 32 + 128 + 15, 32 + 2 * 128])
+def test_short_caches_with_few_or_no_packed_pages(tokens):
+    # no page at all, sink only, sink + a partial tail tile, exactly one page, a page plus a short tail
+    run_case(torch.bfloat16, seed=30 + tokens, batch=2, heads=2, hq=8, tokens=tokens, promote_ratio=0.25)
+
+
+@pytest.mark.parametrize("tokens", [7, 40, 32 + 128 + 15])
+def test_short_caches_token_by_token(tokens):
+    run_case(torch.float16, seed=50 + tokens, batch=1, heads=2, hq=4, tokens=tokens, promote_ratio=0.25,
+             chunks=[1] * tokens)

@@ -116,3 +116,8 @@ def test_unknown_flavour_is_rejected():
 def test_both_split_families(split, monkeypatch):
     monkeypatch.setenv("DARTKV_DECODE_SPLIT", split)
     run_case(torch.bfloat16, seed=9, batch=3, heads=2, hq=8, tokens=32 + 11 * 128 + 9, promote_ratio=0.25)
+
+
+@pytest.mark.parametrize("tokens", [1, 31, 33, 160, 161, 32 + 2 * 128])
+def test_short_caches_with_few_or_no_packed_pages(tokens):
+    run_case(torch.bfloat16, seed=30 + tokens, batch=2, heads=2, hq=8, tokens=tokens, promote_ratio=0.25)
