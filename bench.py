@@ -150,9 +150,30 @@ def measured_peak_gbs() -> tuple[float, str]:
 
 
 # --------------------------------------------------------------------------------------- CPU arm
-def cpu_oracle_decode(ctx: int, seed: int, rows: int, repeats: int):
-    """Time the oracle port of the reference's page-streamed attention on `rows` batch rows."""
+def host_threads() -> int:
+    """Threads the NumPy/BLAS legs may use: every core this process is allowed to run on."""
 
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        return os.cpu_count() or 1
+
+
+def cpu_oracle_decode(ctx: int, seed: int, rows: int, repeats: int):
+    """Time the oracle port of the reference's page-streamed attention on `rows` batch rows.
+
+    The BLAS pools are opened up to every host core for the duration (a launcher may have pinned them to one).
+    """
+
+    try:
+        from threadpoolctl import threadpool_limits
+    except ImportError:
+        return _cpu_oracle_decode(ctx, seed, rows, repeats)
+    with threadpool_limits(limits=host_threads()):
+        return _cpu_oracle_decode(ctx, seed, rows, repeats)
+
+
+def _cpu_oracle_decode(ctx: int, seed: int, rows: int, repeats: int):
     from oracle import dartkv_oracle as orc
 
     rng = np.random.default_rng(seed)
@@ -189,7 +210,7 @@ def reference_arm(args, wl) -> None:
     step_s, _ = cpu_oracle_decode(wl["ctx"], wl["seed"], rows, max(1, min(args.steps, 3)))
     sample_bytes = rows * GEOM["kv_heads"] * bytes_per_bh(wl["ctx"]) + 2 * rows * GEOM["query_heads"] * GEOM["head_dim"] * 2
     value = sample_bytes / step_s / 1e9
-    cores = os.cpu_count() or 1
+    cores = host_threads()
     line = {
         "impl": "reference", "metric": "fused_decode_attention_hbm_gbs", "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
@@ -383,7 +404,7 @@ def gpu_arm(args, wl) -> None:
         step_s, append_s = cpu_oracle_decode(wl["ctx"], wl["seed"], rows, 1)
         sample_bytes = rows * GEOM["kv_heads"] * bytes_per_bh(wl["ctx"]) + 2 * rows * hq * d * 2
         extra["cpu_baseline"] = {
-            "value": sample_bytes / step_s / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
+            "value": sample_bytes / step_s / 1e9, "unit": "GB/s", "cores": host_threads(), "kind": "port",
             "sample": f"{rows} of {wl['batch']} batch rows, full context ({step_s:.2f} s per step; NumPy port of "
                       f"the reference's page-streamed attention, BLAS threads = host cores; oracle append of the "
                       f"sample took {append_s:.1f} s)"}
