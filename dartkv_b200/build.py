@@ -1,4 +1,10 @@
-"""Compile the CUDA sources of this package into ``libdartkv_b200.so`` (sm_100a only)."""
+"""Compile the CUDA sources of this package into ``libdartkv_b200.so`` (sm_100a only).
+
+``python dartkv_b200/build.py [--force] [-v]``; ``-v`` prints ptxas resource usage.  Extra nvcc flags can be
+passed in ``DARTKV_NVCC_FLAGS`` (the decode kernels have build-time knobs for timing experiments: unroll factors
+``-DPEROP_QK_UNROLL=`` / ``-DFUSED_PV_UNROLL=`` ..., and parts that can be compiled out, ``-DFUSED_SKIP_QK``,
+``-DFUSED_SKIP_PV``, ``-DFUSED_SKIP_SETUP``, ``-DDENSE_SKIP``; a library built with the latter computes garbage).
+"""
 
 from __future__ import annotations
 
