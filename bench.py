@@ -34,6 +34,11 @@ WORKLOADS = {
     # packed-page fused GQA decode attention: batch 32, context 8192
     "config3": dict(batch=32, ctx=8192, seed=2),
 }
+# DRAM bytes of ONE decode launch at config 3 measured with ncu (dram__bytes_read.sum / dram__bytes_write.sum of the
+# tensor-core decode kernel, per-op flavour) next to that launch's algorithmic bytes
+NCU_CONFIG3 = {"algorithmic": 192774144, "dram_read": 192.73e6, "dram_write": 5.10e6}
+# the same numbers as dartkv_b200.synthetic.HEADLINE_GEOMETRY (kept here so that the CPU reference arm runs without
+# loading the package or its CUDA library; the GPU arm asserts that the two agree)
 GEOM = dict(query_heads=32, kv_heads=8, head_dim=128, page=128, key_group=128, value_group=64, sinks=32,
             promote_ratio=0.25, bits=2)
 
@@ -65,29 +70,15 @@ def outlier_channels(seed: int) -> torch.Tensor:
     return torch.stack([torch.randperm(GEOM["head_dim"], generator=gen)[:count] for _ in range(GEOM["kv_heads"])])
 
 
-def build_device_cache(batch: int, ctx: int, seed: int, rank: int, device: torch.device):
-    """Fill a cache with `ctx` tokens of synthetic K/V generated on the device, 1024 tokens per append."""
+def build_device_cache(rows, ctx: int, seed: int, device: torch.device, keep_inputs: bool = False, heads=None):
+    """The workload's cache for the global batch rows `rows` (see dartkv_b200.synthetic.build_headline_cache)."""
 
-    import dartkv_b200 as dart
+    from dartkv_b200.synthetic import HEADLINE_GEOMETRY, build_headline_cache
 
-    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=torch.bfloat16, **cache_kwargs()), max_tokens=ctx + 256)
-    gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
-    mult = torch.ones(GEOM["kv_heads"], GEOM["head_dim"], device=device)
-    mult.scatter_(1, outlier_channels(seed).to(device), 10.0)
-    mult = mult.view(1, GEOM["kv_heads"], 1, GEOM["head_dim"])
-    done = 0
-    first = True
-    while done < ctx:
-        step = GEOM["sinks"] if first else min(1024, ctx - done)
-        first = False
-        shape = (batch, GEOM["kv_heads"], step, GEOM["head_dim"])
-        keys = (torch.randn(shape, generator=gen, device=device) * mult).to(torch.bfloat16)
-        values = torch.randn(shape, generator=gen, device=device).to(torch.bfloat16)
-        cache.append(keys, values)
-        done += step
-    query = torch.randn((batch, GEOM["query_heads"], 1, GEOM["head_dim"]), generator=gen, device=device).to(torch.bfloat16)
-    torch.cuda.synchronize(device)
-    return cache, query
+    assert HEADLINE_GEOMETRY == GEOM
+    rows = list(rows)
+    got = build_headline_cache(rows, ctx, seed, device, heads=heads, keep_rows=rows if keep_inputs else None)
+    return got if keep_inputs else got[:2]
 
 
 class ClockSampler:
@@ -151,7 +142,7 @@ def measured_peak_gbs() -> tuple[float, str]:
 
 # --------------------------------------------------------------------------------------- CPU arm
 def host_threads() -> int:
-    """Threads the NumPy/BLAS legs may use: every core this process is allowed to run on."""
+    """Threads the CPU legs may use: every core this process is allowed to run on."""
 
     try:
         return max(1, len(os.sched_getaffinity(0)))
@@ -159,22 +150,24 @@ def host_threads() -> int:
         return os.cpu_count() or 1
 
 
-def cpu_oracle_decode(ctx: int, seed: int, rows: int, repeats: int):
-    """Time the oracle port of the reference's page-streamed attention on `rows` batch rows.
+def reference_package():
+    """The reference's own `dart` package when an install of it sits in oracle/_ref (made by oracle/make_ref.sh),
+    else None.  It is only ever used as the timed CPU / GPU baseline, never by the product path."""
 
-    The BLAS pools are opened up to every host core for the duration (a launcher may have pinned them to one).
-    """
-
+    path = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.isdir(os.path.join(path, "dart")):
+        return None
+    if path not in sys.path:
+        sys.path.insert(0, path)
     try:
-        from threadpoolctl import threadpool_limits
-    except ImportError:
-        return _cpu_oracle_decode(ctx, seed, rows, repeats)
-    with threadpool_limits(limits=host_threads()):
-        return _cpu_oracle_decode(ctx, seed, rows, repeats)
+        import dart
+    except Exception:   # an install that does not import here is the same as no install
+        return None
+    return dart
 
 
-def _cpu_oracle_decode(ctx: int, seed: int, rows: int, repeats: int):
-    from oracle import dartkv_oracle as orc
+def synthetic_rows_cpu(ctx: int, seed: int, rows: int):
+    """bf16 K, V [rows,H,ctx,D] and query [rows,Hq,1,D] as torch CPU tensors (same distributions as the GPU arm)."""
 
     rng = np.random.default_rng(seed)
     h, d, hq = GEOM["kv_heads"], GEOM["head_dim"], GEOM["query_heads"]
@@ -182,43 +175,99 @@ def _cpu_oracle_decode(ctx: int, seed: int, rows: int, repeats: int):
     out = outlier_channels(seed).numpy()
     for head in range(h):
         mult[0, head, 0, out[head]] = 10.0
-    keys = orc.round_to(rng.standard_normal((rows, h, ctx, d), dtype=np.float32) * mult, "bf16")
-    values = orc.round_to(rng.standard_normal((rows, h, ctx, d), dtype=np.float32), "bf16")
-    query = orc.round_to(rng.standard_normal((rows, hq, 1, d), dtype=np.float32), "bf16")
-    cfg = dict(cache_kwargs())
-    cache = orc.OracleCache(orc.CacheConfig(metadata_dtype="bf16", **cfg), "bf16")
-    t0 = time.perf_counter()
-    cache.append(keys[:, :, : GEOM["sinks"]], values[:, :, : GEOM["sinks"]])
-    cache.append(keys[:, :, GEOM["sinks"]:], values[:, :, GEOM["sinks"]:])
-    append_s = time.perf_counter() - t0
-    orc.streamed_attention(query, cache, "bf16")  # warm-up
-    times = []
-    for _ in range(repeats):
+    keys = torch.from_numpy(rng.standard_normal((rows, h, ctx, d), dtype=np.float32) * mult).to(torch.bfloat16)
+    values = torch.from_numpy(rng.standard_normal((rows, h, ctx, d), dtype=np.float32)).to(torch.bfloat16)
+    query = torch.from_numpy(rng.standard_normal((rows, hq, 1, d), dtype=np.float32)).to(torch.bfloat16)
+    return keys, values, query
+
+
+class CpuDecode:
+    """The reference's CPU implementation of the path on `rows` batch rows of the workload at full context:
+    its own package when installed (kind "reference"), else the NumPy port in oracle/ (kind "port")."""
+
+    def __init__(self, ctx: int, seed: int, rows: int):
+        self.cores = host_threads()
+        torch.set_num_threads(self.cores)
+        keys, values, query = synthetic_rows_cpu(ctx, seed, rows)
+        dart = reference_package()
         t0 = time.perf_counter()
-        orc.streamed_attention(query, cache, "bf16")
-        times.append(time.perf_counter() - t0)
-    return float(np.mean(times)), append_s
+        if dart is not None:
+            self.kind = "reference"
+            cfg = dart.DartKVCacheConfig(metadata_dtype=torch.bfloat16, **cache_kwargs())
+            cache = dart.DartKVCache(cfg)
+            cache.append(keys[:, :, : GEOM["sinks"]], values[:, :, : GEOM["sinks"]])
+            cache.append(keys[:, :, GEOM["sinks"]:], values[:, :, GEOM["sinks"]:])
+            self._step = lambda: dart.streamed_dart_attention(query, cache)
+            self.what = "the reference's own streamed_dart_attention on torch CPU tensors"
+        else:
+            from threadpoolctl import threadpool_limits   # the port's matrix products run in the BLAS pool
+
+            from oracle import dartkv_oracle as orc
+
+            self.kind = "port"
+            self._limits = threadpool_limits(limits=self.cores)
+            cache = orc.OracleCache(orc.CacheConfig(metadata_dtype="bf16", **cache_kwargs()), "bf16")
+            k32, v32, q32 = keys.float().numpy(), values.float().numpy(), query.float().numpy()
+            cache.append(k32[:, :, : GEOM["sinks"]], v32[:, :, : GEOM["sinks"]])
+            cache.append(k32[:, :, GEOM["sinks"]:], v32[:, :, GEOM["sinks"]:])
+            self._step = lambda: orc.streamed_attention(q32, cache, "bf16")
+            self.what = "NumPy port of the reference's page-streamed attention (BLAS threads = host cores)"
+        self.append_s = time.perf_counter() - t0
+        self.rows = rows
+        self.bytes = rows * GEOM["kv_heads"] * bytes_per_bh(ctx) + 2 * rows * GEOM["query_heads"] * GEOM["head_dim"] * 2
+
+    def time_steps(self, steps: int, warmup: int) -> float:
+        """Mean seconds per step over exactly `steps` timed steps after `warmup` untimed ones."""
+
+        for _ in range(warmup):
+            self._step()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            self._step()
+        return (time.perf_counter() - t0) / steps
+
+
+def workload_config(args, wl, world: int) -> dict:
+    """The `config` object of the JSON line: identical for the GPU arm and the reference arm of one launch."""
+
+    local_batch = -(-wl["batch"] // world) if wl["batch"] >= world else 1
+    head_groups = 1 if wl["batch"] >= world else world // wl["batch"]
+    local_bytes = step_bytes(local_batch, wl["ctx"]) // head_groups
+    return {"workload": args.workload, "batch": wl["batch"], "context": wl["ctx"], "per_gpu_batch": local_batch,
+            "query_heads": GEOM["query_heads"], "kv_heads": GEOM["kv_heads"], "head_dim": GEOM["head_dim"],
+            "page": GEOM["page"], "bits": "2-bit + 0.25 promotion", "key_group": GEOM["key_group"],
+            "value_group": GEOM["value_group"], "sinks": GEOM["sinks"], "metadata": "bf16",
+            "bytes_per_step": step_bytes(wl["batch"], wl["ctx"]),
+            "dequant": "per-op rounded (reference streamed path)" if args.flavour == "per_op"
+            else "unrounded fp32 (reference Triton kernels)",
+            "l2": f"per-GPU working set {local_bytes / 1e6:.0f} MB exceeds the 126 MB L2",
+            "parallelism": (f"batch sharded over {world} GPU(s)" if head_groups == 1 else
+                            f"batch x KV heads sharded over {world} GPU(s) ({head_groups} head groups)") +
+                           ", output all-gather only"}
 
 
 def reference_arm(args, wl) -> None:
-    """`--impl reference`: the reference's CPU implementation of the path (oracle port), host cores only."""
+    """`--impl reference`: the reference's CPU implementation of the path, host cores only, rank 0 only.
+
+    A step is one decode-attention pass over a bounded sample of the workload (one batch row at full context);
+    exactly `--steps` steps are timed after `--warmup` untimed ones.
+    """
 
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = 1
-    step_s, _ = cpu_oracle_decode(wl["ctx"], wl["seed"], rows, max(1, min(args.steps, 3)))
-    sample_bytes = rows * GEOM["kv_heads"] * bytes_per_bh(wl["ctx"]) + 2 * rows * GEOM["query_heads"] * GEOM["head_dim"] * 2
-    value = sample_bytes / step_s / 1e9
-    cores = host_threads()
+    cpu = CpuDecode(wl["ctx"], wl["seed"], rows=1)
+    warmup = max(1, args.warmup)
+    step_s = cpu.time_steps(args.steps, warmup)
+    value = cpu.bytes / step_s / 1e9
+    sample = (f"{cpu.rows} of {wl['batch']} batch rows at full context per step; {cpu.what}; building the "
+              f"sample's cache took {cpu.append_s:.1f} s (untimed)")
     line = {
         "impl": "reference", "metric": "fused_decode_attention_hbm_gbs", "value": value, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup, "ms_per_step": step_s * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "batch": wl["batch"], "context": wl["ctx"]},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"{rows} of {wl['batch']} batch rows, full context, NumPy port of the reference's "
-                                   "page-streamed attention (BLAS threads = host cores)"},
+        "config": workload_config(args, wl, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cpu.cores, "kind": cpu.kind, "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -226,8 +275,18 @@ def reference_arm(args, wl) -> None:
 
 
 # --------------------------------------------------------------------------------------- GPU arm
+# packed bytes per 128-token page and (batch, kv head): key page by key mode, value page by value bits
+# (key group 128, value group 64, bf16 metadata)
+KEY_PAGE_BYTES = {"mixed": 4096 + 1024 + 128 + 256 + 256, 2: 4096 + 512, 4: 8192 + 512, 8: 16384 + 512}
+VALUE_PAGE_BYTES = {2: 4096 + 1024, 4: 8192 + 1024, 8: 16384 + 1024}
+APPEND_VARIANTS = (("v2_mixed", 2, 0.25), ("v4_mixed", 4, 0.25), ("v8_mixed", 8, 0.25),
+                   ("v2_uniform", 2, 0.0), ("v4_uniform", 4, 0.0), ("v8_uniform", 8, 0.0))
+
+
 def append_microbench(device: torch.device, steps: int, warmup: int) -> dict:
-    """Quantize+pack append microbench: bf16 K,V [16,8,4096,128], 2-bit + 0.25 promotion, 128 tokens per append."""
+    """Quantize+pack append microbench: bf16 K,V [16,8,4096,128], page 128, groups 128/64, 32 sinks; value bits
+    2/4/8 with promoted 2+2-bit keys (ratio 0.25) or uniform keys of the same width; 128 tokens per append and,
+    for the roofline figure, the whole tensor in one append."""
 
     import dartkv_b200 as dart
 
@@ -237,42 +296,89 @@ def append_microbench(device: torch.device, steps: int, warmup: int) -> dict:
     mult.scatter_(1, outlier_channels(1).to(device), 10.0)
     keys = (torch.randn((b, h, t, d), generator=gen, device=device) * mult.view(1, h, 1, d)).to(torch.bfloat16)
     values = torch.randn((b, h, t, d), generator=gen, device=device).to(torch.bfloat16)
-    cfg = dart.DartKVCacheConfig(metadata_dtype=torch.bfloat16, **cache_kwargs())
     start_evt, stop_evt = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-
-    def run(chunk):
-        cache = dart.DartKVCache(cfg, max_tokens=t + 256)
-        cache.append(keys[:, :, :32], values[:, :, :32])
-        torch.cuda.synchronize(device)
-        start_evt.record()
-        pos = 32
-        while pos < t:
-            n = min(chunk, t - pos)
-            cache.append(keys[:, :, pos:pos + n], values[:, :, pos:pos + n])
-            pos += n
-        stop_evt.record()
-        torch.cuda.synchronize(device)
-        return start_evt.elapsed_time(stop_evt) * 1e-3
-
-    out = {}
     pages = (t - 32) // 128
     read = 2 * b * h * (t - 32) * d * 2
-    written = b * h * (pages * (5760 + 5120) + (t - 32 - pages * 128) * d * 2 * 2)
-    for name, chunk in (("per_128_token_step", 128), ("bulk", t)):
-        for _ in range(max(1, warmup)):
-            run(chunk)
-        secs = float(np.mean([run(chunk) for _ in range(max(1, steps))]))
-        out[name] = {"gbs": (read + written) / secs / 1e9, "ms": secs * 1e3,
-                     "appends": -(-(t - 32) // chunk)}
-    out["bytes"] = {"read": read, "written": written}
+    out = {}
+    for name, bits, ratio in APPEND_VARIANTS:
+        kwargs = dict(cache_kwargs(), bits=bits, promote_ratio=ratio)
+        cfg = dart.DartKVCacheConfig(metadata_dtype=torch.bfloat16, **kwargs)
+
+        def run(chunk):
+            cache = dart.DartKVCache(cfg, max_tokens=t + 256)
+            cache.append(keys[:, :, :32], values[:, :, :32])
+            torch.cuda.synchronize(device)
+            start_evt.record()
+            pos = 32
+            while pos < t:
+                n = min(chunk, t - pos)
+                cache.append(keys[:, :, pos:pos + n], values[:, :, pos:pos + n])
+                pos += n
+            stop_evt.record()
+            torch.cuda.synchronize(device)
+            return start_evt.elapsed_time(stop_evt) * 1e-3
+
+        key_page = KEY_PAGE_BYTES["mixed" if ratio > 0 else bits]
+        written = b * h * (pages * (key_page + VALUE_PAGE_BYTES[bits]) + (t - 32 - pages * 128) * d * 2 * 2)
+        entry = {"bytes_read": read, "bytes_written": written}
+        for label, chunk in (("per_128_token_step", 128), ("bulk", t)):
+            for _ in range(max(1, warmup)):
+                run(chunk)
+            secs = float(np.mean([run(chunk) for _ in range(max(1, steps))]))
+            appends = -(-(t - 32) // chunk)
+            entry[label] = {"gbs": (read + written) / secs / 1e9, "ms": secs * 1e3, "appends": appends,
+                            "us_per_append": secs * 1e6 / appends}
+        out[name] = entry
+    # the headline variant keeps its place at the top level
+    out["per_128_token_step"] = out["v2_mixed"]["per_128_token_step"]
+    out["bulk"] = out["v2_mixed"]["bulk"]
+    out["bytes"] = {"read": read, "written": out["v2_mixed"]["bytes_written"]}
     return out
 
 
+def reference_gpu_decode(wl, device: torch.device, steps: int) -> dict:
+    """The reference's own Triton decode kernel (fused_dart_attention, fallback off) on this GPU, on a bounded
+    sample of the workload: min(batch, 8) rows at full context, cache built by the reference's own append."""
+
+    dart = reference_package()
+    if dart is None:
+        return {"unavailable": "no install of the reference under oracle/_ref"}
+    rows = min(wl["batch"], 8)
+    try:
+        cache, query, keys, values = build_device_cache(range(rows), wl["ctx"], wl["seed"], device, keep_inputs=True)
+        del cache
+        cfg = dart.DartKVCacheConfig(metadata_dtype=torch.bfloat16, **cache_kwargs())
+        ref = dart.DartKVCache(cfg)
+        ref.append(keys[:, :, : GEOM["sinks"]], values[:, :, : GEOM["sinks"]])
+        ref.append(keys[:, :, GEOM["sinks"]:], values[:, :, GEOM["sinks"]:])
+        del keys, values
+        for _ in range(2):
+            dart.fused_dart_attention(query, ref, fallback=False)
+        torch.cuda.synchronize(device)
+        start_evt, stop_evt = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        steps = max(1, min(steps, 5))
+        start_evt.record()
+        for _ in range(steps):
+            dart.fused_dart_attention(query, ref, fallback=False)
+        stop_evt.record()
+        torch.cuda.synchronize(device)
+        ms = start_evt.elapsed_time(stop_evt) / steps
+    except Exception as exc:   # e.g. Triton cannot JIT on this device
+        return {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+    sample_bytes = step_bytes(rows, wl["ctx"])
+    return {"value": sample_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "steps": steps,
+            "sample": f"{rows} of {wl['batch']} batch rows at full context; the reference's Triton kernels "
+                      "(one launch per page), same algorithmic bytes per row"}
+
+
 def gpu_arm(args, wl) -> None:
+    import datetime
+
     import torch.distributed as dist
 
     import dartkv_b200 as dart
     from dartkv_b200 import _lib
+    from dartkv_b200.sharding import gather_outputs, shard_plan
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -283,34 +389,68 @@ def gpu_arm(args, wl) -> None:
     torch.cuda.set_device(device)
     if world > 1:
         # the only collective is a gather of [B/N, Hq, D] outputs (1 MB in total): in-switch reduction buys nothing
-        # here and its set-up dominates communicator creation on 8 GPUs
+        # here and its set-up dominates communicator creation on 8 GPUs.  The short timeout makes a rank that is
+        # out of step give up with an error instead of spinning.
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        dist.init_process_group("nccl", device_id=device)
-    from dartkv_b200.sharding import shard_rows
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=120))
 
-    lo, hi = shard_rows(wl["batch"], world, rank)
-    local_batch = hi - lo
-    cache, query = build_device_cache(local_batch, wl["ctx"], wl["seed"], rank, device)
+    shard = shard_plan(wl["batch"], GEOM["kv_heads"], world, rank)
+    local_batch = shard.rows
+    heads = (shard.head_begin, shard.head_end)
+    cache, query = build_device_cache(range(shard.row_begin, shard.row_end), wl["ctx"], wl["seed"], device, heads=heads)
     hq, d = GEOM["query_heads"], GEOM["head_dim"]
-    out = torch.empty((local_batch, hq, d), dtype=torch.bfloat16, device=device)
-    gathered = torch.empty((world * local_batch, hq, d), dtype=torch.bfloat16, device=device) if world > 1 else None
+    hq_local = query.shape[1]
+    out = torch.empty((local_batch, hq_local, d), dtype=torch.bfloat16, device=device)
+    gathered = torch.empty((wl["batch"], hq, d), dtype=torch.bfloat16, device=device) if world > 1 else None
     q3 = query[:, :, 0].contiguous()
+    gather_kwargs = dict(shard=shard, batch=wl["batch"], kv_heads=GEOM["kv_heads"])
+    q_lo, q_hi = shard.query_heads(hq, GEOM["kv_heads"])
 
     flavour = _lib.DEQUANT_FUSED if args.flavour == "fused" else _lib.DEQUANT_PER_OP
 
-    def step():
+    def decode():
         dart.decode_attention(q3, cache, out=out, flavour=flavour)
+
+    def step():
+        decode()
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)  # the only cross-GPU traffic: final output gather
+            gather_outputs(out, gathered, **gather_kwargs)  # the only cross-GPU traffic: final output gather
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    for _ in range(max(3, args.warmup)):
+    warmup = max(3, args.warmup)
+    for _ in range(warmup):
         step()
     barrier()
+
+    # ---- the gathered result is checked once, outside the timed region: this rank's slice must be its own
+    # output, and the first row of the next rank's slice must match a local recomputation of that batch row
+    gather_check = None
+    if world > 1:
+        mine_ok = bool(torch.equal(gathered[shard.row_begin:shard.row_end, q_lo:q_hi], out))
+        peer = shard_plan(wl["batch"], GEOM["kv_heads"], world, (rank + 1) % world)
+        peer_heads = (peer.head_begin, peer.head_end)
+        peer_cache, peer_query = build_device_cache([peer.row_begin], wl["ctx"], wl["seed"], device, heads=peer_heads)
+        peer_out = torch.empty((1, peer_query.shape[1], d), dtype=torch.bfloat16, device=device)
+        dart.decode_attention(peer_query[:, :, 0].contiguous(), peer_cache, out=peer_out, flavour=flavour)
+        p_lo, p_hi = peer.query_heads(hq, GEOM["kv_heads"])
+        got = gathered[peer.row_begin, p_lo:p_hi].float()
+        diff = (got - peer_out[0].float()).abs()
+        # the split of the work differs with the batch size, so the two fp32 sums may round differently: one
+        # output ulp (or 2e-3) is allowed
+        peer_ok = bool(((diff <= 2e-3) | (diff <= got.abs() * 2.0 ** -7)).all())
+        flags = torch.tensor([int(mine_ok), int(peer_ok)], dtype=torch.int32, device=device)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        gather_check = {"own_slice_equal": bool(flags[0].item()), "peer_row_recomputed_within_1ulp": bool(flags[1].item()),
+                        "peer_max_abs": float(diff.max().item())}
+        del peer_cache, peer_query, peer_out
+        if not (gather_check["own_slice_equal"] and gather_check["peer_row_recomputed_within_1ulp"]):
+            raise SystemExit(f"gathered outputs are wrong: {gather_check}")
+        barrier()
+
     start_evt, stop_evt = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_before = _lib.LIB.dartkv_launch_count()
     with ClockSampler(local_rank) as clocks:
@@ -321,13 +461,13 @@ def gpu_arm(args, wl) -> None:
         stop_evt.record()
         launches = _lib.LIB.dartkv_launch_count() - launches_before
         barrier()
-        # keep the sampler alive long enough for at least a few readings under load
         elapsed_ms = start_evt.elapsed_time(stop_evt)
-        if elapsed_ms < 600:
-            t_end = time.time() + 0.6
-            while time.time() < t_end:
-                step()
-            torch.cuda.synchronize(device)
+        # keep the GPU under the same load for ~0.6 s so that the 100 ms clock sampler sees it: a fixed number of
+        # local decode calls, no collective (a collective count that depends on a rank's own clock deadlocks)
+        extra = int(min(20000, max(0, (600.0 - elapsed_ms) / max(elapsed_ms / args.steps, 1e-3))))
+        for _ in range(extra):
+            decode()
+        torch.cuda.synchronize(device)
     t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -339,17 +479,16 @@ def gpu_arm(args, wl) -> None:
     barrier()
     start_evt.record()
     for _ in range(args.steps):
-        dart.decode_attention(q3, cache, out=out, flavour=flavour)
+        decode()
     stop_evt.record()
     torch.cuda.synchronize(device)
     kernel_ms = start_evt.elapsed_time(stop_evt) / args.steps
-    local_bytes = step_bytes(local_batch, wl["ctx"])
+    local_bytes = step_bytes(local_batch, wl["ctx"]) * shard.heads // GEOM["kv_heads"]
     peak, peak_kind = measured_peak_gbs()
     achieved = local_bytes / (kernel_ms * 1e-3) / 1e9
-    # DRAM traffic of one decode launch from the ncu capture of config 3 (profiles/decode_fast_kernel_config3.md):
-    # 192.72 MB read + 6.54 MB written for 192.77 MB algorithmic; traffic grows with the pages processed, so
+    # DRAM traffic of one decode launch from the ncu capture of config 3; it grows with the pages processed, so
     # other workloads scale it by their algorithmic bytes
-    traffic = int(round(local_bytes * (192.72e6 + 6.54e6) / 192774144))
+    traffic = int(round(local_bytes * (NCU_CONFIG3["dram_read"] + NCU_CONFIG3["dram_write"]) / NCU_CONFIG3["algorithmic"]))
 
     # end to end through host buffers: pinned query -> device, attention, output -> pinned host
     host_q = q3.cpu().pin_memory()
@@ -360,8 +499,8 @@ def gpu_arm(args, wl) -> None:
         dev_q.copy_(host_q, non_blocking=True)
         dart.decode_attention(dev_q, cache, out=out, flavour=flavour)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
-            host_out.copy_(gathered[rank * local_batch:(rank + 1) * local_batch], non_blocking=True)
+            gather_outputs(out, gathered, **gather_kwargs)
+            host_out.copy_(gathered[shard.row_begin:shard.row_end, q_lo:q_hi], non_blocking=True)
         else:
             host_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream(device).synchronize()
@@ -381,46 +520,48 @@ def gpu_arm(args, wl) -> None:
     e2e_value = total_bytes / (e2e_ms * 1e-3) / 1e9
 
     extra = {}
+    if gather_check is not None:
+        extra["gather_checked"] = True
+        extra["gather_check"] = gather_check
     if rank == 0 and world == 1 and not args.skip_extras:
         del gathered
+        other = _lib.DEQUANT_FUSED if args.flavour == "per_op" else _lib.DEQUANT_PER_OP
+        for _ in range(3):
+            dart.decode_attention(q3, cache, out=out, flavour=other)
+        torch.cuda.synchronize(device)
+        start_evt.record()
+        for _ in range(args.steps):
+            dart.decode_attention(q3, cache, out=out, flavour=other)
+        stop_evt.record()
+        torch.cuda.synchronize(device)
+        other_ms = start_evt.elapsed_time(stop_evt) / args.steps
+        other_gbs = local_bytes / (other_ms * 1e-3) / 1e9
         if args.flavour == "per_op":
-            # the same call with the arithmetic of the reference's Triton kernels (dequantized values never rounded)
-            for _ in range(3):
-                dart.decode_attention(q3, cache, out=out, flavour=_lib.DEQUANT_FUSED)
-            torch.cuda.synchronize(device)
-            start_evt.record()
-            for _ in range(args.steps):
-                dart.decode_attention(q3, cache, out=out, flavour=_lib.DEQUANT_FUSED)
-            stop_evt.record()
-            torch.cuda.synchronize(device)
-            fused_ms = start_evt.elapsed_time(stop_evt) / args.steps
-            fused_gbs = local_bytes / (fused_ms * 1e-3) / 1e9
             extra["unrounded_fp32_variant"] = {
-                "value": fused_gbs, "unit": "GB/s", "us_per_launch": fused_ms * 1e3, "frac": fused_gbs / peak,
-                "note": "flavour DEQUANT_FUSED: code*scale+zero kept in fp32 like the reference's Triton kernels; "
-                        "not the pinned oracle's arithmetic, so it is reported beside the headline, not as it"}
+                "value": other_gbs, "unit": "GB/s", "us_per_launch": other_ms * 1e3, "frac": other_gbs / peak,
+                "note": "flavour DEQUANT_FUSED: code*scale+zero kept in fp32 like the reference's Triton attention "
+                        "kernels (checked against outputs of those kernels recorded on a B200); reported beside "
+                        "the headline because the headline follows the reference's page-streamed attention"}
+        else:
+            extra["per_op_variant"] = {"value": other_gbs, "unit": "GB/s", "us_per_launch": other_ms * 1e3,
+                                       "frac": other_gbs / peak}
+        del cache
+        torch.cuda.empty_cache()
+        extra["reference_gpu"] = reference_gpu_decode(wl, device, args.steps)
+        torch.cuda.empty_cache()
         extra["append"] = append_microbench(device, steps=3, warmup=1)
-        rows = 1
-        step_s, append_s = cpu_oracle_decode(wl["ctx"], wl["seed"], rows, 1)
-        sample_bytes = rows * GEOM["kv_heads"] * bytes_per_bh(wl["ctx"]) + 2 * rows * hq * d * 2
+        cpu = CpuDecode(wl["ctx"], wl["seed"], rows=1)
+        step_s = cpu.time_steps(3, 1)
         extra["cpu_baseline"] = {
-            "value": sample_bytes / step_s / 1e9, "unit": "GB/s", "cores": host_threads(), "kind": "port",
-            "sample": f"{rows} of {wl['batch']} batch rows, full context ({step_s:.2f} s per step; NumPy port of "
-                      f"the reference's page-streamed attention, BLAS threads = host cores; oracle append of the "
-                      f"sample took {append_s:.1f} s)"}
+            "value": cpu.bytes / step_s / 1e9, "unit": "GB/s", "cores": cpu.cores, "kind": cpu.kind,
+            "sample": f"{cpu.rows} of {wl['batch']} batch rows at full context, 3 timed steps of {step_s:.2f} s; "
+                      f"{cpu.what}; building the sample's cache took {cpu.append_s:.1f} s (untimed)"}
     if rank == 0:
         line = {
             "metric": "fused_decode_attention_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "us_per_step": ms_per_step * 1e3,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "us_per_step": ms_per_step * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "batch": wl["batch"], "context": wl["ctx"], "per_gpu_batch": local_batch,
-                       "query_heads": hq, "kv_heads": GEOM["kv_heads"], "head_dim": d, "page": GEOM["page"],
-                       "bits": "2-bit + 0.25 promotion", "key_group": GEOM["key_group"], "value_group": GEOM["value_group"],
-                       "sinks": GEOM["sinks"], "metadata": "bf16", "bytes_per_step": total_bytes,
-                       "dequant": "per-op rounded (reference streamed path)" if args.flavour == "per_op"
-                       else "unrounded fp32 (reference Triton kernels)",
-                       "l2": f"per-GPU working set {local_bytes / 1e6:.0f} MB exceeds the 126 MB L2",
-                       "parallelism": f"batch sharded over {world} GPU(s), output all-gather only"},
+            "config": workload_config(args, wl, world),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "traffic_unit": "bytes per launch (ncu, config 3 capture scaled by algorithmic bytes)",
                          "peak_kind": peak_kind, "kernel": "decode attention call (all its kernels)",

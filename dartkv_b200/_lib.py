@@ -29,7 +29,7 @@ EXPORTS = (
     "dartkv_channel_scores", "dartkv_select_channels", "dartkv_quantize_key_mixed", "dartkv_dequantize_key_mixed",
     "dartkv_cache_geometry", "dartkv_cache_append", "dartkv_cache_materialize", "dartkv_decode_workspace_bytes",
     "dartkv_decode_attention", "dartkv_decode_plan", "dartkv_decode_status", "dartkv_builtin_scratch_bytes",
-    "dartkv_decode_attention_builtin_scratch",
+    "dartkv_decode_attention_builtin_scratch", "dartkv_shard_range", "dartkv_decode_split_override",
 )
 
 
@@ -59,6 +59,15 @@ class DecodePlanInfo(Structure):
     _fields_ = [
         ("kernel", c_int32), ("quads", c_int32), ("stream_blocks", c_int32), ("total_splits", c_int32),
         ("units", c_int64), ("generic_splits", c_int32), ("generic_chunk", c_int32),
+    ]
+
+
+class Shard(Structure):
+    """Mirror of ``dartkv_shard``."""
+
+    _fields_ = [
+        ("row_begin", c_int32), ("row_end", c_int32), ("head_begin", c_int32), ("head_end", c_int32),
+        ("batch_groups", c_int32), ("head_groups", c_int32), ("rows_padded", c_int32), ("reserved", c_int32),
     ]
 
 
@@ -103,6 +112,8 @@ def _load() -> ctypes.CDLL:
     lib.dartkv_decode_status.argtypes = [p, POINTER(c_int), p]
     lib.dartkv_decode_plan.argtypes = [POINTER(CacheDesc), i32, i32, i32, i32, POINTER(DecodePlanInfo)]
     lib.dartkv_builtin_scratch_bytes.restype = c_int64
+    lib.dartkv_decode_split_override.argtypes = [c_char_p]
+    lib.dartkv_shard_range.argtypes = [i32, i32, i32, i32, POINTER(Shard)]
     lib.dartkv_decode_attention_builtin_scratch.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, p]
     for name in EXPORTS:
         fn = getattr(lib, name)

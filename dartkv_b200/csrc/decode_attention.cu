@@ -282,6 +282,24 @@ static int dartkv_sm_count() {
   return cached;
 }
 
+// work-split override: a debugging / testing knob, kept off the per-call path (the environment is read once)
+static char g_split_override[64] = "";
+static bool g_split_override_ready = false;
+static const char* split_override() {
+  if (!g_split_override_ready) {
+    const char* env = getenv("DARTKV_DECODE_SPLIT");
+    if (env) { strncpy(g_split_override, env, sizeof(g_split_override) - 1); g_split_override[sizeof(g_split_override) - 1] = 0; }
+    g_split_override_ready = true;
+  }
+  return g_split_override[0] ? g_split_override : nullptr;
+}
+extern "C" int dartkv_decode_split_override(const char* spec) {
+  g_split_override_ready = true;
+  g_split_override[0] = 0;
+  if (spec) { strncpy(g_split_override, spec, sizeof(g_split_override) - 1); g_split_override[sizeof(g_split_override) - 1] = 0; }
+  return DARTKV_OK;
+}
+
 static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int query_heads, int flavour, int tokens) {
   DecodeLayout L{};
   const int bh = d->batch * d->kv_heads;
@@ -321,9 +339,10 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
       const long long min_share = (L.quads + 14) / 15;
       long long blocks = resident;
       if (blocks > L.units / min_share) blocks = L.units / min_share;
-      // DARTKV_DECODE_SPLIT=aligned | unaligned | unaligned:<blocks> overrides the model (tests exercise both
-      // families, and blocks that span several rows, with it)
-      const char* force = getenv("DARTKV_DECODE_SPLIT");
+      // "aligned" | "unaligned" | "unaligned:<blocks>" overrides the model (tests exercise both families, and
+      // blocks that span several rows, with it): set through dartkv_decode_split_override(), or once per process
+      // from the environment variable DARTKV_DECODE_SPLIT
+      const char* force = split_override();
       const bool force_unaligned = force && force[0] == 'u', force_aligned = force && force[0] == 'a';
       if (force_unaligned && strchr(force, ':')) {
         const long long wanted = atoll(strchr(force, ':') + 1);
@@ -358,8 +377,7 @@ static int64_t layout_bytes(const dartkv_cache_desc* d, int query_heads, const D
 
 extern "C" int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* d, int query_heads, int max_tokens) {
   if (!d || query_heads <= 0 || max_tokens <= 0) return 0;
-  // upper bound over query dtypes, dequant flavours and every token count up to max_tokens:
-  // the split count is non-decreasing in the token count for both layouts
+  // upper bound over query dtypes, dequant flavours and every token count up to max_tokens
   int64_t best = 0;
   for (int dt = 0; dt < 3; ++dt)
     for (int flavour = 0; flavour < 3; ++flavour) {
@@ -368,6 +386,15 @@ extern "C" int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* d, int
       if (L.fast) L.total_splits = 17;
       best = max(best, layout_bytes(d, query_heads, L));
     }
+  // The generic layout may serve any smaller token count (and is what a tensor-core cache falls back to for other
+  // query dtypes).  Its split count is not monotonic in the token count, because the chunk is rounded up to whole
+  // tiles, but it never exceeds min(blocks wanted, tokens / 64 rounded up): rounding the chunk up only lowers it.
+  {
+    const int bh = d->batch * d->kv_heads;
+    DecodeLayout L{};
+    L.total_splits = min(max(1, (148 * 4 + bh - 1) / bh), max(1, (max_tokens + 63) / 64));
+    best = max(best, layout_bytes(d, query_heads, L));
+  }
   return best;
 }
 

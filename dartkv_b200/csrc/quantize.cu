@@ -26,7 +26,38 @@ void dartkv_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed);
 extern "C" long long dartkv_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" const char* dartkv_last_error(void) { return g_error; }
-extern "C" int dartkv_version(void) { return 100; }
+extern "C" int dartkv_version(void) { return 110; }
+
+// ---------------------------------------------------------------------------- sharding rule (host arithmetic)
+// Every (batch row, KV head) is independent on this path, so ranks own rectangles of rows x heads.  The batch is
+// split first; KV heads are split too only when there are more ranks than batch rows.  With `g` head groups
+// (the smallest divisor of kv_heads that divides world_size and leaves world_size / g <= batch) rank r belongs
+// to batch group r / g and head group r % g; the first batch % (world_size / g) batch groups hold one row more.
+extern "C" int dartkv_shard_range(int batch, int kv_heads, int world_size, int rank, dartkv_shard* out) {
+  DARTKV_REQUIRE(out != nullptr, "shard_range received a null pointer");
+  DARTKV_REQUIRE(batch > 0 && kv_heads > 0, "batch and kv_heads must be positive");
+  DARTKV_REQUIRE(world_size > 0 && rank >= 0 && rank < world_size, "rank must be in [0, world_size)");
+  int groups = 0;
+  for (int g = 1; g <= kv_heads; ++g) {
+    if (kv_heads % g || world_size % g) continue;
+    if (world_size / g <= batch) { groups = g; break; }
+  }
+  DARTKV_REQUIRE(groups > 0,
+                 "cannot shard batch %d x %d KV heads over %d ranks: no divisor of the KV heads divides the rank "
+                 "count and leaves at most one batch group per row", batch, kv_heads, world_size);
+  const int batch_groups = world_size / groups;
+  const int bg = rank / groups, hg = rank % groups;
+  const int base = batch / batch_groups, extra = batch % batch_groups;
+  out->row_begin = bg * base + (bg < extra ? bg : extra);
+  out->row_end = out->row_begin + base + (bg < extra ? 1 : 0);
+  out->head_begin = hg * (kv_heads / groups);
+  out->head_end = out->head_begin + kv_heads / groups;
+  out->batch_groups = batch_groups;
+  out->head_groups = groups;
+  out->rows_padded = base + (extra ? 1 : 0);
+  out->reserved = 0;
+  return DARTKV_OK;
+}
 
 static inline unsigned grid_for(int64_t threads, int block) { return (unsigned)((threads + block - 1) / block); }
 

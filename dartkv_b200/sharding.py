@@ -1,36 +1,102 @@
-"""Batch sharding of the decode path across the GPUs of one node.
+"""Sharding of the decode path across the GPUs of one node, by batch row and KV head.
 
-Every (batch row, KV head) is independent on this path, so a rank owns a contiguous block of
-batch rows with its own cache pools and runs append and attention locally; the only exchange is
-the gather of the attention outputs (one ``all_gather_into_tensor`` per step over NCCL/NVLink).
+Every (batch row, KV head) is independent on this path, so a rank owns a rectangle of batch rows x KV
+heads with its own cache pools and runs append and attention locally; the only exchange is the gather of
+the attention outputs (one all-gather per step over NCCL/NVLink).  The partition rule itself lives in the
+C library (``dartkv_shard_range``) so that non-Python hosts split the work the same way: the batch is split
+first, unevenly if it must be (the first groups hold one row more); KV heads are split as well only when there
+are more ranks than batch rows.
 """
 
 from __future__ import annotations
 
-from typing import Tuple
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Tuple
 
 import torch
 import torch.distributed as dist
 
+from ._lib import LIB, Shard as _CShard, check
+
+
+@dataclass(frozen=True)
+class Shard:
+    """What one rank owns: batch rows ``[row_begin, row_end)`` x KV heads ``[head_begin, head_end)``."""
+
+    row_begin: int
+    row_end: int
+    head_begin: int
+    head_end: int
+    batch_groups: int
+    head_groups: int
+    rows_padded: int
+
+    @property
+    def rows(self) -> int:
+        return self.row_end - self.row_begin
+
+    @property
+    def heads(self) -> int:
+        return self.head_end - self.head_begin
+
+    def query_heads(self, total_query_heads: int, kv_heads: int) -> Tuple[int, int]:
+        """Half-open range of query heads that attend to this shard's KV heads (GQA by contiguous groups)."""
+
+        rep = total_query_heads // kv_heads
+        return self.head_begin * rep, self.head_end * rep
+
+
+def shard_plan(batch: int, kv_heads: int, world_size: int, rank: int) -> Shard:
+    """The rectangle of (batch rows, KV heads) owned by ``rank``; raises ``ValueError`` if it cannot be split."""
+
+    c = _CShard()
+    check(LIB.dartkv_shard_range(int(batch), int(kv_heads), int(world_size), int(rank), ctypes.byref(c)))
+    return Shard(c.row_begin, c.row_end, c.head_begin, c.head_end, c.batch_groups, c.head_groups, c.rows_padded)
+
 
 def shard_rows(batch: int, world_size: int, rank: int) -> Tuple[int, int]:
-    """Half-open range of batch rows owned by ``rank``; the batch must divide evenly."""
+    """Half-open range of batch rows owned by ``rank`` when only the batch is split (``batch >= world_size``)."""
 
     if world_size <= 0 or not 0 <= rank < world_size:
         raise ValueError("rank must be in [0, world_size)")
-    if batch % world_size:
-        raise ValueError(f"batch {batch} does not divide evenly over {world_size} ranks")
-    per_rank = batch // world_size
-    return rank * per_rank, (rank + 1) * per_rank
+    if batch < world_size:
+        raise ValueError(f"batch {batch} has fewer rows than {world_size} ranks: use shard_plan to split KV heads too")
+    plan = shard_plan(batch, 1, world_size, rank)
+    return plan.row_begin, plan.row_end
 
 
-def gather_outputs(local: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """All-gather per-rank outputs ``[B/N, ...]`` into ``[B, ...]`` in rank order (identity for one rank)."""
+def gather_outputs(local: torch.Tensor, out: Optional[torch.Tensor] = None, *, shard: Optional[Shard] = None,
+                   batch: Optional[int] = None, kv_heads: Optional[int] = None) -> torch.Tensor:
+    """All-gather per-rank attention outputs into the full ``[B, Hq, ...]`` tensor (identity for one rank).
+
+    Without ``shard`` every rank holds the same number of batch rows and all heads: the result is the
+    concatenation in rank order (``out`` may be passed to receive it).  With ``shard`` (plus the global
+    ``batch`` and ``kv_heads``) ``local`` is ``[rows, Hq_local, ...]`` of that rectangle; ranks may hold
+    different row counts and different head groups, and the pieces are placed at their global position.
+    """
 
     if not dist.is_available() or not dist.is_initialized() or dist.get_world_size() == 1:
         return local
     world = dist.get_world_size()
+    even = shard is None or (shard.head_groups == 1 and shard.rows_padded * shard.batch_groups == batch)
+    if even:
+        if out is None:
+            out = torch.empty((world * local.shape[0], *local.shape[1:]), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local.contiguous())
+        return out
+    if batch is None or kv_heads is None:
+        raise ValueError("gather_outputs with a shard needs the global batch and kv_heads")
+    padded = local.new_zeros((shard.rows_padded, *local.shape[1:]))
+    padded[: local.shape[0]].copy_(local)
+    flat = local.new_empty((world * shard.rows_padded, *local.shape[1:]))
+    dist.all_gather_into_tensor(flat, padded)
+    pieces = flat.view(world, *padded.shape)
+    heads_local = local.shape[1]
     if out is None:
-        out = torch.empty((world * local.shape[0], *local.shape[1:]), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(out, local.contiguous())
+        out = local.new_empty((batch, heads_local * shard.head_groups, *local.shape[2:]))
+    for r in range(world):
+        peer = shard_plan(batch, kv_heads, world, r)
+        h0 = (r % shard.head_groups) * heads_local
+        out[peer.row_begin:peer.row_end, h0:h0 + heads_local].copy_(pieces[r, : peer.rows])
     return out

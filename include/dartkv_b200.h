@@ -199,6 +199,10 @@ typedef struct {
 } dartkv_decode_plan_info;
 int dartkv_decode_plan(const dartkv_cache_desc* desc, int q_dtype, int query_heads, int flavour, int tokens,
                        dartkv_decode_plan_info* out);
+/* Testing / debugging knob (no counterpart in the reference): force the family of work splits of the tensor-core
+ * layouts for this process: "aligned", "unaligned", "unaligned:<blocks>", or NULL / "" for the cost model.  The
+ * environment variable DARTKV_DECODE_SPLIT gives the initial value (read once).  Not thread-safe. */
+int dartkv_decode_split_override(const char* spec);
 /* Copies the workspace status word to the host (synchronizes the stream): 0 = no bounded wait expired. */
 int dartkv_decode_status(const void* workspace, int* status_out, void* stream);
 
@@ -220,6 +224,20 @@ int64_t dartkv_builtin_scratch_bytes(void);
 int dartkv_decode_attention_builtin_scratch(const dartkv_cache_desc* desc, const void* query, int q_dtype,
                                             int query_heads, float scale, int flavour, int tokens, void* out,
                                             void* stream);
+
+/* ------------------------------------------------------------------ sharding over the GPUs of one node
+ * No counterpart in the reference (it is single-device): every (batch row, KV head) is independent on this path,
+ * so a rank owns rows [row_begin,row_end) x KV heads [head_begin,head_end) with its own pools and no exchange on
+ * the hot path; only the attention outputs are gathered.  The batch is split first (ragged splits allowed: the
+ * first batch groups hold one row more); KV heads are split as well only when world_size > batch.  rows_padded
+ * is the largest row count of any rank (the per-rank extent of an equal-sized all-gather). */
+typedef struct dartkv_shard {
+  int32_t row_begin, row_end;
+  int32_t head_begin, head_end;
+  int32_t batch_groups, head_groups;
+  int32_t rows_padded, reserved;
+} dartkv_shard;
+int dartkv_shard_range(int batch, int kv_heads, int world_size, int rank, dartkv_shard* out);
 
 #ifdef __cplusplus
 }

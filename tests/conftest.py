@@ -21,3 +21,16 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture
+def decode_split():
+    """Force the family of decode work splits for one test (``decode_split("unaligned:7")``); cleared afterwards."""
+
+    from dartkv_b200._lib import LIB
+
+    def force(spec):
+        LIB.dartkv_decode_split_override(spec.encode() if spec else None)
+
+    yield force
+    LIB.dartkv_decode_split_override(None)

@@ -88,6 +88,31 @@ CACHE_CASES = {
         dt="bf16", shape=(1, 2, 32 + 128 + 9, 128), hq=4, chunks=[169], seed=5, outliers=True, store_inputs=False),
 }
 
+# Larger headline-geometry cases read only through the reference's CUDA code paths (make_golden_cuda.py): outputs
+# of its Triton dequantize kernels and of its Triton attention kernels.
+CUDA_EXTRA_CASES = {
+    # config 3 geometry with a shorter context: 32 sinks + 16 pages + 96 pending tokens, outlier key channels
+    "config3_short_bf16": dict(
+        config=dict(_HEADLINE, md="bf16"),
+        dt="bf16", shape=(2, 8, 32 + 16 * 128 + 96, 128), hq=32, chunks=[32, 16 * 128 + 96], seed=2,
+        outliers=True, store_inputs=False),
+    "config3_short_f16": dict(
+        config=dict(_HEADLINE, md="f16"),
+        dt="f16", shape=(1, 8, 32 + 8 * 128 + 96, 128), hq=32, chunks=[32, 8 * 128 + 96], seed=22,
+        outliers=True, store_inputs=False),
+    # the same without outlier channels (plain Gaussian keys)
+    "gaussian_bf16": dict(
+        config=dict(_HEADLINE, md="bf16"),
+        dt="bf16", shape=(1, 4, 32 + 8 * 128 + 40, 128), hq=16, chunks=[32 + 8 * 128 + 40], seed=23,
+        outliers=False, store_inputs=False),
+    # uniform 2-bit keys (no promotion), value group 128
+    "uniform_2bit_bf16": dict(
+        config=dict(bits=2, page_size=128, key_group_size=128, value_group_size=128, sink_tokens=32,
+                    hold_partial_pages=True, md="bf16"),
+        dt="bf16", shape=(1, 4, 32 + 6 * 128 + 17, 128), hq=8, chunks=[32 + 6 * 128 + 17], seed=24,
+        outliers=True, store_inputs=False),
+}
+
 
 def build_inputs(case: dict):
     """K, V ``[B,H,T,D]`` and query ``[B,Hq,1,D]`` for a case, on the CPU, in the case dtype."""

@@ -47,11 +47,8 @@ TOKENS = [1, 31, 32, 33, 159, 160, 161, 32 + 4 * 128, 32 + 5 * 128 + 77, 8192, 3
 
 @pytest.mark.parametrize("split", [None, "aligned", "unaligned", "unaligned:7", "unaligned:3"])
 @pytest.mark.parametrize("flavour", [_lib.DEQUANT_PER_OP, _lib.DEQUANT_FUSED])
-def test_tensor_core_plans_stay_inside_their_partial_slots(flavour, split, monkeypatch):
-    if split is None:
-        monkeypatch.delenv("DARTKV_DECODE_SPLIT", raising=False)
-    else:
-        monkeypatch.setenv("DARTKV_DECODE_SPLIT", split)
+def test_tensor_core_plans_stay_inside_their_partial_slots(flavour, split, decode_split):
+    decode_split(split)
     for (batch, heads), tokens in itertools.product(ROWS, TOKENS):
         d = make_desc(batch, heads)
         info = plan(d, _lib.BF16, 4 * heads, flavour, tokens)
@@ -95,3 +92,21 @@ def test_plan_argument_errors():
     assert LIB.dartkv_decode_plan(ctypes.byref(d), _lib.BF16, 3, 0, 100, ctypes.byref(info)) == -1
     assert LIB.dartkv_decode_plan(ctypes.byref(d), _lib.BF16, 8, 9, 100, ctypes.byref(info)) == -1
     assert LIB.dartkv_decode_plan(ctypes.byref(d), _lib.BF16, 8, 0, 0, ctypes.byref(info)) == -1
+
+
+@pytest.mark.parametrize("kwargs", [dict(value_bits=4), dict(key_bits=4, promoted=0), dict(value_group=32), dict()],
+                         ids=["v4", "k4", "vg32", "headline"])
+def test_workspace_bound_covers_every_smaller_token_count(kwargs):
+    # a workspace sized for a capacity must serve every token count up to it, for every query dtype and flavour
+    # (the generic split count is not monotonic in the token count: its chunk is rounded up to whole tiles)
+    for batch, heads, hq in ((2, 8, 32), (1, 8, 32), (1, 1, 4), (16, 8, 32)):
+        d = make_desc(batch, heads, **kwargs)
+        for capacity in (300, 3000, 4256, 8352):
+            have = LIB.dartkv_decode_workspace_bytes(ctypes.byref(d), hq, capacity)
+            worst = 0
+            for tokens in range(1, capacity + 1, 1 if capacity <= 3000 else 7):
+                for q_dtype, flavour in ((_lib.BF16, _lib.DEQUANT_PER_OP), (_lib.F32, _lib.DEQUANT_PER_OP),
+                                         (_lib.BF16, _lib.DEQUANT_FUSED)):
+                    info = plan(d, q_dtype, hq, flavour, tokens)
+                    worst = max(worst, 16 + batch * hq * info.total_splits * (2 + 128) * 4)
+            assert have >= worst, (kwargs, batch, heads, capacity, have, worst)

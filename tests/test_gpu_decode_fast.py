@@ -126,9 +126,9 @@ def test_full_context_properties():
 
 
 @pytest.mark.parametrize("split", ["aligned", "unaligned", "unaligned:7", "unaligned:5"])
-def test_both_split_families_and_blocks_that_span_rows(split, monkeypatch):
+def test_both_split_families_and_blocks_that_span_rows(split, decode_split):
     # 6 (batch, kv head) rows x 3 four-page units: with 7 or 5 blocks every block's share crosses a row boundary
-    monkeypatch.setenv("DARTKV_DECODE_SPLIT", split)
+    decode_split(split)
     run_case(torch.bfloat16, seed=9, batch=3, heads=2, hq=8, tokens=32 + 11 * 128 + 9, promote_ratio=0.25)
 
 

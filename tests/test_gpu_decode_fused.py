@@ -113,8 +113,8 @@ def test_unknown_flavour_is_rejected():
 
 
 @pytest.mark.parametrize("split", ["aligned", "unaligned:7"])
-def test_both_split_families(split, monkeypatch):
-    monkeypatch.setenv("DARTKV_DECODE_SPLIT", split)
+def test_both_split_families(split, decode_split):
+    decode_split(split)
     run_case(torch.bfloat16, seed=9, batch=3, heads=2, hq=8, tokens=32 + 11 * 128 + 9, promote_ratio=0.25)
 
 
