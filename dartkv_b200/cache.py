@@ -276,21 +276,27 @@ class DartKVCache:
         if self._desc is None:
             self._device = device
             self._allocate(batch, heads, head_dim, keys.dtype, device, chunk)
-        cfg, life = self.config, self._life
+        # the kernels index chunk tokens with 16 bits: longer chunks are appended in pieces, which the lifecycle
+        # treats exactly like one append of the whole chunk (pages are cut at the same absolute positions) as long
+        # as the first piece carries the whole sink prefix
+        limit = 65535 // self.config.page_size * self.config.page_size
+        if chunk > limit and channel_indices is None and self.config.sink_tokens <= limit \
+                and not self.config.value_local_tokens and (self.config.hold_partial_pages or self.config.local_tokens):
+            for start in range(0, chunk, limit):
+                self.append(keys[:, :, start:start + limit], values[:, :, start:start + limit])
+            return
         if chunk > 65535:
-            raise ValueError("append chunks longer than 65535 tokens must be split by the caller")
+            raise ValueError("append chunks longer than 65535 tokens must be split by the caller for this cache "
+                             "configuration (its page boundaries depend on the chunk boundaries)")
+        cfg = self.config
         if cfg.promote_ratio > 0.0 and cfg.channel_selection != "magnitude" and channel_indices is None:
             channel_indices = self._host_selected_indices(keys, chunk)
+        # plan on a copy of the lifecycle state: the host state advances only once the launch has been accepted, so
+        # a failed append (bad argument, out of memory while growing the pools, CUDA error) leaves both in step
+        life = LifecycleState(self._life.seen, self._life.k_packed_end, self._life.v_packed_end,
+                              list(self._life.pages), list(self._life.sink_pieces))
         fields = plan_append(cfg, life, chunk)
         d = self._desc
-        rows_needed = life.v_packed_end - cfg.sink_tokens
-        if len(life.pages) > d.max_key_pages or rows_needed > d.max_value_tokens:
-            # pools grow by doubling; the old contents are copied on the current stream
-            self._ensure_capacity(2 * len(life.pages) if len(life.pages) > d.max_key_pages else d.max_key_pages,
-                                  2 * rows_needed if rows_needed > d.max_value_tokens else d.max_value_tokens)
-        plan = self._plan
-        for name in _PLAN_FIELDS:
-            setattr(plan, name, getattr(fields, name))
         idx = None
         if channel_indices is not None and d.promoted:
             expected = fields.num_pages + fields.requantize_last_page
@@ -300,10 +306,19 @@ class DartKVCache:
             if fields.requantize_last_page:
                 idx = torch.cat((idx[:, :1].reshape(-1), idx[:, 1:].reshape(-1)))
             idx = idx.contiguous()
+        rows_needed = life.v_packed_end - cfg.sink_tokens
+        if len(life.pages) > d.max_key_pages or rows_needed > d.max_value_tokens:
+            # pools grow by doubling; the old contents are copied on the current stream
+            self._ensure_capacity(2 * len(life.pages) if len(life.pages) > d.max_key_pages else d.max_key_pages,
+                                  2 * rows_needed if rows_needed > d.max_value_tokens else d.max_value_tokens)
+        plan = self._plan
+        for name in _PLAN_FIELDS:
+            setattr(plan, name, getattr(fields, name))
         with device_guard(device):
             check(LIB.dartkv_cache_append(
                 ctypes.byref(d), ctypes.byref(plan), ptr(keys), ptr(values), keys.stride(0), keys.stride(1),
                 keys.stride(2), ptr(idx), ptr(self._pools["nonfinite"]), stream_ptr(device)))
+        self._life = life
         self._layout_version += 1
         self._invalidate_page_descriptors()
 

@@ -82,10 +82,22 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cach
     for (int k = 0; k < GEN_MAX_D / GEN_THREADS; ++k) acc[r][k] = 0.0f;
   __syncthreads();
 
+  // A packed value segment [vs, ve) (page_size tokens from sink_tokens on, the last one ending at the packed end)
+  // that a key-segment boundary cuts is materialized by the reference with its per-op dequantization: the key
+  // boundaries are the page edges and the end of the packed keys.
+  auto value_flavour = [&](int tok) -> int {
+    if (a.flavour == DARTKV_DEQUANT_PER_OP || d.regular_pages) return a.flavour;   // regular pages share the value edges
+    const int vs = d.sink_tokens + (tok - d.sink_tokens) / d.page_size * d.page_size;
+    const int ve = min(v_end, vs + d.page_size);
+    if (vs >= k_end) return a.flavour;
+    const int pg = gen_find_page(d, pages, vs);
+    return d.page_start[pg] + d.page_tokens[pg] < ve ? DARTKV_DEQUANT_PER_OP : a.flavour;
+  };
   int t = lo;
   while (t < hi) {
     // ---- locate the key segment that holds token t
     int seg_end, kind, page_first = 0, page_n = 0;
+    int key_flavour = a.flavour;
     const uint8_t* page = nullptr;
     if (t < sink_filled) {
       kind = 0; seg_end = min(hi, sink_filled);
@@ -96,6 +108,13 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cach
       page_n = d.page_tokens[pg];
       seg_end = min(hi, page_first + page_n);
       page = d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes;
+      // A key page that a value-segment boundary cuts is materialized by the reference with its per-op
+      // dequantization whatever the device (src/dart/cache.py:557-560); only whole pages reach its fp32 kernels.
+      // Value boundaries: sink_tokens + i * page_size below the packed end of the values, and that end itself.
+      if (a.flavour != DARTKV_DEQUANT_PER_OP && page_first < v_end) {
+        const int next_value_edge = d.sink_tokens + ((page_first - d.sink_tokens) / d.page_size + 1) * d.page_size;
+        if (min(next_value_edge, v_end) < page_first + page_n) key_flavour = DARTKV_DEQUANT_PER_OP;
+      }
       if (d.key_mode == DARTKV_MIXED_PAGE) {
         __syncthreads();
         for (int c = tid; c < D; c += GEN_THREADS) s_slot[c] = -1;
@@ -131,7 +150,7 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cach
             const int bits = d.key_bits, vpb = 8 / bits, row_bytes = ceil_div(G * Gk, vpb);
             code = (page[(int64_t)c * row_bytes + j / vpb] >> ((j % vpb) * bits)) & ((1u << bits) - 1u);
           }
-          v = affine_restore((float)code, s, z, d.md_dtype, d.dtype, a.flavour);
+          v = affine_restore((float)code, s, z, d.md_dtype, d.dtype, key_flavour);
         }
         s_tile[tt * DP + c] = v;
       }
@@ -172,7 +191,7 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cach
           uint32_t code = (d.v_codes[row * d.value_row_bytes + c / vpb] >> ((c % vpb) * bits)) & ((1u << bits) - 1u);
           float s = load_f(d.v_meta, d.md_dtype, (row * 2 + 0) * d.value_groups + g);
           float z = load_f(d.v_meta, d.md_dtype, (row * 2 + 1) * d.value_groups + g);
-          v = affine_restore((float)code, s, z, d.md_dtype, d.dtype, a.flavour);
+          v = affine_restore((float)code, s, z, d.md_dtype, d.dtype, value_flavour(tok));
         }
         s_tile[tt * DP + c] = v;
       }

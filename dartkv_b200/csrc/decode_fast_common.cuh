@@ -101,6 +101,7 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
   while (t < seen) {
     if (t >= sink_filled && t < fast_end) { t = fast_end; continue; }
     int seg_end, kind;
+    bool fused_key = fused;
     const uint8_t* page = nullptr;
     int page_first = 0;
     if (t < sink_filled) { kind = 0; seg_end = sink_filled; }
@@ -110,6 +111,9 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
       page_first = d.sink_tokens + pg * d.page_size;
       seg_end = min(seen, page_first + d.page_size);
       page = d.k_pages + ((int64_t)bh * d.max_key_pages + pg) * d.key_page_bytes;
+      // a key page that the end of the packed values cuts is materialized by the reference with its per-op
+      // dequantization (src/dart/cache.py:557-560); only whole pages reach its fp32 kernels
+      fused_key = fused && !(page_first < v_end && v_end < page_first + d.page_size);
       __syncthreads();
       if (tid < 128) bs.slot_map[tid] = -1;
       __syncthreads();
@@ -226,7 +230,7 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
           if (slot >= 0) code |= ((page[d.key_off_high + slot * 32 + j / 4] >> ((j % 4) * 2)) & 3u) << 2;
           const float s = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_scale)[ch]);
           const float z = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_zero)[ch]);
-          kv[i] = fused ? __fmaf_rn((float)code, s, z) : rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn((float)code, s)), z));
+          kv[i] = fused_key ? __fmaf_rn((float)code, s, z) : rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn((float)code, s)), z));
         }
       } else {
         kv[0] = H::to_float((uint16_t)(k_raw.x & 0xFFFF)); kv[1] = H::to_float((uint16_t)(k_raw.x >> 16));

@@ -194,6 +194,57 @@ def cache_cases(dart, out: dict) -> None:
         out[f"{prefix}/dense_unquantized"] = npy(dense)
 
 
+TINY_QWEN3 = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, head_dim=8, max_position_embeddings=128)
+TINY_QWEN3_CACHE = dict(key_bits=2, value_bits=2, key_group_size=8, value_group_size=8, sink_tokens=2, page_size=8,
+                        local_tokens=1, value_local_tokens=8, hold_partial_pages=True, promote_bits=4,
+                        promote_ratio=0.25)
+
+
+def tiny_qwen3(seed: int = 0):
+    """The two-layer Qwen3 of the reference's tests/test_reproduction.py:353-395, weights drawn on the CPU."""
+
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    torch.manual_seed(seed)
+    config = Qwen3Config(**TINY_QWEN3)
+    config._attn_implementation = "eager"
+    return Qwen3ForCausalLM(config).eval()
+
+
+def qwen3_hook_case(dart, out: dict) -> None:
+    """Greedy tokens of the reference's dart-engine decode hook: 13-token prompt + 20 new tokens, batch 2, fp32."""
+
+    from oracle.ref_compat import patch_reference_integrations
+
+    patch_reference_integrations(dart)
+    from dart.integrations import DartHFCache, attach_dart_fused_attention
+
+    model = attach_dart_fused_attention(tiny_qwen3())
+    gen = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, TINY_QWEN3["vocab_size"], (2, 13), generator=gen)
+    cache = DartHFCache(dart.DartKVCacheConfig(metadata_dtype=torch.float32, **TINY_QWEN3_CACHE))
+    tokens = prompt
+    margins = []
+    step_logits = []
+    with torch.inference_mode():
+        logits = model(prompt, past_key_values=cache, use_cache=True).logits[:, -1]
+        for _ in range(20):
+            top2 = logits.topk(2, dim=-1).values
+            margins.append((top2[:, 0] - top2[:, 1]).numpy().copy())
+            step_logits.append(logits.numpy().copy())
+            nxt = logits.argmax(-1, keepdim=True)
+            tokens = torch.cat((tokens, nxt), dim=1)
+            logits = model(nxt, past_key_values=cache, use_cache=True).logits[:, -1]
+    assert tokens.shape == (2, 33) and cache.get_seq_length() == 33
+    out["prompt"] = prompt.numpy()
+    out["tokens"] = tokens.numpy()
+    out["margins"] = np.stack(margins)          # [step, batch] gap between the two largest logits
+    out["logits"] = np.stack(step_logits)       # [step, batch, vocab]
+    out["weight_checksum"] = np.array(float(sum(p.detach().double().abs().sum() for p in model.parameters())))
+    print("tiny Qwen3 hook: smallest top-2 logit margin", float(np.min(out["margins"])))
+
+
 def main() -> None:
     if len(sys.argv) < 2:
         raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference project>")
@@ -208,7 +259,10 @@ def main() -> None:
     caches: dict = {}
     cache_cases(dart, caches)
     np.savez_compressed(os.path.join(HERE, "caches.npz"), **caches)
-    for fn in ("primitives.npz", "caches.npz"):
+    hook: dict = {}
+    qwen3_hook_case(dart, hook)
+    np.savez_compressed(os.path.join(HERE, "qwen3_hook.npz"), **hook)
+    for fn in ("primitives.npz", "caches.npz", "qwen3_hook.npz"):
         print(fn, os.path.getsize(os.path.join(HERE, fn)), "bytes")
 
 

@@ -63,12 +63,28 @@ def main() -> None:
         cfg_kwargs = dict(case["config"])
         cfg_kwargs["metadata_dtype"] = TORCH_DTYPES[cfg_kwargs.pop("md")]
         cache = dart.DartKVCache(dart.DartKVCacheConfig(**cfg_kwargs))
+        # the promoted channels of every mixed key page, in the order the cache quantizes them: the parity tests
+        # feed them to the append kernels so that the packed bytes are the ones read here
+        import dart.cache as dart_cache
+        calls = []
+        original = dart_cache.quantize_key_mixed
+
+        def recording(*args, **kwargs):
+            result = original(*args, **kwargs)
+            calls.append(result.channel_indices.numpy().copy())
+            return result
+
+        dart_cache.quantize_key_mixed = recording
         start = 0
         for chunk in case["chunks"]:
             cache.append(keys[..., start:start + chunk, :], values[..., start:start + chunk, :])
             start += chunk
+        dart_cache.quantize_key_mixed = original
         scale = case.get("scale")
         prefix = f"cuda/{name}"
+        if calls:
+            out[f"{prefix}/mixed_indices"] = np.concatenate([c.reshape(c.shape[0], c.shape[1], -1, c.shape[-1])
+                                                             for c in calls], axis=2)   # [B,H,pages,K]
         cpu_f32 = dart.streamed_dart_attention(query.float(), cache, scale=scale)
         out[f"{prefix}/cpu_streamed_f32"] = npy(cpu_f32)
         cache.to("cuda")

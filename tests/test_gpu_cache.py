@@ -17,6 +17,7 @@ from tests.helpers import load_golden, to_np
 pytestmark = pytest.mark.gpu
 
 CACHES = load_golden("caches.npz")
+CUDA_GOLD = load_golden("cuda_reference.npz")
 
 
 def sha(*arrays):
@@ -178,9 +179,9 @@ def test_fused_attention_matches_reference_streaming_attention(name):
     two = torch.cat((query, query.flip(1)), dim=2).cuda()
     streamed = dart.streamed_dart_attention(two, cache, scale=case.get("scale"))
     torch.testing.assert_close(streamed[:, :, :1], out, rtol=0, atol=0)
-    # fp32-dequant flavour equals the oracle's restatement of the reference's CUDA/Triton arithmetic
+    # fp32-dequant flavour: what the reference's streamed attention returns for CUDA tensors (recorded on a B200)
     flav = dart.decode_attention(query[:, :, 0].float().cuda(), cache, scale=case.get("scale"), flavour=1)
-    assert torch.isfinite(flav).all()
+    np.testing.assert_allclose(to_np(flav), CUDA_GOLD[f"cuda/{name}/streamed_f32"][:, :, 0], rtol=0, atol=1e-5)
 
 
 def test_config1_report_matches_reference_figures():
@@ -426,3 +427,41 @@ def test_hf_cache_reorder_without_requantizing():
     index = torch.tensor([1, 1, 0], device="cuda")
     assert torch.equal(keys_after, keys_before.index_select(0, index))
     assert torch.equal(values_after, values_before.index_select(0, index))
+
+
+def test_failed_append_leaves_host_and_device_lifecycle_in_step():
+    cfg = dart.DartKVCacheConfig(bits=2, page_size=8, hold_partial_pages=True, key_group_size=8, value_group_size=8,
+                                 sink_tokens=2, promote_ratio=0.25, metadata_dtype=torch.float32)
+    cache = dart.DartKVCache(cfg)
+    keys, values, _ = make_kvq(21, 1, 2, 40, 16, dtype=torch.float32)
+    cache.append(keys[:, :, :13].cuda(), values[:, :, :13].cuda())
+    before = (cache.seen_tokens, cache._life.k_packed_end, list(cache._life.pages))
+    # a forced channel list with the wrong page count is rejected after the step has been planned
+    with pytest.raises(ValueError, match="channel_indices must carry"):
+        cache.append(keys[:, :, 13:30].cuda(), values[:, :, 13:30].cuda(),
+                     channel_indices=torch.zeros(1, 2, 5, 4, dtype=torch.int64))
+    assert (cache.seen_tokens, cache._life.k_packed_end, list(cache._life.pages)) == before
+    cache.append(keys[:, :, 13:].cuda(), values[:, :, 13:].cuda())
+    whole = dart.DartKVCache(cfg)
+    whole.append(keys[:, :, :13].cuda(), values[:, :, :13].cuda())
+    whole.append(keys[:, :, 13:].cuda(), values[:, :, 13:].cuda())
+    for a, b in zip(cache.get(), whole.get()):
+        assert torch.equal(a, b)
+
+
+def test_chunks_longer_than_the_kernel_limit_are_appended_in_pieces():
+    # the reference accepts any chunk length (src/dart/cache.py:168-190); 70,000 tokens exceed the 16-bit chunk index
+    cfg = dart.DartKVCacheConfig(bits=2, page_size=128, hold_partial_pages=True, key_group_size=128,
+                                 value_group_size=64, sink_tokens=32, metadata_dtype=torch.bfloat16)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    keys = torch.randn((1, 1, 70000, 128), generator=gen, device="cuda").to(torch.bfloat16)
+    values = torch.randn((1, 1, 70000, 128), generator=gen, device="cuda").to(torch.bfloat16)
+    one = dart.DartKVCache(cfg)
+    one.append(keys, values)
+    pieces = dart.DartKVCache(cfg)
+    for start in range(0, 70000, 10000):
+        pieces.append(keys[:, :, start:start + 10000], values[:, :, start:start + 10000])
+    assert one.seen_tokens == pieces.seen_tokens == 70000 and one._life.pages == pieces._life.pages
+    for a, b in zip(one.get(), pieces.get()):
+        assert torch.equal(a, b)
+    assert one.storage_bytes == pieces.storage_bytes

@@ -88,3 +88,33 @@ def test_fused_hook_matches_materializing_path_logits():
         model(prompt, past_key_values=fused, use_cache=True)
         got = model(nxt, past_key_values=fused, use_cache=True).logits
     torch.testing.assert_close(got, expected, rtol=2e-3, atol=2e-3)
+
+
+def test_decode_hook_greedy_tokens_equal_the_reference_hook():
+    """The reference's tiny Qwen3 run (tests/test_reproduction.py:353-395: 13-token prompt + 20 greedy tokens,
+    Kitty lifecycle, fp32) through its own dart-engine hook on the CPU gives these token ids and logits; the
+    same weights through this package's hook and kernels must give the same tokens."""
+
+    import numpy as np
+
+    from tests.golden.make_golden import TINY_QWEN3, TINY_QWEN3_CACHE, tiny_qwen3
+    from tests.helpers import load_golden
+
+    gold = load_golden("qwen3_hook.npz")
+    model = tiny_qwen3()
+    checksum = float(sum(p.detach().double().abs().sum() for p in model.parameters()))
+    assert abs(checksum - float(gold["weight_checksum"])) < 1e-6 * checksum, "the seeded weights differ from the recorded run"
+    model = attach_dart_fused_attention(model.cuda())
+    cache = DartHFCache(dart.DartKVCacheConfig(metadata_dtype=torch.float32, **TINY_QWEN3_CACHE))
+    prompt = torch.from_numpy(gold["prompt"]).cuda()
+    tokens = prompt
+    with torch.no_grad():
+        logits = model(prompt, past_key_values=cache, use_cache=True).logits[:, -1]
+        for step in range(20):
+            np.testing.assert_allclose(logits.cpu().numpy(), gold["logits"][step], rtol=0, atol=2e-4)
+            nxt = logits.argmax(-1, keepdim=True)
+            tokens = torch.cat((tokens, nxt), dim=1)
+            logits = model(nxt, past_key_values=cache, use_cache=True).logits[:, -1]
+    assert tokens.shape == (2, 13 + 20) and TINY_QWEN3["vocab_size"] == 128
+    np.testing.assert_array_equal(tokens.cpu().numpy(), gold["tokens"])
+    assert cache.get_seq_length() == 33

@@ -158,3 +158,18 @@ def test_large_seeded_pages_match_oracle():
     np.testing.assert_array_equal(to_np(m.high_values), om.high_values)
     np.testing.assert_array_equal(to_np(m.scale), om.scale)
     np.testing.assert_array_equal(to_np(m.zero_point), om.zero_point)
+
+
+def test_random_channel_selection_is_shared_across_the_batch():
+    # src/dart/mixed.py:145-152: one random permutation per head, the same for every batch row
+    keys = torch.randn(3, 2, 16, 32).cuda()
+    mask, indices = dart.select_key_channels(keys, 0.25, strategy="random")
+    assert tuple(mask.shape) == (3, 2, 32) and tuple(indices.shape) == (3, 2, 8)
+    assert mask.dtype == torch.bool and int(mask.sum()) == 3 * 2 * 8
+    assert torch.equal(indices[0], indices[1]) and torch.equal(indices[0], indices[2])
+    for head in range(2):
+        assert len(set(indices[0, head].tolist())) == 8
+        assert torch.equal(mask[0, head].nonzero().flatten().cpu(), indices[0, head].sort().values.cpu())
+    q = dart.quantize_key_mixed(keys, group_size=16, promote_ratio=0.25, strategy="random")
+    assert tuple(q.high_values.shape[:3]) == (3, 2, 8) and torch.equal(q.channel_indices[0], q.channel_indices[2])
+    assert (q.dequantize() - keys).abs().max() < 1.6
