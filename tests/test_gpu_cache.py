@@ -10,6 +10,7 @@ import torch
 
 import dartkv_b200 as dart
 from dartkv_b200.lifecycle import plan_append
+from dartkv_b200.synthetic import make_kvq
 from oracle import dartkv_oracle as orc
 from tests.golden.cases import CACHE_CASES, TORCH_DTYPES, build_inputs
 from tests.helpers import load_golden, to_np
