@@ -19,6 +19,7 @@ DENSE_PAGE, QUANTIZED_PAGE, MIXED_PAGE = 0, 1, 2
 DIV_TRUE, DIV_RECIPROCAL = 0, 1
 DEQUANT_PER_OP, DEQUANT_FP32, DEQUANT_FUSED = 0, 1, 2
 SCORE_MAGNITUDE, SCORE_VARIANCE = 0, 1
+OK, EINVAL, ECUDA, ELIMIT = 0, -1, -2, -3
 
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 CODE_DTYPE = {v: k for k, v in DTYPE_CODE.items()}
@@ -30,6 +31,7 @@ EXPORTS = (
     "dartkv_cache_geometry", "dartkv_cache_append", "dartkv_cache_materialize", "dartkv_decode_workspace_bytes",
     "dartkv_decode_attention", "dartkv_decode_plan", "dartkv_decode_status", "dartkv_builtin_scratch_bytes",
     "dartkv_decode_attention_builtin_scratch", "dartkv_shard_range", "dartkv_decode_split_override",
+    "dartkv_lifecycle_plan", "dartkv_cache_append_step",
 )
 
 
@@ -60,6 +62,19 @@ class DecodePlanInfo(Structure):
         ("kernel", c_int32), ("quads", c_int32), ("stream_blocks", c_int32), ("total_splits", c_int32),
         ("units", c_int64), ("generic_splits", c_int32), ("generic_chunk", c_int32),
     ]
+
+
+class LifecycleConfig(Structure):
+    """Mirror of ``dartkv_lifecycle_config``."""
+
+    _fields_ = [("page_size", c_int32), ("sink_tokens", c_int32), ("local_tokens", c_int32),
+                ("value_local_tokens", c_int32), ("hold_partial_pages", c_int32)]
+
+
+class LifecycleStateC(Structure):
+    """Mirror of ``dartkv_lifecycle_state``."""
+
+    _fields_ = [("seen", c_int32), ("k_packed_end", c_int32), ("v_packed_end", c_int32), ("key_pages", c_int32)]
 
 
 class Shard(Structure):
@@ -113,6 +128,9 @@ def _load() -> ctypes.CDLL:
     lib.dartkv_decode_plan.argtypes = [POINTER(CacheDesc), i32, i32, i32, i32, POINTER(DecodePlanInfo)]
     lib.dartkv_builtin_scratch_bytes.restype = c_int64
     lib.dartkv_decode_split_override.argtypes = [c_char_p]
+    lib.dartkv_lifecycle_plan.argtypes = [POINTER(LifecycleConfig), POINTER(LifecycleStateC), i32, POINTER(AppendPlan)]
+    lib.dartkv_cache_append_step.argtypes = [POINTER(CacheDesc), POINTER(LifecycleConfig), POINTER(LifecycleStateC), p, p,
+                                             i32, i64, i64, i64, p, p, POINTER(AppendPlan), p]
     lib.dartkv_shard_range.argtypes = [i32, i32, i32, i32, POINTER(Shard)]
     lib.dartkv_decode_attention_builtin_scratch.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, p]
     for name in EXPORTS:

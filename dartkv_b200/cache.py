@@ -147,6 +147,10 @@ class DartKVCache:
         self._page_run_cache: dict = {}
         self._forced_indices: Optional[torch.Tensor] = None
         self._plan = AppendPlan()
+        cfg = self.config
+        self._c_cfg = _lib.LifecycleConfig(cfg.page_size, cfg.sink_tokens, cfg.local_tokens, cfg.value_local_tokens,
+                                           int(cfg.hold_partial_pages))
+        self._c_state = _lib.LifecycleStateC()
 
     # ------------------------------------------------------------------ simple accessors
     @property
@@ -291,34 +295,57 @@ class DartKVCache:
         cfg = self.config
         if cfg.promote_ratio > 0.0 and cfg.channel_selection != "magnitude" and channel_indices is None:
             channel_indices = self._host_selected_indices(keys, chunk)
-        # plan on a copy of the lifecycle state: the host state advances only once the launch has been accepted, so
-        # a failed append (bad argument, out of memory while growing the pools, CUDA error) leaves both in step
-        life = LifecycleState(self._life.seen, self._life.k_packed_end, self._life.v_packed_end,
-                              list(self._life.pages), list(self._life.sink_pieces))
-        fields = plan_append(cfg, life, chunk)
         d = self._desc
-        idx = None
-        if channel_indices is not None and d.promoted:
-            expected = fields.num_pages + fields.requantize_last_page
+        plan = self._plan
+        if channel_indices is None or not d.promoted:
+            # common path, one call: the library plans the step from its own copy of the lifecycle state and appends.
+            # It refuses (nothing launched, state unchanged) when the pools are too small: grow them and repeat.
+            for attempt in range(2):
+                with device_guard(device):
+                    rc = LIB.dartkv_cache_append_step(
+                        ctypes.byref(d), ctypes.byref(self._c_cfg), ctypes.byref(self._c_state), ptr(keys), ptr(values),
+                        chunk, keys.stride(0), keys.stride(1), keys.stride(2), None, ptr(self._pools["nonfinite"]),
+                        ctypes.byref(plan), stream_ptr(device))
+                if rc != _lib.ELIMIT or attempt:
+                    break
+                rows_needed = plan.value_end - cfg.sink_tokens if plan.value_end > plan.value_begin else 0
+                self._ensure_capacity(
+                    2 * plan.key_pages_after if plan.key_pages_after > d.max_key_pages else d.max_key_pages,
+                    2 * rows_needed if rows_needed > d.max_value_tokens else d.max_value_tokens)
+            check(rc)
+        else:
+            # forced promoted channels: plan first (their page count has to match the step), then append
+            state = _lib.LifecycleStateC(self._c_state.seen, self._c_state.k_packed_end, self._c_state.v_packed_end,
+                                         self._c_state.key_pages)
+            check(LIB.dartkv_lifecycle_plan(ctypes.byref(self._c_cfg), ctypes.byref(state), chunk, ctypes.byref(plan)))
+            expected = plan.num_pages + plan.requantize_last_page
             idx = channel_indices.to(device=device, dtype=torch.int32).reshape(batch * heads, -1, d.promoted)
             if idx.shape[1] != expected:
                 raise ValueError(f"channel_indices must carry {expected} pages, got {idx.shape[1]}")
-            if fields.requantize_last_page:
+            if plan.requantize_last_page:
                 idx = torch.cat((idx[:, :1].reshape(-1), idx[:, 1:].reshape(-1)))
             idx = idx.contiguous()
-        rows_needed = life.v_packed_end - cfg.sink_tokens
-        if len(life.pages) > d.max_key_pages or rows_needed > d.max_value_tokens:
-            # pools grow by doubling; the old contents are copied on the current stream
-            self._ensure_capacity(2 * len(life.pages) if len(life.pages) > d.max_key_pages else d.max_key_pages,
-                                  2 * rows_needed if rows_needed > d.max_value_tokens else d.max_value_tokens)
-        plan = self._plan
-        for name in _PLAN_FIELDS:
-            setattr(plan, name, getattr(fields, name))
-        with device_guard(device):
-            check(LIB.dartkv_cache_append(
-                ctypes.byref(d), ctypes.byref(plan), ptr(keys), ptr(values), keys.stride(0), keys.stride(1),
-                keys.stride(2), ptr(idx), ptr(self._pools["nonfinite"]), stream_ptr(device)))
-        self._life = life
+            rows_needed = plan.value_end - cfg.sink_tokens if plan.value_end > plan.value_begin else 0
+            if plan.key_pages_after > d.max_key_pages or rows_needed > d.max_value_tokens:
+                self._ensure_capacity(
+                    2 * plan.key_pages_after if plan.key_pages_after > d.max_key_pages else d.max_key_pages,
+                    2 * rows_needed if rows_needed > d.max_value_tokens else d.max_value_tokens)
+            with device_guard(device):
+                check(LIB.dartkv_cache_append(
+                    ctypes.byref(d), ctypes.byref(plan), ptr(keys), ptr(values), keys.stride(0), keys.stride(1),
+                    keys.stride(2), ptr(idx), ptr(self._pools["nonfinite"]), stream_ptr(device)))
+            self._c_state = state
+        # the step was accepted: bring the host-side segment bookkeeping up to date from its plan
+        life = self._life
+        if plan.sink_copy:
+            life.sink_pieces.append((plan.chunk_start, plan.sink_copy))
+        page = cfg.page_size
+        for i in range(plan.num_pages):
+            life.pages.append((plan.page_token_start + i * page,
+                               plan.last_page_tokens if i == plan.num_pages - 1 else page))
+        life.seen = plan.seen_after
+        life.k_packed_end = plan.k_packed_end_after
+        life.v_packed_end = plan.v_packed_end_after
         self._layout_version += 1
         self._invalidate_page_descriptors()
 

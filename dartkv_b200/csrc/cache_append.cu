@@ -525,3 +525,105 @@ extern "C" int dartkv_cache_materialize(const dartkv_cache_desc* desc, int side,
   DARTKV_LAUNCH_OK("materialize_kernel");
   return DARTKV_OK;
 }
+
+
+// ---------------------------------------------------------------------------- host-side lifecycle planner
+// The integer bookkeeping of the reference's cache lifecycle (src/dart/cache.py:168-190, 403-470) as a host
+// function: which chunk tokens go to the sink rows, which become key pages, which value rows get packed and what
+// stays dense in the ring.  Pages are appended in sequence order, so the state is four integers.
+extern "C" int dartkv_lifecycle_plan(const dartkv_lifecycle_config* cfg, dartkv_lifecycle_state* state,
+                                     int chunk_tokens, dartkv_append_plan* plan) {
+  DARTKV_REQUIRE(cfg != nullptr && state != nullptr && plan != nullptr, "lifecycle_plan received a null pointer");
+  DARTKV_REQUIRE(chunk_tokens > 0, "key/value sequence and head dimensions must be non-empty");
+  DARTKV_REQUIRE(cfg->page_size > 0 && cfg->sink_tokens >= 0 && cfg->local_tokens >= 0 && cfg->value_local_tokens >= 0,
+                 "bad lifecycle configuration");
+  const int page = cfg->page_size, sink_total = cfg->sink_tokens;
+  const int seen = state->seen;
+  DARTKV_REQUIRE((int64_t)seen + chunk_tokens < (1ll << 31) - 2 * page, "token count overflows 32 bits");
+  const int sink_copy = min(max(0, sink_total - seen), chunk_tokens);
+  const int rest = chunk_tokens - sink_copy;
+  const int rest_start = seen + sink_copy;
+  const int chunk_end = seen + chunk_tokens;
+  const int sink_filled_after = min(chunk_end, sink_total);
+  // invariant: packed_end is the end of the packed range, or min(seen, sink_tokens) while nothing is packed
+  const int k_end = state->k_packed_end, v_end = state->v_packed_end;
+  const int pending_k = seen - k_end, pending_v = seen - v_end;
+  int num_pages = 0, last_page_tokens = page;
+  const int page_token_start = pending_k ? k_end : rest_start;
+  const int value_begin = pending_v ? v_end : rest_start;
+  int value_end = value_begin;
+  int requantize = 0;
+  if (rest > 0) {
+    if (cfg->value_local_tokens) {
+      // keys page by page behind `local_tokens`, values token by token behind the newest `value_local_tokens`;
+      // a one-token append right after a prompt that ended on a page boundary re-quantizes the last page
+      if (seen > 0 && pending_k == 0 && cfg->local_tokens == 1 && rest == 1 && state->key_pages > 0) requantize = 1;
+      const int stream = pending_k + rest;
+      const int local = seen == 0 ? 0 : cfg->local_tokens;
+      num_pages = max(0, stream - local) / page;
+      value_end = value_begin + max(0, pending_v + rest - cfg->value_local_tokens);
+    } else if (cfg->hold_partial_pages || cfg->local_tokens) {
+      const int stream = pending_k + rest;
+      num_pages = max(0, stream - cfg->local_tokens) / page;
+      value_end = value_begin + num_pages * page;
+    } else {
+      num_pages = (rest + page - 1) / page;
+      last_page_tokens = rest - (num_pages - 1) * page;
+      value_end = value_begin + rest;
+    }
+  }
+  int k_end_after;
+  if (num_pages > 0) k_end_after = page_token_start + (num_pages - 1) * page + last_page_tokens;
+  else if (state->key_pages > 0) k_end_after = k_end;
+  else k_end_after = sink_filled_after;
+  int v_end_after;
+  if (value_end > value_begin) v_end_after = value_end;
+  else if (v_end > sink_total) v_end_after = v_end;
+  else v_end_after = sink_filled_after;
+  plan->chunk_start = seen;
+  plan->chunk_tokens = chunk_tokens;
+  plan->sink_copy = sink_copy;
+  plan->first_page = state->key_pages;
+  plan->num_pages = num_pages;
+  plan->page_token_start = page_token_start;
+  plan->last_page_tokens = last_page_tokens;
+  plan->value_begin = value_begin;
+  plan->value_end = value_end;
+  plan->ring_begin = max(k_end_after, rest_start);
+  plan->reserved = 0;
+  plan->seen_after = chunk_end;
+  plan->k_packed_end_after = k_end_after;
+  plan->v_packed_end_after = v_end_after;
+  plan->key_pages_after = state->key_pages + num_pages;
+  plan->requantize_last_page = requantize;
+  state->seen = chunk_end;
+  state->k_packed_end = k_end_after;
+  state->v_packed_end = v_end_after;
+  state->key_pages += num_pages;
+  return DARTKV_OK;
+}
+
+// Plan and append in one call.  The state advances only if every launch of the step was accepted.
+extern "C" int dartkv_cache_append_step(const dartkv_cache_desc* desc, const dartkv_lifecycle_config* cfg,
+                                        dartkv_lifecycle_state* state, const void* keys, const void* values,
+                                        int chunk_tokens, int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                                        const int32_t* indices, int32_t* nonfinite, dartkv_append_plan* plan_out,
+                                        void* stream) {
+  DARTKV_REQUIRE(state != nullptr, "append_step received a null pointer");
+  dartkv_lifecycle_state next = *state;
+  dartkv_append_plan plan;
+  int rc = dartkv_lifecycle_plan(cfg, &next, chunk_tokens, &plan);
+  if (rc) return rc;
+  if (plan_out) *plan_out = plan;
+  DARTKV_REQUIRE(desc != nullptr, "null descriptor");
+  if (plan.key_pages_after > desc->max_key_pages ||
+      (plan.value_end > plan.value_begin && plan.value_end - desc->sink_tokens > desc->max_value_tokens)) {
+    dartkv_set_error("append needs %d key pages and %d packed value rows; the pools hold %d and %d: grow them first",
+                     plan.key_pages_after, plan.value_end - desc->sink_tokens, desc->max_key_pages, desc->max_value_tokens);
+    return DARTKV_ELIMIT;
+  }
+  rc = dartkv_cache_append(desc, &plan, keys, values, stride_b, stride_h, stride_t, indices, nonfinite, stream);
+  if (rc) return rc;
+  *state = next;
+  return DARTKV_OK;
+}

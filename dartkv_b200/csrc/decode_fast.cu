@@ -27,6 +27,13 @@
 
 namespace {
 
+// timing experiments only (a library built with these computes garbage)
+#if defined(PEROP_SKIP_MMA)
+#define PEROP_MMA(acc, a0, a1, a2, a3, b0, b1) ((acc)[0] += __uint_as_float((a0) ^ (a1) ^ (a2) ^ (a3) ^ (b0) ^ (b1)))
+#else
+#define PEROP_MMA(acc, a0, a1, a2, a3, b0, b1) H::mma(acc, a0, a1, a2, a3, b0, b1)
+#endif
+
 #ifndef PEROP_QK_UNROLL
 #define PEROP_QK_UNROLL 2
 #endif
@@ -76,6 +83,7 @@ __device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc&
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) s_acc[e][mt][i] = 0.0f;
+#if !defined(PEROP_SKIP_QK)
   for (int ks = 0; ks < prom_steps; ++ks) {
     const int s0 = 8 * ks + c, s1 = s0 + 4;
     const uint4 a0 = ps.kpar_a[s0], a1 = ps.kpar_a[s1];
@@ -92,17 +100,22 @@ __device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc&
 #ifndef PEROP_SINGLE_ACC
     if (ks & 1) {
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[1][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+      for (int mt = 0; mt < 2; ++mt) PEROP_MMA(s_acc[1][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
     } else
 #endif
     {
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) H::mma(s_acc[0][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+      for (int mt = 0; mt < 2; ++mt) PEROP_MMA(s_acc[0][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
     }
   }
   auto plain_step = [&](int ks, float (&acc)[2][4]) {
+#if defined(PEROP_SKIP_KPAR)
+    const uint4 a0 = make_uint4(cc.mask[0], cc.mask[1], cc.magic[0], cc.magic[1]), a1 = a0;
+    const uint2 o0 = make_uint2(cc.magic[2], 32u * (8 * ks + c)), o1 = make_uint2(cc.magic[2], 32u * (8 * ks + c + 4));
+#else
     const uint4 a0 = ps.kpar_a[8 * ks + c], a1 = ps.kpar_a[8 * ks + c + 4];
     const uint2 o0 = ps.kpar_b[8 * ks + c], o1 = ps.kpar_b[8 * ks + c + 4];
+#endif
     const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
     const uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + o1.y);
     uint32_t r0[4], r1[4];
@@ -111,7 +124,7 @@ __device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc&
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) H::mma(acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
+    for (int mt = 0; mt < 2; ++mt) PEROP_MMA(acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
   };
 #ifdef PEROP_SINGLE_ACC
 #pragma unroll kQkUnroll
@@ -126,6 +139,7 @@ __device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc&
     plain_step(kp + 1, s_acc[1]);
   }
 #endif
+#endif   // PEROP_SKIP_QK
 
   // ---- online softmax for head c over this warp's 64 tokens (this thread: 8 of them)
   float mx = -INFINITY;
@@ -185,6 +199,7 @@ __device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc&
   // byte selectors that duplicate the scale / zero of this thread's value group into both halves
   const uint32_t sel_s = GN == 2 ? (gv ? 0x3232u : 0x1010u) : 0x1010u;
   const uint32_t sel_z = GN == 2 ? (gv ? 0x3232u : 0x1010u) : 0x3232u;
+#if !defined(PEROP_SKIP_PV)
 #pragma unroll kPvUnroll
   for (int ks = 0; ks < 8; ++ks) {
     const int t0 = 16 * ks + 4 * HF + c, t1 = t0 + 8;
@@ -209,10 +224,13 @@ __device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc&
     const uint32_t pl0 = (uint32_t)prob_lo[l0] << shift, pl1 = (uint32_t)prob_lo[l1] << shift;
     // all hi-part MMAs first, then the lo parts: back-to-back MMAs never share an accumulator
 #pragma unroll
-    for (int mt = 0; mt < 4; ++mt) H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], ph0, ph1);
+    for (int mt = 0; mt < 4; ++mt) PEROP_MMA(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], ph0, ph1);
+#if !defined(PEROP_SKIP_PVLO)
 #pragma unroll
-    for (int mt = 0; mt < 4; ++mt) H::mma(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], pl0, pl1);
+    for (int mt = 0; mt < 4; ++mt) PEROP_MMA(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], pl0, pl1);
+#endif
   }
+#endif   // PEROP_SKIP_PV
 }
 
 template <int DT>
@@ -319,6 +337,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
 
       // ---- per-page setup: each warp orders the channels (promoted slots first) into its own copy, then
       // fills the per-position constants of its half of the contraction positions
+#if !defined(PEROP_SKIP_SETUP)
       {
         uint8_t* order = ps.order[hf];
         uint8_t* flag = ps.is_promoted[hf];
@@ -356,6 +375,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
           ps.kpar_b[p] = make_uint2(H::mul(ss, H::neg_magic(2)), 32u * ch);
         }
       }
+#endif
       pair_barrier(pair);
 
       if (d.value_groups == 2) {

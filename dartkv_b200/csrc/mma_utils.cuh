@@ -150,6 +150,18 @@ __device__ __forceinline__ uint32_t align_codes(uint32_t w, int code, int pos, i
   return left >= 0 ? (w << left) : (w >> (-left));
 }
 
+// timing experiments only (a library built with these computes garbage): drop one of the two packed ops
+#if defined(PEROP_SKIP_ADD)
+#define DQ_ADD(t, z) (t)
+#else
+#define DQ_ADD(t, z) H::add((t), (z))
+#endif
+#if defined(PEROP_SKIP_FMA)
+#define DQ_FMA(m, s, ms) (m)
+#else
+#define DQ_FMA(m, s, ms) H::fma((m), (s), (ms))
+#endif
+
 // ---------------------------------------------------------------------------- exact packed dequantization
 // A packed word holds sixteen 2-bit codes; code u of the low half and code u of the high half share
 // a (scale, zero) pair, so one 32-bit register of two 16-bit floats is produced per u:
@@ -171,7 +183,7 @@ __device__ __forceinline__ void dequant_word2(const CodeConsts<DT>& k, uint32_t 
       if (u < 8) {
         const uint32_t m = and_or(x, k.mask[j], k.magic[j]);
         const uint32_t ms = j == 0 ? ms0 : (j == 1 ? ms1 : ms2);
-        r[u] = H::add(H::fma(m, ss, ms), zz);
+        r[u] = DQ_ADD(DQ_FMA(m, ss, ms), zz);
       }
     }
   }
@@ -192,7 +204,7 @@ __device__ __forceinline__ void dequant_word4(const CodeConsts<DT>& k, uint32_t 
       const int u = 2 * grp + j;
       // the high field of position j sits where the low field of position j+1 does
       const uint32_t m = and_or(xh, k.mask[j + 1], and_or(xl, k.mask[j], k.magic[j]));
-      r[u] = H::add(H::fma(m, ss, j == 0 ? ms0 : ms1), zz);
+      r[u] = DQ_ADD(DQ_FMA(m, ss, j == 0 ? ms0 : ms1), zz);
     }
   }
 }
@@ -207,17 +219,17 @@ __device__ __forceinline__ void dequant_half2(const CodeConsts<DT>& k, uint32_t 
   if (HF == 0) {
     const uint32_t xa = align_codes(w, 0, P0);   // codes 0,1,2 at positions 0,1,2
     const uint32_t xb = align_codes(w, 3, P0);   // code 3 at position 0
-    r[0] = H::add(H::fma(and_or(xa, k.mask[0], k.magic[0]), ss, ms0), zz);
-    r[1] = H::add(H::fma(and_or(xa, k.mask[1], k.magic[1]), ss, ms1), zz);
-    r[2] = H::add(H::fma(and_or(xa, k.mask[2], k.magic[2]), ss, ms2), zz);
-    r[3] = H::add(H::fma(and_or(xb, k.mask[0], k.magic[0]), ss, ms0), zz);
+    r[0] = DQ_ADD(DQ_FMA(and_or(xa, k.mask[0], k.magic[0]), ss, ms0), zz);
+    r[1] = DQ_ADD(DQ_FMA(and_or(xa, k.mask[1], k.magic[1]), ss, ms1), zz);
+    r[2] = DQ_ADD(DQ_FMA(and_or(xa, k.mask[2], k.magic[2]), ss, ms2), zz);
+    r[3] = DQ_ADD(DQ_FMA(and_or(xb, k.mask[0], k.magic[0]), ss, ms0), zz);
   } else {
     const uint32_t xa = align_codes(w, 3, P0);   // codes 4,5 at positions 1,2
     const uint32_t xb = align_codes(w, 6, P0);   // codes 6,7 at positions 0,1
-    r[0] = H::add(H::fma(and_or(xa, k.mask[1], k.magic[1]), ss, ms1), zz);
-    r[1] = H::add(H::fma(and_or(xa, k.mask[2], k.magic[2]), ss, ms2), zz);
-    r[2] = H::add(H::fma(and_or(xb, k.mask[0], k.magic[0]), ss, ms0), zz);
-    r[3] = H::add(H::fma(and_or(xb, k.mask[1], k.magic[1]), ss, ms1), zz);
+    r[0] = DQ_ADD(DQ_FMA(and_or(xa, k.mask[1], k.magic[1]), ss, ms1), zz);
+    r[1] = DQ_ADD(DQ_FMA(and_or(xa, k.mask[2], k.magic[2]), ss, ms2), zz);
+    r[2] = DQ_ADD(DQ_FMA(and_or(xb, k.mask[0], k.magic[0]), ss, ms0), zz);
+    r[3] = DQ_ADD(DQ_FMA(and_or(xb, k.mask[1], k.magic[1]), ss, ms1), zz);
   }
 }
 
@@ -234,7 +246,7 @@ __device__ __forceinline__ void dequant_half4(const CodeConsts<DT>& k, uint32_t 
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const uint32_t m = and_or(xh, k.mask[j + 1], and_or(xl, k.mask[j], k.magic[j]));
-      r[2 * grp + j] = H::add(H::fma(m, ss, j == 0 ? ms0 : ms1), zz);
+      r[2 * grp + j] = DQ_ADD(DQ_FMA(m, ss, j == 0 ? ms0 : ms1), zz);
     }
   }
 }

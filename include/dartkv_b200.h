@@ -164,6 +164,25 @@ int dartkv_cache_append(const dartkv_cache_desc* desc, const dartkv_append_plan*
                         int64_t stride_b, int64_t stride_h, int64_t stride_t,
                         const int32_t* indices, int32_t* nonfinite, void* stream);
 
+/* The lifecycle rules themselves as host arithmetic, so that an append needs no bookkeeping in the caller's
+ * language: dartkv_lifecycle_plan turns (configuration, state, chunk length) into the plan of the step and
+ * advances the state (src/dart/cache.py:168-190,403-470; the state is what the reference keeps in its segment
+ * lists: tokens seen, end of the packed keys, end of the packed values, key pages so far).
+ * dartkv_cache_append_step plans and appends in one call; the state advances only if the step was accepted, and
+ * DARTKV_ELIMIT is returned (nothing launched, state unchanged) when the pools of desc are too small for the step. */
+typedef struct dartkv_lifecycle_config {
+  int32_t page_size, sink_tokens, local_tokens, value_local_tokens, hold_partial_pages;
+} dartkv_lifecycle_config;
+typedef struct dartkv_lifecycle_state {
+  int32_t seen, k_packed_end, v_packed_end, key_pages;
+} dartkv_lifecycle_state;
+int dartkv_lifecycle_plan(const dartkv_lifecycle_config* cfg, dartkv_lifecycle_state* state, int chunk_tokens,
+                          dartkv_append_plan* plan);
+int dartkv_cache_append_step(const dartkv_cache_desc* desc, const dartkv_lifecycle_config* cfg,
+                             dartkv_lifecycle_state* state, const void* keys, const void* values, int chunk_tokens,
+                             int64_t stride_b, int64_t stride_h, int64_t stride_t, const int32_t* indices,
+                             int32_t* nonfinite, dartkv_append_plan* plan_out, void* stream);
+
 /* Materialize tokens [t0, t1) of the cache as dense [B,H,t1-t0,D] tensors (cache.get(),
  * src/dart/cache.py:192-199); side 0 = keys, 1 = values. */
 int dartkv_cache_materialize(const dartkv_cache_desc* desc, int side, int32_t t0, int32_t t1, int flavour,

@@ -31,10 +31,21 @@ def _check_sequence(cfg: dart.DartKVCacheConfig, chunks, head_dim=8):
     rng = np.random.default_rng(0)
     oracle = orc.OracleCache(_oracle_cfg(cfg), "f32")
     state = LifecycleState()
+    c_cfg = _lib.LifecycleConfig(cfg.page_size, cfg.sink_tokens, cfg.local_tokens, cfg.value_local_tokens,
+                                 int(cfg.hold_partial_pages))
+    c_state = _lib.LifecycleStateC()
+    c_plan = _lib.AppendPlan()
     for chunk in chunks:
         data = rng.standard_normal((1, 1, chunk, head_dim)).astype(np.float32)
         oracle.append(data, data)
         plan = plan_append(cfg, state, chunk)
+        # the library's own planner (what dartkv_cache_append_step runs) gives the same plan and state
+        assert _lib.LIB.dartkv_lifecycle_plan(ctypes.byref(c_cfg), ctypes.byref(c_state), chunk, ctypes.byref(c_plan)) == 0
+        for name, _ in _lib.AppendPlan._fields_:
+            if name != "reserved":
+                assert getattr(c_plan, name) == getattr(plan, name), name
+        assert (c_state.seen, c_state.k_packed_end, c_state.v_packed_end, c_state.key_pages) == \
+            (state.seen, state.k_packed_end, state.v_packed_end, len(state.pages))
         assert plan.seen_after == oracle.seen_tokens
         # key pages: one per quantized oracle key segment, same lengths
         oracle_pages = [orc.segment_tokens(s) for s in oracle.key_segments if not isinstance(s, np.ndarray)]
