@@ -8,10 +8,11 @@
 // row into the next; the host chooses).  A block of 8 warps (4 warp pairs) hands page p of its run to pair
 // p % 4.  A pair streams its pages through a two-stage shared-memory ring filled by 1-D bulk async copies
 // (one key blob of up to 5760 bytes, 4096 bytes of value codes and up to 1024 bytes of value metadata per
-// page, completion on an mbarrier).  The two warps of a pair split the page's tokens (codes 0-3 / 4-7 of
-// every packed 16-bit half, i.e. 64 tokens each) and keep private online-softmax states, so they only meet
-// at two named barriers per page; the block merges all eight states when it leaves a row and writes one
-// partial per row it touched.  One more short block per row, launched after the stream blocks, handles the
+// page, completion on an mbarrier).  For the logits the two warps of a pair split the CONTRACTION (alternate
+// steps of eight channels each, whole 32-bit code words per thread) and swap half of their partial sums through
+// shared memory; for the softmax and P.V they split the page's TOKENS (codes 0-3 / 4-7 of every packed 16-bit
+// half, i.e. 64 tokens each) and keep private online-softmax states.  They meet at two named barriers per page;
+// the block merges all eight states when it leaves a row and writes one partial per row it touched.  One more short block per row, launched after the stream blocks, handles the
 // dense tokens: the sink prefix and everything after the last page that is packed on both the key and the
 // value side.
 //
@@ -35,10 +36,10 @@ namespace {
 #endif
 
 #ifndef PEROP_QK_UNROLL
-#define PEROP_QK_UNROLL 2
+#define PEROP_QK_UNROLL 3
 #endif
 #ifndef PEROP_PV_UNROLL
-#define PEROP_PV_UNROLL 2
+#define PEROP_PV_UNROLL 8
 #endif
 constexpr int kQkUnroll = PEROP_QK_UNROLL, kPvUnroll = PEROP_PV_UNROLL;
 
@@ -62,95 +63,97 @@ struct BlockSmem {
 // One warp's share of a staged page: QK over its 64 tokens, online softmax, PV over the same tokens.
 // GN = value groups per token (1 or 2).
 template <int DT, int GN>
-__device__ __forceinline__ void page_half(const int HF, const dartkv_cache_desc& d, PairSmem& ps, const uint8_t* blob, uint16_t* prob,
-                                          const uint8_t* q_thread, const CodeConsts<DT>& cc, int K, int prom_steps,
+__device__ __forceinline__ void page_half(const int HF, const int pair, const int lane, const dartkv_cache_desc& d, PairSmem& ps,
+                                          const uint8_t* blob, uint16_t* prob, uint16_t* partner_prob, const uint8_t* q_thread, const CodeConsts<DT>& cc, int K, int prom_steps,
                                           float scale2, int g, int c, int jp, int hq, int gv, float (&o_acc)[4][4],
                                           float& m_run, float& l_run) {
   using H = Half2Ops<DT>;
-  // HF is a run-time value, so one copy of this code serves both warps of a pair: the second warp shifts its four
-  // codes of every half-word down into the place of the first warp's
-  const int half_shift = 8 * HF;
   const uint8_t* low_thread = blob + 4 * g;   // + 32 * channel = this thread's word of the channel row
   const uint32_t* high = reinterpret_cast<const uint32_t*>(blob + d.key_off_high);
 
-  // ---- logits: S[token pair][(head, j')] over the doubled contraction (channel, j); this warp's
-  // token pairs are codes 4*HF .. 4*HF+3 of every half-word: m-tile mt covers local pairs 2mt, 2mt+1.
-  // Even and odd contraction steps use separate accumulators so consecutive MMAs are independent.
-  float s_acc[2][2][4];
+  // ---- logits.  The two warps of a pair split the CONTRACTION: warp HF takes the steps of eight positions
+  // 2i + HF, i = 0..7 (the promoted slots come first in the order, so both warps get their share of them), and
+  // computes partial logits of all 128 tokens: S[token pair][(head, j')] over the doubled contraction
+  // (channel, j).  A thread reads the whole 32-bit word g of a channel row (tokens 16g .. 16g+15): register u
+  // pairs tokens 16g+u and 16g+u+8, m-tile mt takes registers 2mt (row g) and 2mt+1 (row g+8).
+  float s_acc[4][4];
 #pragma unroll
-  for (int e = 0; e < 2; ++e)
+  for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) s_acc[e][mt][i] = 0.0f;
+    for (int i = 0; i < 4; ++i) s_acc[mt][i] = 0.0f;
 #if !defined(PEROP_SKIP_QK)
-  for (int ks = 0; ks < prom_steps; ++ks) {
-    const int s0 = 8 * ks + c, s1 = s0 + 4;
+  const int my_prom_steps = (prom_steps + 1 - HF) >> 1;   // promoted steps with the parity of this warp
+  for (int i = 0; i < my_prom_steps; ++i) {
+    const int s0 = 8 * (2 * i + HF) + c, s1 = s0 + 4;
     const uint4 a0 = ps.kpar_a[s0], a1 = ps.kpar_a[s1];
     const uint2 o0 = ps.kpar_b[s0], o1 = ps.kpar_b[s1];
     const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
     const uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + o1.y);
     const uint32_t h0 = s0 < K ? high[s0 * 8 + g] : 0u;
     const uint32_t h1 = s1 < K ? high[s1 * 8 + g] : 0u;
-    uint32_t r0[4], r1[4];
-    dequant_half4<DT, 0>(cc, w0 >> half_shift, h0 >> half_shift, a0.x, a0.y, a0.z, a0.w, r0);
-    dequant_half4<DT, 0>(cc, w1 >> half_shift, h1 >> half_shift, a1.x, a1.y, a1.z, a1.w, r1);
+    uint32_t r0[8], r1[8];
+    dequant_word4<DT>(cc, w0, h0, a0.x, a0.y, a0.z, a0.w, r0);
+    dequant_word4<DT>(cc, w1, h1, a1.x, a1.y, a1.z, a1.w, r1);
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
-#ifndef PEROP_SINGLE_ACC
-    if (ks & 1) {
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt) PEROP_MMA(s_acc[1][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
-    } else
-#endif
-    {
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt) PEROP_MMA(s_acc[0][mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
-    }
+    for (int mt = 0; mt < 4; ++mt) PEROP_MMA(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
   }
-  auto plain_step = [&](int ks, float (&acc)[2][4]) {
+#pragma unroll kQkUnroll
+  for (int i = my_prom_steps; i < 8; ++i) {
+    const int s0 = 8 * (2 * i + HF) + c, s1 = s0 + 4;
 #if defined(PEROP_SKIP_KPAR)
     const uint4 a0 = make_uint4(cc.mask[0], cc.mask[1], cc.magic[0], cc.magic[1]), a1 = a0;
-    const uint2 o0 = make_uint2(cc.magic[2], 32u * (8 * ks + c)), o1 = make_uint2(cc.magic[2], 32u * (8 * ks + c + 4));
+    const uint2 o0 = make_uint2(cc.magic[2], 32u * s0), o1 = make_uint2(cc.magic[2], 32u * s1);
 #else
-    const uint4 a0 = ps.kpar_a[8 * ks + c], a1 = ps.kpar_a[8 * ks + c + 4];
-    const uint2 o0 = ps.kpar_b[8 * ks + c], o1 = ps.kpar_b[8 * ks + c + 4];
+    const uint4 a0 = ps.kpar_a[s0], a1 = ps.kpar_a[s1];
+    const uint2 o0 = ps.kpar_b[s0], o1 = ps.kpar_b[s1];
 #endif
     const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
     const uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + o1.y);
-    uint32_t r0[4], r1[4];
-    dequant_half2<DT, 0>(cc, w0 >> half_shift, a0.x, a0.y, a0.z, a0.w, o0.x, r0);
-    dequant_half2<DT, 0>(cc, w1 >> half_shift, a1.x, a1.y, a1.z, a1.w, o1.x, r1);
+    uint32_t r0[8], r1[8];
+    dequant_word2<DT>(cc, w0, a0.x, a0.y, a0.z, a0.w, o0.x, r0);
+    dequant_word2<DT>(cc, w1, a1.x, a1.y, a1.z, a1.w, o1.x, r1);
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) PEROP_MMA(acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
-  };
-#ifdef PEROP_SINGLE_ACC
-#pragma unroll kQkUnroll
-  for (int ks = prom_steps; ks < 16; ++ks) plain_step(ks, s_acc[0]);
-#else
-  // one plain step, if needed, to put the unrolled loop on an even step index
-  const int first_plain = prom_steps + (prom_steps & 1);
-  if (first_plain != prom_steps && prom_steps < 16) plain_step(prom_steps, s_acc[1]);
-#pragma unroll kQkUnroll
-  for (int kp = first_plain; kp < 16; kp += 2) {
-    plain_step(kp, s_acc[0]);
-    plain_step(kp + 1, s_acc[1]);
+    for (int mt = 0; mt < 4; ++mt) PEROP_MMA(s_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], b0, b1);
   }
-#endif
 #endif   // PEROP_SKIP_QK
+
+  // ---- exchange: this warp goes on with the tokens of m-tiles 2HF and 2HF+1 (codes 4HF .. 4HF+3 of every packed
+  // half-word), so it hands its partial logits of the other two m-tiles to its partner and takes the partner's
+  // partials of its own.  The message travels through the receiver's probability table, which is idle here: both
+  // warps left the previous page's P.V behind at the barrier that ended that page.
+  float s_sum[2][4];
+  {
+    float4* to_partner = reinterpret_cast<float4*>(partner_prob);
+    const float4* from_partner = reinterpret_cast<const float4*>(prob);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      float4 v;
+      v.x = HF ? s_acc[mt][0] : s_acc[2 + mt][0]; v.y = HF ? s_acc[mt][1] : s_acc[2 + mt][1];
+      v.z = HF ? s_acc[mt][2] : s_acc[2 + mt][2]; v.w = HF ? s_acc[mt][3] : s_acc[2 + mt][3];
+      to_partner[mt * 32 + lane] = v;
+    }
+    pair_barrier(pair);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      const float4 v = from_partner[mt * 32 + lane];
+      s_sum[mt][0] = ((HF ? s_acc[2 + mt][0] : s_acc[mt][0]) + v.x) * scale2;
+      s_sum[mt][1] = ((HF ? s_acc[2 + mt][1] : s_acc[mt][1]) + v.y) * scale2;
+      s_sum[mt][2] = ((HF ? s_acc[2 + mt][2] : s_acc[mt][2]) + v.z) * scale2;
+      s_sum[mt][3] = ((HF ? s_acc[2 + mt][3] : s_acc[mt][3]) + v.w) * scale2;
+    }
+    __syncwarp();   // every lane has read its message before any lane writes probabilities over it
+  }
 
   // ---- online softmax for head c over this warp's 64 tokens (this thread: 8 of them)
   float mx = -INFINITY;
-  float s_sum[2][4];
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      s_sum[mt][i] = (s_acc[0][mt][i] + s_acc[1][mt][i]) * scale2;
-      mx = fmaxf(mx, s_sum[mt][i]);
-    }
+    for (int i = 0; i < 4; ++i) mx = fmaxf(mx, s_sum[mt][i]);
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
@@ -336,7 +339,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       const uint16_t* kzero = reinterpret_cast<const uint16_t*>(blob + d.key_off_zero);
 
       // ---- per-page setup: each warp orders the channels (promoted slots first) into its own copy, then
-      // fills the per-position constants of its half of the contraction positions
+      // fills the per-position constants of the contraction steps it owns (steps 2i + hf); nothing of this is
+      // shared with the other warp of the pair
 #if !defined(PEROP_SKIP_SETUP)
       {
         uint8_t* order = ps.order[hf];
@@ -367,7 +371,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
         __syncwarp();
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-          const int p = 64 * hf + lane + 32 * i;
+          const int f = lane + 32 * i;                        // 64 positions of this warp
+          const int p = 8 * (2 * (f >> 3) + hf) + (f & 7);
           const int ch = order[p];
           const uint32_t ss = (uint32_t)kscale[ch] * 0x00010001u;
           const uint32_t zz = (uint32_t)kzero[ch] * 0x00010001u;
@@ -376,12 +381,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
         }
       }
 #endif
-      pair_barrier(pair);
+      __syncwarp();
 
       if (d.value_groups == 2) {
-        page_half<DT, 2>(hf, d, ps, blob, ps.prob[hf], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
+        page_half<DT, 2>(hf, pair, lane, d, ps, blob, ps.prob[hf], ps.prob[hf ^ 1], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
       } else {
-        page_half<DT, 1>(hf, d, ps, blob, ps.prob[hf], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
+        page_half<DT, 1>(hf, pair, lane, d, ps, blob, ps.prob[hf], ps.prob[hf ^ 1], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
       }
 
       pair_barrier(pair);
