@@ -378,7 +378,7 @@ def gpu_arm(args, wl) -> None:
 
     import dartkv_b200 as dart
     from dartkv_b200 import _lib
-    from dartkv_b200.sharding import gather_outputs, shard_plan
+    from dartkv_b200.sharding import PeerGather, gather_outputs, shard_plan
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -405,6 +405,15 @@ def gpu_arm(args, wl) -> None:
     q3 = query[:, :, 0].contiguous()
     gather_kwargs = dict(shard=shard, batch=wl["batch"], kv_heads=GEOM["kv_heads"])
     q_lo, q_hi = shard.query_heads(hq, GEOM["kv_heads"])
+    # how the outputs reach every rank: stored straight into the peers' gathered tensors by the kernel that
+    # normalizes them ("peer", the default), or an NCCL all-gather after the decode call ("nccl")
+    peer, gather_kind = None, "nccl all_gather_into_tensor"
+    if world > 1 and args.gather == "peer":
+        try:
+            peer = PeerGather(shard, wl["batch"], hq, GEOM["kv_heads"], d, torch.bfloat16, device)
+            gather_kind = "peer stores from the decode kernels (symmetric memory over NVLink, no multicast)"
+        except Exception as exc:   # symmetric memory cannot be set up on this machine: NCCL does the gather
+            gather_kind = f"nccl all_gather_into_tensor (peer stores unavailable: {type(exc).__name__}: {str(exc)[:120]})"
 
     flavour = _lib.DEQUANT_FUSED if args.flavour == "fused" else _lib.DEQUANT_PER_OP
 
@@ -412,6 +421,10 @@ def gpu_arm(args, wl) -> None:
         dart.decode_attention(q3, cache, out=out, flavour=flavour)
 
     def step():
+        nonlocal gathered
+        if peer is not None:
+            gathered = dart.decode_attention(q3, cache, out=out, flavour=flavour, peer_gather=peer)
+            return
         decode()
         if world > 1:
             gather_outputs(out, gathered, **gather_kwargs)  # the only cross-GPU traffic: final output gather
@@ -431,13 +444,13 @@ def gpu_arm(args, wl) -> None:
     gather_check = None
     if world > 1:
         mine_ok = bool(torch.equal(gathered[shard.row_begin:shard.row_end, q_lo:q_hi], out))
-        peer = shard_plan(wl["batch"], GEOM["kv_heads"], world, (rank + 1) % world)
-        peer_heads = (peer.head_begin, peer.head_end)
-        peer_cache, peer_query = build_device_cache([peer.row_begin], wl["ctx"], wl["seed"], device, heads=peer_heads)
+        other = shard_plan(wl["batch"], GEOM["kv_heads"], world, (rank + 1) % world)
+        peer_heads = (other.head_begin, other.head_end)
+        peer_cache, peer_query = build_device_cache([other.row_begin], wl["ctx"], wl["seed"], device, heads=peer_heads)
         peer_out = torch.empty((1, peer_query.shape[1], d), dtype=torch.bfloat16, device=device)
         dart.decode_attention(peer_query[:, :, 0].contiguous(), peer_cache, out=peer_out, flavour=flavour)
-        p_lo, p_hi = peer.query_heads(hq, GEOM["kv_heads"])
-        got = gathered[peer.row_begin, p_lo:p_hi].float()
+        p_lo, p_hi = other.query_heads(hq, GEOM["kv_heads"])
+        got = gathered[other.row_begin, p_lo:p_hi].float()
         diff = (got - peer_out[0].float()).abs()
         # the split of the work differs with the batch size, so the two fp32 sums may round differently: one
         # output ulp (or 2e-3) is allowed
@@ -497,11 +510,15 @@ def gpu_arm(args, wl) -> None:
 
     def e2e_step():
         dev_q.copy_(host_q, non_blocking=True)
-        dart.decode_attention(dev_q, cache, out=out, flavour=flavour)
-        if world > 1:
+        if peer is not None:
+            full = dart.decode_attention(dev_q, cache, out=out, flavour=flavour, peer_gather=peer)
+            host_out.copy_(full[shard.row_begin:shard.row_end, q_lo:q_hi], non_blocking=True)
+        elif world > 1:
+            dart.decode_attention(dev_q, cache, out=out, flavour=flavour)
             gather_outputs(out, gathered, **gather_kwargs)
             host_out.copy_(gathered[shard.row_begin:shard.row_end, q_lo:q_hi], non_blocking=True)
         else:
+            dart.decode_attention(dev_q, cache, out=out, flavour=flavour)
             host_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream(device).synchronize()
 
@@ -523,6 +540,8 @@ def gpu_arm(args, wl) -> None:
     if gather_check is not None:
         extra["gather_checked"] = True
         extra["gather_check"] = gather_check
+        extra["gather"] = gather_kind
+        extra["decode_status"] = cache.decode_status()
     if rank == 0 and world == 1 and not args.skip_extras:
         del gathered
         other = _lib.DEQUANT_FUSED if args.flavour == "per_op" else _lib.DEQUANT_PER_OP
@@ -679,6 +698,8 @@ def main() -> None:
     parser.add_argument("--skip-extras", action="store_true", help="skip the append microbench and the CPU baseline")
     parser.add_argument("--flavour", choices=("per_op", "fused"), default="per_op",
                         help="dequantization arithmetic of the timed decode call (default: the pinned per-op rounding)")
+    parser.add_argument("--gather", choices=("peer", "nccl"), default="peer",
+                        help="multi-GPU output gather: peer stores from the decode kernels (default) or NCCL")
     parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (e.g. one rank's share)")
     parser.add_argument("--context", type=int, default=0, help="override the workload's context length")
     args = parser.parse_args()

@@ -31,7 +31,7 @@ EXPORTS = (
     "dartkv_cache_geometry", "dartkv_cache_append", "dartkv_cache_materialize", "dartkv_decode_workspace_bytes",
     "dartkv_decode_attention", "dartkv_decode_plan", "dartkv_decode_status", "dartkv_builtin_scratch_bytes",
     "dartkv_decode_attention_builtin_scratch", "dartkv_shard_range", "dartkv_decode_split_override",
-    "dartkv_lifecycle_plan", "dartkv_cache_append_step",
+    "dartkv_lifecycle_plan", "dartkv_cache_append_step", "dartkv_decode_attention_scatter",
 )
 
 
@@ -75,6 +75,17 @@ class LifecycleStateC(Structure):
     """Mirror of ``dartkv_lifecycle_state``."""
 
     _fields_ = [("seen", c_int32), ("k_packed_end", c_int32), ("v_packed_end", c_int32), ("key_pages", c_int32)]
+
+
+MAX_PEERS = 8
+
+
+class PeerScatter(Structure):
+    """Mirror of ``dartkv_peer_scatter``."""
+
+    _fields_ = [("world_size", c_int32), ("rank", c_int32), ("dst_row_begin", c_int32), ("dst_head_begin", c_int32),
+                ("dst_heads_total", c_int32), ("epoch", ctypes.c_uint32), ("out", c_void_p * MAX_PEERS),
+                ("flags", c_void_p * MAX_PEERS)]
 
 
 class Shard(Structure):
@@ -124,6 +135,8 @@ def _load() -> ctypes.CDLL:
     lib.dartkv_decode_workspace_bytes.argtypes = [POINTER(CacheDesc), i32, i32]
     lib.dartkv_decode_workspace_bytes.restype = c_int64
     lib.dartkv_decode_attention.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, i64, p, p]
+    lib.dartkv_decode_attention_scatter.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, i64, p,
+                                                    POINTER(PeerScatter), p]
     lib.dartkv_decode_status.argtypes = [p, POINTER(c_int), p]
     lib.dartkv_decode_plan.argtypes = [POINTER(CacheDesc), i32, i32, i32, i32, POINTER(DecodePlanInfo)]
     lib.dartkv_builtin_scratch_bytes.restype = c_int64

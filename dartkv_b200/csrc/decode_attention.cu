@@ -9,6 +9,7 @@
 // This file holds the generic kernel (any page geometry, bit width, dtype; CUDA-core fp32 math)
 // and the merge; the tensor-core kernel for the headline geometry is in decode_fast.cu.
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -235,9 +236,23 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cach
 // one block per (batch, query head): combine split partials, normalize, cast
 // With stream_blocks > 0 (tensor-core layouts) a row's valid slots are its dense slot 0 plus one per stream block
 // that touched its (batch, kv head); the remaining slots of the row hold stale data and are skipped.
+// With peers.world_size > 1 the normalized rows are also stored into every rank's gathered output tensor (plain
+// stores through peer-mapped pointers over NVLink), and the block that finishes last publishes this rank's arrival
+// flag on every peer and then waits, with a bound, for every peer's flag on this rank: when the kernel ends, the
+// gathered tensor of this rank is complete.  Nothing here waits on another kernel of the same GPU.
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 __global__ void decode_merge_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
                                     const float* __restrict__ part_acc, int total_splits, int D, void* out, int out_dt,
-                                    int stream_blocks, int64_t units, int quads, int query_heads, int kv_heads) {
+                                    int stream_blocks, int64_t units, int quads, int query_heads, int kv_heads,
+                                    dartkv_peer_scatter peers, int* status, unsigned int* done_counter) {
   // launched with programmatic stream serialization: the grid may become resident while the kernel before it
   // drains, and waits here until that kernel's memory is visible
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -260,13 +275,39 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_m, const floa
     if (ms != -INFINITY) l += part_l[row * splits + s] * expf(ms - m);
   }
   float inv = 1.0f / fmaxf(l, 1e-20f);
+  const int64_t out_row = blockIdx.x;
+  const int64_t peer_row = (int64_t)(peers.dst_row_begin + out_row / query_heads) * peers.dst_heads_total +
+                           peers.dst_head_begin + out_row % query_heads;
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float acc = 0.0f;
     for (int s = 0; s < splits; ++s) {
       float ms = part_m[row * splits + s];
       if (ms != -INFINITY) acc += part_acc[(row * splits + s) * D + c] * expf(ms - m);
     }
-    store_f(out, out_dt, row * D + c, acc * inv);
+    store_f(out, out_dt, out_row * D + c, acc * inv);
+    for (int p = 0; p < peers.world_size; ++p) store_f(peers.out[p], out_dt, peer_row * D + c, acc * inv);
+  }
+  if (peers.world_size > 1) {
+    __threadfence_system();   // this thread's peer stores are visible system-wide before the block reports in
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int ticket = atomicAdd(done_counter, 1u);
+      if (ticket == gridDim.x - 1) {
+        *done_counter = 0;      // ready for the next call on this stream
+        __threadfence_system();
+        for (int p = 0; p < peers.world_size; ++p) st_release_sys(peers.flags[p] + peers.rank, peers.epoch);
+        // every peer's rows have landed here once its flag shows this step (or a later one)
+        bool ok = true;
+        for (int p = 0; p < peers.world_size && ok; ++p) {
+          ok = false;
+          for (int spin = 0; spin < (1 << 21); ++spin) {   // about half a second with the sleep below
+            if ((int)(ld_acquire_sys(peers.flags[peers.rank] + p) - peers.epoch) >= 0) { ok = true; break; }
+            __nanosleep(200);
+          }
+        }
+        if (!ok) atomicExch(status, 2);
+      }
+    }
   }
 }
 
@@ -289,16 +330,16 @@ int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, 
                                  float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream);
 
 static int dartkv_sm_count() {
-  static int cached = 0;
-  if (cached == 0) {
-    int device = 0, count = 0;
-    if (cudaGetDevice(&device) == cudaSuccess &&
-        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && count > 0)
-      cached = count;
-    else
-      cached = 148;   // B200
+  // per device: a process may drive GPUs of different sizes
+  static std::atomic<int> cached[64];
+  int device = 0, count = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+  count = cached[device].load(std::memory_order_relaxed);
+  if (count == 0) {
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = 148;   // B200
+    cached[device].store(count, std::memory_order_relaxed);
   }
-  return cached;
+  return count;
 }
 
 // work-split override: a debugging / testing knob, kept off the per-call path (the environment is read once)
@@ -442,9 +483,9 @@ extern "C" int dartkv_decode_status(const void* workspace, int* status_out, void
   return DARTKV_OK;
 }
 
-extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads,
-                                       float scale, int flavour, int tokens, void* workspace,
-                                       int64_t workspace_bytes, void* out, void* stream_) {
+static int decode_attention_impl(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads,
+                                 float scale, int flavour, int tokens, void* workspace, int64_t workspace_bytes,
+                                 void* out, const dartkv_peer_scatter* peers, void* stream_) {
   DARTKV_REQUIRE(d != nullptr, "null descriptor");
   DARTKV_REQUIRE(query && out && workspace, "decode_attention received a null pointer");
   DARTKV_REQUIRE(dartkv_valid_dtype(q_dtype), "query must be f32, f16 or bf16");
@@ -493,12 +534,39 @@ extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* q
     attribute.val.programmaticStreamSerializationAllowed = 1;
     config.attrs = &attribute;
     config.numAttrs = 1;
+    dartkv_peer_scatter none{};
+    unsigned int* done_counter = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(workspace) + 4);
     DARTKV_CUDA_OK(cudaLaunchKernelEx(&config, decode_merge_kernel, (const float*)part_m, (const float*)part_l,
                                       (const float*)part_acc, L.total_splits, D, out, q_dtype,
-                                      L.fast ? L.stream_blocks : 0, (int64_t)L.units, L.quads, query_heads, d->kv_heads));
+                                      L.fast ? L.stream_blocks : 0, (int64_t)L.units, L.quads, query_heads, d->kv_heads,
+                                      peers ? *peers : none, status, done_counter));
   }
   DARTKV_LAUNCH_OK("decode_merge_kernel");
   return DARTKV_OK;
+}
+
+extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads,
+                                       float scale, int flavour, int tokens, void* workspace,
+                                       int64_t workspace_bytes, void* out, void* stream) {
+  return decode_attention_impl(d, query, q_dtype, query_heads, scale, flavour, tokens, workspace, workspace_bytes, out,
+                               nullptr, stream);
+}
+
+extern "C" int dartkv_decode_attention_scatter(const dartkv_cache_desc* d, const void* query, int q_dtype,
+                                               int query_heads, float scale, int flavour, int tokens, void* workspace,
+                                               int64_t workspace_bytes, void* out, const dartkv_peer_scatter* peers,
+                                               void* stream) {
+  DARTKV_REQUIRE(peers != nullptr, "decode_attention_scatter received a null pointer");
+  DARTKV_REQUIRE(peers->world_size >= 1 && peers->world_size <= DARTKV_MAX_PEERS, "world_size must be in [1, %d]",
+                 DARTKV_MAX_PEERS);
+  DARTKV_REQUIRE(peers->rank >= 0 && peers->rank < peers->world_size, "rank must be in [0, world_size)");
+  DARTKV_REQUIRE(peers->dst_row_begin >= 0 && peers->dst_head_begin >= 0 &&
+                     peers->dst_head_begin + query_heads <= peers->dst_heads_total,
+                 "the rows of this rank do not fit the gathered tensor");
+  for (int p = 0; p < peers->world_size; ++p)
+    DARTKV_REQUIRE(peers->out[p] != nullptr && peers->flags[p] != nullptr, "peer %d has a null pointer", p);
+  return decode_attention_impl(d, query, q_dtype, query_heads, scale, flavour, tokens, workspace, workspace_bytes, out,
+                               peers, stream);
 }
 
 // ---------------------------------------------------------------------------- built-in scratch variant

@@ -24,6 +24,8 @@
 // K, (token, j) for V) against a block-diagonal query / probability operand whose columns are
 // (query head, j).  Algorithmic HBM bytes per page and (batch, kv head): 10880.
 
+#include <atomic>
+
 #include "decode_fast_common.cuh"
 
 namespace {
@@ -439,14 +441,15 @@ int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int
   FastArgs a{query, query_heads, scale, flavour, quads, stream_blocks, units, total_splits, part_m, part_l, part_acc, status};
   dim3 grid(stream_blocks + d->batch * d->kv_heads);
   {
-    // the shared-memory opt-in is per device and per kernel: ask once
-    static bool ready[64] = {};
+    // the shared-memory opt-in is per device and per kernel: ask once per device (the flags are atomic; two threads
+    // that race on a device's first call both set the attribute, which is harmless)
+    static std::atomic<bool> ready[64];
     int device = 0;
     DARTKV_CUDA_OK(cudaGetDevice(&device));
-    if (device < 0 || device >= 64 || !ready[device]) {
+    if (device < 0 || device >= 64 || !ready[device].load(std::memory_order_acquire)) {
       DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fast_kernel<DARTKV_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
       DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fast_kernel<DARTKV_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-      if (device >= 0 && device < 64) ready[device] = true;
+      if (device >= 0 && device < 64) ready[device].store(true, std::memory_order_release);
     }
   }
   if (d->dtype == DARTKV_BF16) {

@@ -20,8 +20,13 @@ from .page_table import DartPageRun, DartPageTable
 
 
 def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional[float] = None,
-                     flavour: int = _lib.DEQUANT_PER_OP, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One query token per (batch, query head): ``query`` and the result are ``[B, Hq, D]``."""
+                     flavour: int = _lib.DEQUANT_PER_OP, out: Optional[torch.Tensor] = None,
+                     peer_gather=None) -> torch.Tensor:
+    """One query token per (batch, query head): ``query`` and the result are ``[B, Hq, D]``.
+
+    With ``peer_gather`` (a ``dartkv_b200.sharding.PeerGather``) the kernels also deliver this rank's rows to every
+    rank of the node and the gathered tensor ``[B_total, Hq_total, D]`` of the step is returned instead.
+    """
 
     if cache.shape is None or cache.seen_tokens == 0:
         raise ValueError("cache is empty")
@@ -40,6 +45,13 @@ def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional
         out = torch.empty_like(q)
     factor = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     workspace, capacity = cache.decode_workspace(q.shape[1])
+    if peer_gather is not None:
+        peers, gathered = peer_gather.next_step()
+        with device_guard(device):
+            check(LIB.dartkv_decode_attention_scatter(
+                ctypes.byref(cache.descriptor), ptr(q), _lib.DTYPE_CODE[q.dtype], q.shape[1], float(factor), flavour,
+                seen, ptr(workspace), workspace.numel(), ptr(out), ctypes.byref(peers), stream_ptr(device)))
+        return gathered
     with device_guard(device):
         check(LIB.dartkv_decode_attention(
             ctypes.byref(cache.descriptor), ptr(q), _lib.DTYPE_CODE[q.dtype], q.shape[1], float(factor), flavour,

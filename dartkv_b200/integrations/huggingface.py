@@ -78,7 +78,7 @@ class DartHFCache(Cache):
             raise RuntimeError(f"layer {layer_idx} has not been initialized") from exc
 
     def last_update_was_prefill(self, layer_idx: int) -> bool:
-        """Whether the most recent update for ``layer_idx`` created the layer."""
+        """True when the last ``update`` of this layer was its prefill, i.e. the call that created its cache."""
 
         return self._last_update_prefill.get(layer_idx, False)
 

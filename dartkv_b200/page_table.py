@@ -258,12 +258,4 @@ def _stack_uniform_run(table: DartPageTable, segments, first_page_index: int) ->
         value_group_size=first_value.group_size, page_size=table.page_size).validate()
 
 
-def _segment_mode(segment) -> int:
-    if isinstance(segment, torch.Tensor):
-        return DENSE_PAGE
-    if isinstance(segment, MixedQuantizedKey):
-        return MIXED_PAGE
-    return QUANTIZED_PAGE
-
-
 __all__ = ["DENSE_PAGE", "MIXED_PAGE", "QUANTIZED_PAGE", "DartPageTable", "DartPageRun"]

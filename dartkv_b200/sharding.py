@@ -100,3 +100,59 @@ def gather_outputs(local: torch.Tensor, out: Optional[torch.Tensor] = None, *, s
         h0 = (r % shard.head_groups) * heads_local
         out[peer.row_begin:peer.row_end, h0:h0 + heads_local].copy_(pieces[r, : peer.rows])
     return out
+
+
+class PeerGather:
+    """Gathered attention outputs delivered by the decode kernels themselves instead of an all-gather.
+
+    Every rank allocates two gathered tensors ``[batch, query_heads, head_dim]`` and a flag array in symmetric
+    memory (``torch.distributed._symmetric_memory``: each rank's allocation is mapped into every other rank of the
+    node).  ``decode_attention(..., peer_gather=self)`` then makes the kernel that normalizes the output rows store
+    them into all ranks' gathered tensors over NVLink, publish an arrival flag per peer and wait (bounded) for the
+    peers' flags; the call returns this rank's gathered tensor for the step.  Two tensors alternate because a rank
+    may run one step ahead of its slowest peer.  All ranks must make the same sequence of calls.
+    """
+
+    def __init__(self, shard: Shard, batch: int, query_heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype,
+                 device: torch.device, group=None) -> None:
+        import os
+
+        # plain peer mappings are all this needs: do not bind the allocations to an NVLink multicast object
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from ._lib import MAX_PEERS, PeerScatter
+
+        group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > MAX_PEERS:
+            raise ValueError(f"at most {MAX_PEERS} ranks (one node) can exchange outputs this way")
+        self.shard = shard
+        self.gathered = [symm_mem.empty((batch, query_heads, head_dim), dtype=dtype, device=device) for _ in range(2)]
+        self.flags = symm_mem.empty((max(self.world, 4),), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        handles = [symm_mem.rendezvous(t, group) for t in self.gathered]
+        flag_handle = symm_mem.rendezvous(self.flags, group)
+        self._handles = handles + [flag_handle]   # keep the mappings alive
+        q_lo, _ = shard.query_heads(query_heads, kv_heads)
+        self._structs = []
+        for handle in handles:
+            st = PeerScatter()
+            st.world_size, st.rank = self.world, self.rank
+            st.dst_row_begin, st.dst_head_begin, st.dst_heads_total = shard.row_begin, q_lo, query_heads
+            for peer in range(self.world):
+                st.out[peer] = int(handle.buffer_ptrs[peer])
+                st.flags[peer] = int(flag_handle.buffer_ptrs[peer])
+            self._structs.append(st)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)   # every rank's flags are zero before anyone publishes one
+
+    def next_step(self):
+        """(descriptor, gathered tensor) of the next step."""
+
+        self.epoch += 1
+        st = self._structs[self.epoch & 1]
+        st.epoch = self.epoch
+        return st, self.gathered[self.epoch & 1]

@@ -244,6 +244,30 @@ int dartkv_decode_attention_builtin_scratch(const dartkv_cache_desc* desc, const
                                             int query_heads, float scale, int flavour, int tokens, void* out,
                                             void* stream);
 
+/* Decode attention whose final step also delivers the output rows to every GPU of the node (no counterpart in the
+ * reference, which is single-device; it replaces an all-gather of the outputs after dartkv_decode_attention).
+ * The kernel that normalizes the rows stores them, besides `out`, into each rank's gathered tensor
+ * [batch, dst_heads_total, head_dim] through peer-mapped pointers (plain stores over NVLink, no multicast), at batch
+ * row dst_row_begin and query head dst_head_begin; its last block then writes `epoch` into flags[p][rank] on every
+ * peer p and waits until flags[rank][p] of every peer shows `epoch` (or a later one).  When the call's kernels have
+ * finished on this rank's stream, this rank's gathered tensor holds every rank's rows of the step.
+ *  - out[p] / flags[p]: the gathered tensor and the uint32 flag array [world_size] of rank p, as mapped into this
+ *    process (out[rank] / flags[rank] are this rank's own); flags start at zero and epochs grow by one per step.
+ *  - A rank may run at most one step ahead of its slowest peer, so callers alternate between two gathered tensors.
+ *  - The wait is bounded (about half a second): if a peer never arrives the workspace status word becomes 2 and the
+ *    kernel returns; nothing spins on a kernel of the same GPU.  All ranks must make the call for the step to end. */
+#define DARTKV_MAX_PEERS 8
+typedef struct dartkv_peer_scatter {
+  int32_t world_size, rank;
+  int32_t dst_row_begin, dst_head_begin, dst_heads_total;
+  uint32_t epoch;
+  void* out[DARTKV_MAX_PEERS];
+  uint32_t* flags[DARTKV_MAX_PEERS];
+} dartkv_peer_scatter;
+int dartkv_decode_attention_scatter(const dartkv_cache_desc* desc, const void* query, int q_dtype, int query_heads,
+                                    float scale, int flavour, int tokens, void* workspace, int64_t workspace_bytes,
+                                    void* out, const dartkv_peer_scatter* peers, void* stream);
+
 /* ------------------------------------------------------------------ sharding over the GPUs of one node
  * No counterpart in the reference (it is single-device): every (batch row, KV head) is independent on this path,
  * so a rank owns rows [row_begin,row_end) x KV heads [head_begin,head_end) with its own pools and no exchange on
