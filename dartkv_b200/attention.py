@@ -43,8 +43,37 @@ def streamed_dart_attention(query: torch.Tensor, cache: DartKVCache, *, scale: O
         raise ValueError("query batch and head_dim must match the cache")
     if query.shape[1] % kv_heads:
         raise ValueError("query heads must be divisible by cache KV heads")
-    outputs = [decode_attention(query[:, :, i], cache, scale=scale) for i in range(query.shape[2])]
-    return torch.stack(outputs, dim=2)
+    tokens = query.shape[2]
+    if tokens == 1:
+        return decode_attention(query[:, :, 0], cache, scale=scale).unsqueeze(2)
+    # Several query tokens (no mask between them, like the reference): the tokens of a query head attend to the
+    # same KV head, so t tokens x rep query heads are served by ONE launch as t * rep query heads of that KV head.
+    # The tensor-core kernels take up to 4 of them per KV head, the generic kernel up to 16.
+    rep = query.shape[1] // kv_heads
+    per_launch = max(1, 16 // rep)
+    if rep <= 4 and _tensor_core_plan(cache, query.dtype, kv_heads * rep * max(1, 4 // rep)):
+        per_launch = max(1, 4 // rep)
+    outputs = []
+    for first in range(0, tokens, per_launch):
+        chunk = query[:, :, first:first + per_launch]                      # [B, H*rep, t, D]
+        t = chunk.shape[2]
+        packed = chunk.reshape(batch, kv_heads, rep * t, head_dim)        # (head, token) pairs of one KV head together
+        out = decode_attention(packed.reshape(batch, kv_heads * rep * t, head_dim), cache, scale=scale)
+        outputs.append(out.view(batch, kv_heads * rep, t, head_dim))
+    return torch.cat(outputs, dim=2) if len(outputs) > 1 else outputs[0]
+
+
+def _tensor_core_plan(cache: DartKVCache, dtype: torch.dtype, query_heads: int) -> bool:
+    """Whether a decode call with this many query heads would run on a tensor-core kernel."""
+
+    import ctypes
+
+    from . import _lib
+
+    info = _lib.DecodePlanInfo()
+    rc = _lib.LIB.dartkv_decode_plan(ctypes.byref(cache.descriptor), _lib.DTYPE_CODE[dtype], query_heads,
+                                     _lib.DEQUANT_PER_OP, cache.seen_tokens, ctypes.byref(info))
+    return rc == 0 and info.kernel != 0
 
 
 __all__ = ["dense_attention", "streamed_dart_attention"]

@@ -142,3 +142,32 @@ def test_short_caches_with_few_or_no_packed_pages(tokens):
 def test_short_caches_token_by_token(tokens):
     run_case(torch.float16, seed=50 + tokens, batch=1, heads=2, hq=4, tokens=tokens, promote_ratio=0.25,
              chunks=[1] * tokens)
+
+
+@pytest.mark.parametrize("hq,tokens", [(2, 4), (4, 3), (8, 5)])
+def test_several_query_tokens_share_launches(hq, tokens):
+    # reference attention.py:70-72 attends every query token to the whole cache (no mask between them): the tokens
+    # of a head travel as extra heads of its KV head, up to four per launch on the tensor-core kernel
+    keys, values, query = make_kvq(40 + hq, 2, 2, 32 + 3 * 128 + 20, 128, query_heads=hq, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(tokens)
+    multi = torch.randn(2, hq, tokens, 128, generator=gen).to(torch.bfloat16)
+    cfg = dict(bits=2, page_size=128, key_group_size=128, value_group_size=64, sink_tokens=32, hold_partial_pages=True,
+               promote_ratio=0.25)
+    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=torch.bfloat16, **cfg))
+    oracle = orc.OracleCache(orc.CacheConfig(metadata_dtype="bf16", **cfg), "bf16")
+    cache.append(keys.cuda(), values.cuda())
+    oracle.append(to_np(keys), to_np(values))
+    from dartkv_b200 import _lib as lib_mod
+    before = lib_mod.LIB.dartkv_launch_count()
+    out = dart.streamed_dart_attention(multi.cuda(), cache)
+    launches = lib_mod.LIB.dartkv_launch_count() - before
+    per_launch = max(1, 4 // (hq // 2))
+    assert launches == 2 * -(-tokens // per_launch)          # decode + merge kernel per group of tokens
+    ref32 = orc.streamed_attention(to_np(multi), oracle, "bf16", return_f32=True)
+    assert tuple(out.shape) == (2, hq, tokens, 128)
+    assert np.all(np.abs(to_np(out) - ref32) <= np.abs(ref32) * 2.0 ** -8 + 2e-5)
+    # fp32 queries take the generic kernel, up to sixteen (head, token) pairs per KV head and launch
+    out32 = dart.streamed_dart_attention(multi.float().cuda(), cache)
+    np.testing.assert_allclose(to_np(out32), ref32, rtol=0, atol=1e-5)
+    single = dart.fused_dart_attention(multi[:, :, 1:2].cuda(), cache, fallback=False)
+    assert torch.equal(single, out[:, :, 1:2])
