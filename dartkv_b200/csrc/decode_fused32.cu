@@ -44,6 +44,8 @@ struct FusedPairSmem {
   // the other still reads this page's
   uint2 w_low[2][128];           // per channel: fp16 q*s*f of heads (0,1) and (2,3)
   uint2 w_high[2][32];           // per promoted slot: fp16 4*q*s*f of its channel, zero past the last slot
+  uint2 w_high_lo[2][32];        // what the fp16 rounding of w_high dropped, as fp16: the high plane carries most of a
+                                 // promoted (outlier) channel's magnitude, so its weights get a second term
   uint32_t u[2][8 * kUStride];   // per warp: [local token][head] = fp16 p*s*fv of (value group 0 | group 1 << 16)
   float bias_part[2][2][4];      // [table][warp]: partial sum_ch q*z per head
   uint64_t bar[2];
@@ -135,16 +137,22 @@ __device__ __forceinline__ void fused_page_half(const int HF, const int tb, cons
     // high plane of the promoted slots
     const uint8_t* high_thread = blob + d.key_off_high + 4 * g + 32 * c;
     const uint8_t* wh_thread = reinterpret_cast<const uint8_t*>(ps.w_high[tb]) + 8 * c + 4 * (g >> 2);
+    const uint8_t* wl_thread = reinterpret_cast<const uint8_t*>(ps.w_high_lo[tb]) + 8 * c + 4 * (g >> 2);
     for (int ks = 0; ks < prom_steps; ++ks) {
       uint32_t w0 = *reinterpret_cast<const uint32_t*>(high_thread + 256 * ks);
       uint32_t w1 = *reinterpret_cast<const uint32_t*>(high_thread + 256 * ks + 128);
       w0 >>= 8 * HF; w1 >>= 8 * HF;   // HF is a run-time value: one copy of this code serves both warps of a pair
       const uint32_t b0 = prmt(*reinterpret_cast<const uint32_t*>(wh_thread + 64 * ks), 0u, sel_w);
       const uint32_t b1 = prmt(*reinterpret_cast<const uint32_t*>(wh_thread + 64 * ks + 32), 0u, sel_w);
+      const uint32_t l0 = prmt(*reinterpret_cast<const uint32_t*>(wl_thread + 64 * ks), 0u, sel_w);
+      const uint32_t l1 = prmt(*reinterpret_cast<const uint32_t*>(wl_thread + 64 * ks + 32), 0u, sel_w);
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-        mma_f16(s_acc[mt], w0 & (0x00030003u << (4 * mt)), w0 & (0x000C000Cu << (4 * mt)), w1 & (0x00030003u << (4 * mt)),
-                w1 & (0x000C000Cu << (4 * mt)), b0, b1);
+      for (int mt = 0; mt < 2; ++mt) {
+        const uint32_t a0 = w0 & (0x00030003u << (4 * mt)), a1 = w0 & (0x000C000Cu << (4 * mt));
+        const uint32_t a2 = w1 & (0x00030003u << (4 * mt)), a3 = w1 & (0x000C000Cu << (4 * mt));
+        mma_f16(s_acc[mt], a0, a1, a2, a3, b0, b1);
+        mma_f16(s_odd[mt], a0, a1, a2, a3, l0, l1);   // same codes against the dropped part of the weights
+      }
     }
 #endif
   }
@@ -422,14 +430,19 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
         }
         // promoted slots: warp 1 of the pair, lane = slot
         if (hf == 1 && prom_steps > 0) {
-          uint2 wh = make_uint2(0u, 0u);
+          uint2 wh = make_uint2(0u, 0u), wl = make_uint2(0u, 0u);
           if (lane < K) {
             const int ch = reinterpret_cast<const int32_t*>(blob + d.key_off_index)[lane] & 127;
             const float s4 = 4.0f * f * md_to_float<DT>(reinterpret_cast<const uint16_t*>(blob + d.key_off_scale)[ch]);
             const float4 qh = *reinterpret_cast<const float4*>(bs.qf[ch]);
-            wh = make_uint2(pack_f16x2(qh.x * s4, qh.y * s4), pack_f16x2(qh.z * s4, qh.w * s4));
+            const float e0 = qh.x * s4, e1 = qh.y * s4, e2 = qh.z * s4, e3 = qh.w * s4;
+            wh = make_uint2(pack_f16x2(e0, e1), pack_f16x2(e2, e3));
+            const float2 h01 = __half22float2(*reinterpret_cast<const __half2*>(&wh.x));
+            const float2 h23 = __half22float2(*reinterpret_cast<const __half2*>(&wh.y));
+            wl = make_uint2(pack_f16x2(e0 - h01.x, e1 - h01.y), pack_f16x2(e2 - h23.x, e3 - h23.y));
           }
           ps.w_high[stage][lane] = wh;
+          ps.w_high_lo[stage][lane] = wl;
         }
       }
 #endif

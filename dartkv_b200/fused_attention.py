@@ -41,6 +41,19 @@ def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional
     if device != cache._device:
         raise ValueError("query and cache must be on the same device")
     q = query.contiguous()
+    rep = q.shape[1] // kv_heads
+    if rep > 4 and peer_gather is None and _grouped_heads_pay_off(cache, q.dtype, kv_heads, flavour, seen):
+        # The tensor-core kernels take up to four query heads per KV head.  Wider groups (5..16 heads per KV head)
+        # are served four heads at a time: every pass streams the packed pages again, which is still far cheaper
+        # than the CUDA-core kernel that would otherwise take the whole group.
+        grouped = q.view(batch, kv_heads, rep, head_dim)
+        result = out if out is not None else torch.empty_like(q)
+        result_view = result.view(batch, kv_heads, rep, head_dim)
+        for first in range(0, rep, 4):
+            part = grouped[:, :, first:first + 4].reshape(batch, -1, head_dim)
+            result_view[:, :, first:first + 4] = decode_attention(part, cache, scale=scale, flavour=flavour).view(
+                batch, kv_heads, -1, head_dim)
+        return result
     if out is None:
         out = torch.empty_like(q)
     factor = scale if scale is not None else 1.0 / math.sqrt(head_dim)
@@ -57,6 +70,15 @@ def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional
             ctypes.byref(cache.descriptor), ptr(q), _lib.DTYPE_CODE[q.dtype], q.shape[1], float(factor), flavour,
             seen, ptr(workspace), workspace.numel(), ptr(out), stream_ptr(device)))
     return out
+
+
+def _grouped_heads_pay_off(cache: DartKVCache, dtype: torch.dtype, kv_heads: int, flavour: int, seen: int) -> bool:
+    """True when a call with four query heads per KV head would run on a tensor-core kernel."""
+
+    info = _lib.DecodePlanInfo()
+    rc = LIB.dartkv_decode_plan(ctypes.byref(cache.descriptor), _lib.DTYPE_CODE[dtype], 4 * kv_heads, flavour, seen,
+                                ctypes.byref(info))
+    return rc == 0 and info.kernel != 0
 
 
 def fused_dart_attention(

@@ -113,12 +113,13 @@ def test_fused_flavour_equals_the_reference_triton_attention(name):
     np.testing.assert_allclose(to_np(out32), ref32, rtol=0, atol=1e-5)
     if case["dt"] != "f32":
         # 16-bit query: on the headline page geometry this is the tensor-core kernel, whose q*scale and p*scale
-        # weights are rounded to fp16 (2^-12 relative): measured within 2.7e-3 of the Triton kernel's fp32 result
-        # on keys with outlier channels (|out| up to 2.5), 1.3e-4 on Gaussian keys
+        # weights are fp16 (the high plane of promoted channels gets a second fp16 term).  Bar: 2e-3 on top of half
+        # an output ulp of the Triton kernel's fp32 result; measured 5.8e-4 with promoted keys that have outlier
+        # channels (|out| up to 2.5), 1.6e-3 with uniform 2-bit keys on the same data, 1e-4 on Gaussian keys
         out = dart.decode_attention(q3, cache, scale=scale, flavour=dart.DEQUANT_FUSED)
         ref16 = GOLD[f"cuda/{name}/fused"][:, :, 0]
         excess = np.abs(to_np(out) - ref32) - np.abs(ref32) * HALF_ULP[case["dt"]]
-        assert float(excess.max()) <= 3.5e-3, float(excess.max())
+        assert float(excess.max()) <= 2e-3, float(excess.max())
         diff = np.abs(to_np(out) - ref16)
-        assert np.all(diff <= 3.5e-3 + np.abs(ref16) * 2 * HALF_ULP[case["dt"]]), float(diff.max())
+        assert np.all(diff <= 2e-3 + np.abs(ref16) * 2 * HALF_ULP[case["dt"]]), float(diff.max())
     assert cache.decode_status() == 0

@@ -171,3 +171,24 @@ def test_several_query_tokens_share_launches(hq, tokens):
     np.testing.assert_allclose(to_np(out32), ref32, rtol=0, atol=1e-5)
     single = dart.fused_dart_attention(multi[:, :, 1:2].cuda(), cache, fallback=False)
     assert torch.equal(single, out[:, :, 1:2])
+
+
+@pytest.mark.parametrize("hq", [12, 16])
+def test_more_than_four_query_heads_per_kv_head_run_in_groups_of_four(hq):
+    # 6 and 8 query heads per KV head: two tensor-core passes instead of the CUDA-core kernel
+    from dartkv_b200 import _lib as lib_mod
+
+    cache, oracle, query = None, None, None
+    keys, values, query = make_kvq(50 + hq, 2, 2, 32 + 4 * 128 + 11, 128, query_heads=hq, dtype=torch.bfloat16)
+    cfg = dict(bits=2, page_size=128, key_group_size=128, value_group_size=64, sink_tokens=32, hold_partial_pages=True,
+               promote_ratio=0.25)
+    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=torch.bfloat16, **cfg))
+    oracle = orc.OracleCache(orc.CacheConfig(metadata_dtype="bf16", **cfg), "bf16")
+    cache.append(keys.cuda(), values.cuda())
+    oracle.append(to_np(keys), to_np(values))
+    before = lib_mod.LIB.dartkv_launch_count()
+    out = dart.fused_dart_attention(query.cuda(), cache, fallback=False)
+    assert lib_mod.LIB.dartkv_launch_count() - before == 2 * 2      # two passes of (decode + merge)
+    ref32 = orc.streamed_attention(to_np(query), oracle, "bf16", return_f32=True)
+    assert np.all(np.abs(to_np(out) - ref32) <= np.abs(ref32) * 2.0 ** -8 + 2e-5)
+    assert cache.decode_status() == 0
