@@ -172,32 +172,39 @@ __device__ __forceinline__ double any_abs_as_double(uint32_t magnitude) {
 }
 
 // KBITS: 0 = mixed 2+2-bit keys, else uniform keys with KBITS bits.
-// One block of 64 threads per (batch*head, page); thread p owns the adjacent channels 2p, 2p+1, which
-// travel together as one packed pair through both passes.
-template <int DT, int KBITS>
-__global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d, RowSource src, int first_slot,
-                                                            int num_pages, int page_token_start,
-                                                            const int32_t* __restrict__ indices, int32_t* nonfinite) {
+// One block of 64 * TQ threads per (batch*head, page); thread (tq, p) owns the adjacent channels 2p, 2p+1, which
+// travel together as one packed pair through both passes, for the tokens of quarter tq (TQ = 1, 2 or 4 splits
+// of the page's 128 tokens).  The splits meet twice in shared memory: for the channel statistics after pass 1
+// and for the ranks of the promoted channels.  More threads per page mean more resident warps per SM (the page
+// staging, 32 KiB, is what limits the pages per SM) and a shorter critical path when a step brings few pages.
+template <int DT, int KBITS, int TQ>
+__global__ void __launch_bounds__(64 * TQ) fast_key_pages_kernel(dartkv_cache_desc d, RowSource src, int first_slot,
+                                                                 int num_pages, int page_token_start,
+                                                                 const int32_t* __restrict__ indices, int32_t* nonfinite) {
   using P = Pack16<DT>;
+  constexpr int TOK = kP / TQ;   // tokens per thread and pass
   __shared__ __align__(16) uint32_t s_page[kP * 64];   // [token][channel pair]
   __shared__ __align__(16) uint32_t s_key[kD];
-  const int bh = blockIdx.x, pg = blockIdx.y, p = threadIdx.x;
+  __shared__ uint32_t s_part[TQ > 1 ? 3 * TQ * 64 : 1];      // [min | max | smallest magnitude][split][pair]
+  __shared__ double s_sum[TQ > 1 ? 2 * TQ * 64 : 1];         // [low | high channel][split][pair]
+  __shared__ int s_rank[TQ > 1 ? TQ * kD : 1];               // [split][channel]
+  const int bh = blockIdx.x, pg = blockIdx.y, p = threadIdx.x & 63, tq = threadIdx.x >> 6;
   const int t0 = page_token_start + pg * kP;
   const uint16_t *chunk_base, *ring_base;
   src.bases(bh, chunk_base, ring_base);
-  // stage the page: 2048 16-byte pieces, 32 per thread (thread p: piece p%16 of rows p/16, p/16+4, ...)
+  // stage the page: 2048 16-byte pieces (thread: piece tid%16 of rows tid/16, tid/16 + 4*TQ, ...)
   {
-    const int piece = p & 15, r0 = p >> 4;
+    const int piece = threadIdx.x & 15, r0 = threadIdx.x >> 4;
     char* dst = reinterpret_cast<char*>(s_page) + r0 * 256 + piece * 16;
     if (t0 >= src.chunk_start) {
       const char* from = reinterpret_cast<const char*>(chunk_base + (int64_t)(t0 - src.chunk_start + r0) * src.st) + piece * 16;
-      const int64_t step = src.st * 8;   // four rows, in bytes
+      const int64_t step = src.st * (8 * TQ);   // 4 * TQ rows, in bytes
 #pragma unroll 8
-      for (int k = 0; k < kP / 4; ++k) cp_async16(dst + k * 1024, from + k * step);
+      for (int k = 0; k < kP / (4 * TQ); ++k) cp_async16(dst + k * (1024 * TQ), from + k * step);
     } else {
-      for (int k = 0; k < kP / 4; ++k)
-        cp_async16(dst + k * 1024,
-                   reinterpret_cast<const char*>(src.row_from(chunk_base, ring_base, t0 + r0 + 4 * k)) + piece * 16);
+      for (int k = 0; k < kP / (4 * TQ); ++k)
+        cp_async16(dst + k * (1024 * TQ),
+                   reinterpret_cast<const char*>(src.row_from(chunk_base, ring_base, t0 + r0 + 4 * TQ * k)) + piece * 16);
     }
   }
   cp_async_wait_all();
@@ -208,11 +215,11 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
   // pass 1: packed min / max (NaN-propagating, so Inf/NaN inputs surface in them) and, for mixed pages,
   // sum |k| per channel in double (exact for 16-bit inputs).  The loop takes every magnitude for a normal
   // number; the smallest magnitude seen says whether a channel has to be summed again with care.
-  uint32_t mn2 = col[0], mx2 = mn2, min_mag2 = 0xFFFFFFFFu;
+  uint32_t mn2 = col[tq * TOK * 64], mx2 = mn2, min_mag2 = 0xFFFFFFFFu;
   constexpr uint32_t kMinNormal = DT == DARTKV_BF16 ? 0x80u : 0x400u;
   double sum_lo = 0.0, sum_hi = 0.0;
 #pragma unroll 8
-  for (int t = 0; t < kP; ++t) {
+  for (int t = tq * TOK; t < (tq + 1) * TOK; ++t) {
     const uint32_t x2 = col[t * 64];
     mn2 = P::min2(mn2, x2);
     mx2 = P::max2(mx2, x2);
@@ -221,6 +228,30 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
       min_mag2 = umin16x2(min_mag2, mag2);
       sum_lo += normal_abs_as_double<DT>(mag2 & 0xFFFFu);
       sum_hi += normal_abs_as_double<DT>(mag2 >> 16);
+    }
+  }
+  if (TQ > 1) {
+    // the splits of a channel pair exchange their partial statistics; every split then holds the page's values
+    s_part[(0 * TQ + tq) * 64 + p] = mn2;
+    s_part[(1 * TQ + tq) * 64 + p] = mx2;
+    if (KBITS == 0) {
+      s_part[(2 * TQ + tq) * 64 + p] = min_mag2;
+      s_sum[(0 * TQ + tq) * 64 + p] = sum_lo;
+      s_sum[(1 * TQ + tq) * 64 + p] = sum_hi;
+    }
+    __syncthreads();
+    mn2 = s_part[(0 * TQ) * 64 + p];
+    mx2 = s_part[(1 * TQ) * 64 + p];
+    if (KBITS == 0) { min_mag2 = s_part[(2 * TQ) * 64 + p]; sum_lo = s_sum[p]; sum_hi = s_sum[TQ * 64 + p]; }
+#pragma unroll
+    for (int o = 1; o < TQ; ++o) {
+      mn2 = P::min2(mn2, s_part[(0 * TQ + o) * 64 + p]);
+      mx2 = P::max2(mx2, s_part[(1 * TQ + o) * 64 + p]);
+      if (KBITS == 0) {
+        min_mag2 = umin16x2(min_mag2, s_part[(2 * TQ + o) * 64 + p]);
+        sum_lo += s_sum[(0 * TQ + o) * 64 + p];     // sums of 16-bit magnitudes are exact in double: any order
+        sum_hi += s_sum[(1 * TQ + o) * 64 + p];
+      }
     }
   }
   const float mn_lo = P::lo(mn2), mn_hi = P::hi(mn2), mx_lo = P::lo(mx2), mx_hi = P::hi(mx2);
@@ -238,10 +269,10 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
         if (ch == c_lo) slot_lo = k;
         if (ch == c_hi) slot_hi = k;
       }
-      for (int k = p; k < K; k += 64) idx_field[k] = mine[k];
+      for (int k = threadIdx.x; k < K; k += 64 * TQ) idx_field[k] = mine[k];
     } else if (K == kD) {
       slot_lo = c_lo; slot_hi = c_hi;
-      idx_field[c_lo] = c_lo; idx_field[c_hi] = c_hi;
+      if (tq == 0) { idx_field[c_lo] = c_lo; idx_field[c_hi] = c_hi; }
     } else if (K > 0) {
       if ((min_mag2 & 0xFFFFu) < kMinNormal || (min_mag2 >> 16) < kMinNormal) {   // zeros or subnormals: sum again
         sum_lo = 0.0; sum_hi = 0.0;
@@ -255,18 +286,29 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
       // patterns order like integers and one unsigned key carries both criteria
       const uint32_t key_lo = ((uint32_t)P::bits(__fdiv_rn((float)sum_lo, (float)kP)) << 7) | (uint32_t)(kD - 1 - c_lo);
       const uint32_t key_hi = ((uint32_t)P::bits(__fdiv_rn((float)sum_hi, (float)kP)) << 7) | (uint32_t)(kD - 1 - c_hi);
-      s_key[c_lo] = key_lo;
-      s_key[c_hi] = key_hi;
+      if (tq == 0) {
+        s_key[c_lo] = key_lo;
+        s_key[c_hi] = key_hi;
+      }
       __syncthreads();
+      // every split counts the larger keys among its share of the 128 channels
       int rank_lo = 0, rank_hi = 0;
 #pragma unroll 4
-      for (int o = 0; o < kD / 4; ++o) {
+      for (int o = tq * (kD / 4 / TQ); o < (tq + 1) * (kD / 4 / TQ); ++o) {
         const uint4 k4 = reinterpret_cast<const uint4*>(s_key)[o];
         rank_lo += (k4.x > key_lo) + (k4.y > key_lo) + (k4.z > key_lo) + (k4.w > key_lo);
         rank_hi += (k4.x > key_hi) + (k4.y > key_hi) + (k4.z > key_hi) + (k4.w > key_hi);
       }
-      if (rank_lo < K) { slot_lo = rank_lo; idx_field[rank_lo] = c_lo; }
-      if (rank_hi < K) { slot_hi = rank_hi; idx_field[rank_hi] = c_hi; }
+      if (TQ > 1) {
+        s_rank[tq * kD + c_lo] = rank_lo;
+        s_rank[tq * kD + c_hi] = rank_hi;
+        __syncthreads();
+        rank_lo = 0; rank_hi = 0;
+#pragma unroll
+        for (int o = 0; o < TQ; ++o) { rank_lo += s_rank[o * kD + c_lo]; rank_hi += s_rank[o * kD + c_hi]; }
+      }
+      if (rank_lo < K) { slot_lo = rank_lo; if (tq == 0) idx_field[rank_lo] = c_lo; }
+      if (rank_hi < K) { slot_hi = rank_hi; if (tq == 0) idx_field[rank_hi] = c_hi; }
     }
     qmax_lo = slot_lo >= 0 ? 15.0f : 3.0f;
     qmax_hi = slot_hi >= 0 ? 15.0f : 3.0f;
@@ -274,31 +316,36 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
     qmax_lo = qmax_hi = (float)((1 << KBITS) - 1);
   }
   const float scale_lo = scale_of<DT>(mn_lo, mx_lo, qmax_lo), scale_hi = scale_of<DT>(mn_hi, mx_hi, qmax_hi);
-  store_f(page + d.key_off_scale, d.md_dtype, 2 * p, scale_lo);
-  store_f(page + d.key_off_scale, d.md_dtype, 2 * p + 1, scale_hi);
-  store_f(page + d.key_off_zero, d.md_dtype, 2 * p, mn_lo);
-  store_f(page + d.key_off_zero, d.md_dtype, 2 * p + 1, mn_hi);
+  if (tq == 0) {
+    store_f(page + d.key_off_scale, d.md_dtype, 2 * p, scale_lo);
+    store_f(page + d.key_off_scale, d.md_dtype, 2 * p + 1, scale_hi);
+    store_f(page + d.key_off_zero, d.md_dtype, 2 * p, mn_lo);
+    store_f(page + d.key_off_zero, d.md_dtype, 2 * p + 1, mn_hi);
+  }
   const float inv_lo = inverse_scale<DT>(scale_lo), inv_hi = inverse_scale<DT>(scale_hi);
   const uint32_t cap2 = (uint32_t)P::bits((DT == DARTKV_BF16 ? 128.0f : 1024.0f) + qmax_lo) |
                         ((uint32_t)P::bits((DT == DARTKV_BF16 ? 128.0f : 1024.0f) + qmax_hi) << 16);
 
   // pass 2: codes of (channel 2p, channel 2p+1) for one token per step.  A plane's fields of both channels
   // gather in one register (channel 2p in the low half, 2p+1 in the high half, 16/BITS tokens each); two such
-  // registers split into one 32-bit word per channel.
+  // registers split into one 32-bit word per channel.  Split tq produces words [tq, tq+1) * WORDS / TQ.
   constexpr int BITS = KBITS == 0 ? 2 : KBITS;      // bits per stored plane
   constexpr int CODE_BITS = KBITS == 0 ? 4 : KBITS; // bits the quantizer produces
   constexpr int PER_HALF = 16 / BITS;               // tokens per 16-bit half of a plane word
   constexpr int WORDS = kP / (2 * PER_HALF);        // 32-bit words per channel and plane
+  constexpr int MY_WORDS = WORDS / TQ;              // words of this split
+  constexpr int CHUNK = MY_WORDS < 4 ? MY_WORDS : 4;   // words per store
+  static_assert(MY_WORDS >= 2 && MY_WORDS % CHUNK == 0, "page words do not split this way");
   constexpr uint32_t FIELD2 = ((1u << BITS) - 1u) * 0x00010001u;
   uint32_t* low_lo = reinterpret_cast<uint32_t*>(page + (2 * p) * (WORDS * 4));
   uint32_t* low_hi = low_lo + WORDS;
   uint32_t* high_lo = (KBITS == 0 && slot_lo >= 0) ? reinterpret_cast<uint32_t*>(page + d.key_off_high + slot_lo * (WORDS * 4)) : nullptr;
   uint32_t* high_hi = (KBITS == 0 && slot_hi >= 0) ? reinterpret_cast<uint32_t*>(page + d.key_off_high + slot_hi * (WORDS * 4)) : nullptr;
 #pragma unroll 1
-  for (int w4 = 0; w4 < WORDS; w4 += 4) {
-    uint32_t a_lo[4], a_hi[4], b_lo[4], b_hi[4];   // a: low plane, b: high plane
+  for (int w4 = tq * MY_WORDS; w4 < (tq + 1) * MY_WORDS; w4 += CHUNK) {
+    uint32_t a_lo[CHUNK], a_hi[CHUNK], b_lo[CHUNK], b_hi[CHUNK];   // a: low plane, b: high plane
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < CHUNK; ++q) {
       uint32_t acc_a[2], acc_b[2];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -329,11 +376,20 @@ __global__ void __launch_bounds__(64) fast_key_pages_kernel(dartkv_cache_desc d,
         b_hi[q] = __byte_perm(acc_b[0], acc_b[1], 0x7632);
       }
     }
-    reinterpret_cast<uint4*>(low_lo)[w4 / 4] = make_uint4(a_lo[0], a_lo[1], a_lo[2], a_lo[3]);
-    reinterpret_cast<uint4*>(low_hi)[w4 / 4] = make_uint4(a_hi[0], a_hi[1], a_hi[2], a_hi[3]);
-    if (KBITS == 0) {
-      if (high_lo) reinterpret_cast<uint4*>(high_lo)[w4 / 4] = make_uint4(b_lo[0], b_lo[1], b_lo[2], b_lo[3]);
-      if (high_hi) reinterpret_cast<uint4*>(high_hi)[w4 / 4] = make_uint4(b_hi[0], b_hi[1], b_hi[2], b_hi[3]);
+    if (CHUNK == 4) {
+      reinterpret_cast<uint4*>(low_lo)[w4 / 4] = make_uint4(a_lo[0], a_lo[1], a_lo[2], a_lo[3]);
+      reinterpret_cast<uint4*>(low_hi)[w4 / 4] = make_uint4(a_hi[0], a_hi[1], a_hi[2], a_hi[3]);
+      if (KBITS == 0) {
+        if (high_lo) reinterpret_cast<uint4*>(high_lo)[w4 / 4] = make_uint4(b_lo[0], b_lo[1], b_lo[2], b_lo[3]);
+        if (high_hi) reinterpret_cast<uint4*>(high_hi)[w4 / 4] = make_uint4(b_hi[0], b_hi[1], b_hi[2], b_hi[3]);
+      }
+    } else {
+      reinterpret_cast<uint2*>(low_lo)[w4 / 2] = make_uint2(a_lo[0], a_lo[CHUNK - 1]);
+      reinterpret_cast<uint2*>(low_hi)[w4 / 2] = make_uint2(a_hi[0], a_hi[CHUNK - 1]);
+      if (KBITS == 0) {
+        if (high_lo) reinterpret_cast<uint2*>(high_lo)[w4 / 2] = make_uint2(b_lo[0], b_lo[CHUNK - 1]);
+        if (high_hi) reinterpret_cast<uint2*>(high_hi)[w4 / 2] = make_uint2(b_hi[0], b_hi[CHUNK - 1]);
+      }
     }
   }
   if (bad && nonfinite) *nonfinite = 1;
@@ -438,20 +494,30 @@ int dartkv_append_fast_supported(const dartkv_cache_desc* d, const dartkv_append
   return ok;
 }
 
+#ifndef APPEND_KEY_SPLITS
+#define APPEND_KEY_SPLITS 4
+#endif
+
+template <int DT, int TQ>
+static int launch_keys_split(const dartkv_cache_desc& d, const dartkv_append_plan& p, const RowSource& src,
+                             const int32_t* indices, int32_t* nonfinite, cudaStream_t stream) {
+  dim3 grid(d.batch * d.kv_heads, p.num_pages);
+  if (d.key_mode == DARTKV_MIXED_PAGE)
+    fast_key_pages_kernel<DT, 0, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+  else if (d.key_bits == 2)
+    fast_key_pages_kernel<DT, 2, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+  else if (d.key_bits == 4)
+    fast_key_pages_kernel<DT, 4, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+  else
+    fast_key_pages_kernel<DT, 8, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+  DARTKV_LAUNCH_OK("fast_key_pages_kernel");
+  return DARTKV_OK;
+}
+
 template <int DT>
 static int launch_keys(const dartkv_cache_desc& d, const dartkv_append_plan& p, const RowSource& src,
                        const int32_t* indices, int32_t* nonfinite, cudaStream_t stream) {
-  dim3 grid(d.batch * d.kv_heads, p.num_pages);
-  if (d.key_mode == DARTKV_MIXED_PAGE)
-    fast_key_pages_kernel<DT, 0><<<grid, 64, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
-  else if (d.key_bits == 2)
-    fast_key_pages_kernel<DT, 2><<<grid, 64, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
-  else if (d.key_bits == 4)
-    fast_key_pages_kernel<DT, 4><<<grid, 64, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
-  else
-    fast_key_pages_kernel<DT, 8><<<grid, 64, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
-  DARTKV_LAUNCH_OK("fast_key_pages_kernel");
-  return DARTKV_OK;
+  return launch_keys_split<DT, APPEND_KEY_SPLITS>(d, p, src, indices, nonfinite, stream);
 }
 
 template <int DT>
