@@ -36,7 +36,7 @@ WORKLOADS = {
 }
 # DRAM bytes of ONE decode launch at config 3 measured with ncu (dram__bytes_read.sum / dram__bytes_write.sum of the
 # tensor-core decode kernel, per-op flavour) next to that launch's algorithmic bytes
-NCU_CONFIG3 = {"algorithmic": 192774144, "dram_read": 192.73e6, "dram_write": 5.10e6}
+NCU_CONFIG3 = {"algorithmic": 192774144, "dram_read": 192.73e6, "dram_write": 4.11e6}
 # the same numbers as dartkv_b200.synthetic.HEADLINE_GEOMETRY (kept here so that the CPU reference arm runs without
 # loading the package or its CUDA library; the GPU arm asserts that the two agree)
 GEOM = dict(query_heads=32, kv_heads=8, head_dim=128, page=128, key_group=128, value_group=64, sinks=32,
@@ -753,6 +753,7 @@ def qwen3_decode(args) -> None:
     with ClockSampler(0) as clocks:
         ms, launches, cache = run(True)
     hot_ms = sum(a.elapsed_time(b) for a, b in spans)
+    reference_gpu = reference_qwen3_decode(config, prompt, device, min(new_tokens, 16))
     line = {
         "metric": "qwen3_8b_arch_decode_tokens_per_s", "value": batch * new_tokens / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": 1, "steps": new_tokens, "warmup": 1, "ms_per_step": ms / new_tokens, "higher_is_better": True,
@@ -761,11 +762,59 @@ def qwen3_decode(args) -> None:
                    "batch": batch, "prompt": prompt_len, "new_tokens": new_tokens,
                    "cache": "2-bit + 0.25 promotion, page 128, groups 128/64, 32 sinks, local 1, value local 128, bf16 metadata"},
         "attention_share_of_step": hot_ms / ms, "hot_path_ms_per_step": hot_ms / new_tokens,
+        "reference_gpu": reference_gpu,
         "compression_ratio": cache.compression_ratio, "gpu_launches": int(launches), "clocks": clocks.summary(),
         "e2e": {"value": batch * new_tokens / (ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0, "note": "token ids stay on the device between steps"},
     }
     print(json.dumps(line), flush=True)
+
+
+def reference_qwen3_decode(config, prompt, device, new_tokens: int) -> dict:
+    """The same model and prompt through the reference's own DartHFCache and dart-engine hook (Triton kernels) on this
+    GPU, for a few tokens: the GPU baseline of the Qwen3 decode figure."""
+
+    dart_ref = reference_package()
+    if dart_ref is None:
+        return {"unavailable": "no install of the reference under oracle/_ref"}
+    try:
+        from transformers import Qwen3ForCausalLM
+
+        from oracle.ref_compat import patch_reference_integrations
+
+        patch_reference_integrations(dart_ref)
+        from dart.integrations import DartHFCache as RefCache
+        from dart.integrations import attach_dart_fused_attention as ref_attach
+
+        torch.manual_seed(3)
+        torch.set_default_dtype(torch.bfloat16)
+        with torch.device(device):
+            model = Qwen3ForCausalLM(config)
+        torch.set_default_dtype(torch.float32)
+        model = ref_attach(model.eval())
+        cfg = dart_ref.DartKVCacheConfig(bits=2, promote_ratio=0.25, page_size=128, key_group_size=128,
+                                         value_group_size=64, sink_tokens=32, hold_partial_pages=True, local_tokens=1,
+                                         value_local_tokens=128, metadata_dtype=torch.bfloat16)
+        cache = RefCache(cfg)
+        with torch.no_grad():
+            logits = model(prompt, past_key_values=cache, use_cache=True).logits[:, -1]
+            token = logits.argmax(-1, keepdim=True)
+            for _ in range(2):   # Triton compiles on the first decode steps
+                token = model(token, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(new_tokens):
+                token = model(token, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
+            t1.record()
+            torch.cuda.synchronize(device)
+        ms = t0.elapsed_time(t1)
+        del model, cache
+        torch.cuda.empty_cache()
+    except Exception as exc:
+        return {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+    return {"value": prompt.shape[0] * new_tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms / new_tokens,
+            "steps": new_tokens, "what": "the reference's DartHFCache + dart-engine hook (Triton page kernels) on this GPU, "
+                                         "same architecture, weights seed, prompt and cache configuration"}
 
 
 def main() -> None:
