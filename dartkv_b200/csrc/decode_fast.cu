@@ -38,7 +38,7 @@ namespace {
 #endif
 
 #ifndef PEROP_QK_UNROLL
-#define PEROP_QK_UNROLL 3
+#define PEROP_QK_UNROLL 8
 #endif
 #ifndef PEROP_PV_UNROLL
 #define PEROP_PV_UNROLL 8
@@ -64,7 +64,7 @@ struct BlockSmem {
 
 // One warp's share of a staged page: QK over its 64 tokens, online softmax, PV over the same tokens.
 // GN = value groups per token (1 or 2).
-template <int DT, int GN>
+template <int DT, int GN, int KP>
 __device__ __forceinline__ void page_half(const int HF, const int pair, const int lane, const dartkv_cache_desc& d, PairSmem& ps,
                                           const uint8_t* blob, uint16_t* prob, uint16_t* partner_prob, const uint8_t* q_thread, const CodeConsts<DT>& cc, int K, int prom_steps,
                                           float scale2, int g, int c, int jp, int hq, int gv, float (&o_acc)[4][4],
@@ -91,8 +91,9 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
     const uint2 o0 = ps.kpar_b[s0], o1 = ps.kpar_b[s1];
     const uint32_t w0 = *reinterpret_cast<const uint32_t*>(low_thread + o0.y);
     const uint32_t w1 = *reinterpret_cast<const uint32_t*>(low_thread + o1.y);
-    const uint32_t h0 = s0 < K ? high[s0 * 8 + g] : 0u;
-    const uint32_t h1 = s1 < K ? high[s1 * 8 + g] : 0u;
+    // with a promoted count that is a multiple of eight every position of a promoted step is a promoted slot
+    const uint32_t h0 = (KP >= 0 || s0 < K) ? high[s0 * 8 + g] : 0u;
+    const uint32_t h1 = (KP >= 0 || s1 < K) ? high[s1 * 8 + g] : 0u;
     uint32_t r0[8], r1[8];
     dequant_word4<DT>(cc, w0, h0, a0.x, a0.y, a0.z, a0.w, r0);
     dequant_word4<DT>(cc, w1, h1, a1.x, a1.y, a1.z, a1.w, r1);
@@ -238,7 +239,10 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
 #endif   // PEROP_SKIP_PV
 }
 
-template <int DT>
+// GN: value groups per token (1 or 2).  KP: promoted channels per page when that is a multiple of eight known to
+// the host (0, 8, 16, 24, 32), else -1 (read from the descriptor): with the count fixed the logits loops have
+// constant trip counts and no per-position "is this slot promoted" test.
+template <int DT, int GN, int KP>
 __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_desc d, FastArgs a) {
   using H = Half2Ops<DT>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -288,7 +292,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     mbar_fence_init();
   }
   __syncthreads();
-  const int K = d.key_mode == DARTKV_MIXED_PAGE ? d.promoted : 0;
+  const int K = KP >= 0 ? KP : (d.key_mode == DARTKV_MIXED_PAGE ? d.promoted : 0);
   const int prom_steps = (K + 7) >> 3;
   const int jp = g & 1, hq = g >> 1;
   const uint8_t* q_thread = reinterpret_cast<const uint8_t*>(&bs.q32[0][g]);   // + 32 * channel
@@ -385,11 +389,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
 #endif
       __syncwarp();
 
-      if (d.value_groups == 2) {
-        page_half<DT, 2>(hf, pair, lane, d, ps, blob, ps.prob[hf], ps.prob[hf ^ 1], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
-      } else {
-        page_half<DT, 1>(hf, pair, lane, d, ps, blob, ps.prob[hf], ps.prob[hf ^ 1], q_thread, cc, K, prom_steps, scale2, g, c, jp, hq, gv, o_acc, m_run, l_run);
-      }
+      page_half<DT, GN, KP>(hf, pair, lane, d, ps, blob, ps.prob[hf], ps.prob[hf ^ 1], q_thread, cc, K, prom_steps, scale2, g, c, jp,
+                            hq, gv, o_acc, m_run, l_run);
 
       pair_barrier(pair);
       // the stage is free again: prefetch the page two iterations ahead
@@ -434,6 +435,28 @@ int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int qu
   return 1;
 }
 
+// every (dtype, value groups, promoted count) variant of the kernel
+using FastKernel = void (*)(dartkv_cache_desc, FastArgs);
+template <int DT, int GN>
+static FastKernel fast_variant_kp(int kp) {
+  switch (kp) {
+    case 0: return decode_fast_kernel<DT, GN, 0>;
+    case 8: return decode_fast_kernel<DT, GN, 8>;
+    case 16: return decode_fast_kernel<DT, GN, 16>;
+    case 24: return decode_fast_kernel<DT, GN, 24>;
+    case 32: return decode_fast_kernel<DT, GN, 32>;
+    default: return decode_fast_kernel<DT, GN, -1>;
+  }
+}
+static FastKernel fast_variant(int dtype, int value_groups, int kp) {
+  if (dtype == DARTKV_BF16) return value_groups == 2 ? fast_variant_kp<DARTKV_BF16, 2>(kp) : fast_variant_kp<DARTKV_BF16, 1>(kp);
+  return value_groups == 2 ? fast_variant_kp<DARTKV_F16, 2>(kp) : fast_variant_kp<DARTKV_F16, 1>(kp);
+}
+static void launch_variant(int dtype, int value_groups, int kp, dim3 grid, cudaStream_t stream, const dartkv_cache_desc& d,
+                           const FastArgs& a) {
+  fast_variant(dtype, value_groups, kp)<<<grid, kThreads, kSmemBytes, stream>>>(d, a);
+}
+
 int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
                               int flavour, int quads, int stream_blocks, long long units, int total_splits,
                               float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream) {
@@ -447,16 +470,17 @@ int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int
     int device = 0;
     DARTKV_CUDA_OK(cudaGetDevice(&device));
     if (device < 0 || device >= 64 || !ready[device].load(std::memory_order_acquire)) {
-      DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fast_kernel<DARTKV_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-      DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fast_kernel<DARTKV_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+      for (int dt : {DARTKV_BF16, DARTKV_F16})
+        for (int gn : {1, 2})
+          for (int kp : {-1, 0, 8, 16, 24, 32})
+            DARTKV_CUDA_OK(cudaFuncSetAttribute(fast_variant(dt, gn, kp), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)kSmemBytes));
       if (device >= 0 && device < 64) ready[device].store(true, std::memory_order_release);
     }
   }
-  if (d->dtype == DARTKV_BF16) {
-    decode_fast_kernel<DARTKV_BF16><<<grid, kThreads, kSmemBytes, stream>>>(*d, a);
-  } else {
-    decode_fast_kernel<DARTKV_F16><<<grid, kThreads, kSmemBytes, stream>>>(*d, a);
-  }
+  const int promoted = d->key_mode == DARTKV_MIXED_PAGE ? d->promoted : 0;
+  const int kp = (promoted % 8 == 0 && promoted <= 32) ? promoted : -1;
+  launch_variant(d->dtype, d->value_groups, kp, grid, stream, *d, a);
   DARTKV_LAUNCH_OK("decode_fast_kernel");
   return DARTKV_OK;
 }

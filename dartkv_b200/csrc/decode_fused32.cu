@@ -278,7 +278,9 @@ __device__ __forceinline__ void fused_page_half(const int HF, const int tb, cons
   }
 }
 
-template <int DT>
+// GN: value groups per token (1 or 2).  KP: promoted channels per page when that is a multiple of eight known to
+// the host (0, 8, 16, 24, 32), else -1 (read from the descriptor).
+template <int DT, int GN, int KP>
 __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cache_desc d, FastArgs a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   FusedPairSmem* psm_all = reinterpret_cast<FusedPairSmem*>(smem_raw);
@@ -327,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
     mbar_fence_init();
   }
   __syncthreads();
-  const int K = d.key_mode == DARTKV_MIXED_PAGE ? d.promoted : 0;
+  const int K = KP >= 0 ? KP : (d.key_mode == DARTKV_MIXED_PAGE ? d.promoted : 0);
   const int prom_steps = (K + 7) >> 3;
   const float scale2 = a.scale * kLog2e;
   // weight operand: column n = g is (head g >> 1, j' = g & 1); the 32-bit word read holds the fp16 weights of the
@@ -451,11 +453,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
       pair_barrier(pair);
       if (issuer && pg != pg0 && pg + kPairs < p_end) issue(pg + kPairs, stage ^ 1);
 
-      if (d.value_groups == 2) {
-        fused_page_half<DT, 2>(hf, stage, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
-      } else {
-        fused_page_half<DT, 1>(hf, stage, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
-      }
+      fused_page_half<DT, GN>(hf, stage, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
 
     }
 
@@ -507,6 +505,24 @@ int dartkv_decode_fused32_supported(const dartkv_cache_desc* d, int q_dtype, int
   return 1;
 }
 
+// every (dtype, value groups, promoted count) variant of the kernel
+using FusedKernel = void (*)(dartkv_cache_desc, FastArgs);
+template <int DT, int GN>
+static FusedKernel fused_variant_kp(int kp) {
+  switch (kp) {
+    case 0: return decode_fused32_kernel<DT, GN, 0>;
+    case 8: return decode_fused32_kernel<DT, GN, 8>;
+    case 16: return decode_fused32_kernel<DT, GN, 16>;
+    case 24: return decode_fused32_kernel<DT, GN, 24>;
+    case 32: return decode_fused32_kernel<DT, GN, 32>;
+    default: return decode_fused32_kernel<DT, GN, -1>;
+  }
+}
+static FusedKernel fused_variant(int dtype, int value_groups, int kp) {
+  if (dtype == DARTKV_BF16) return value_groups == 2 ? fused_variant_kp<DARTKV_BF16, 2>(kp) : fused_variant_kp<DARTKV_BF16, 1>(kp);
+  return value_groups == 2 ? fused_variant_kp<DARTKV_F16, 2>(kp) : fused_variant_kp<DARTKV_F16, 1>(kp);
+}
+
 int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
                                  int flavour, int quads, int stream_blocks, long long units, int total_splits,
                                  float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream) {
@@ -520,16 +536,17 @@ int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, 
     int device = 0;
     DARTKV_CUDA_OK(cudaGetDevice(&device));
     if (device < 0 || device >= 64 || !ready[device].load(std::memory_order_acquire)) {
-      DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fused32_kernel<DARTKV_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmemBytes));
-      DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_fused32_kernel<DARTKV_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmemBytes));
+      for (int dt : {DARTKV_BF16, DARTKV_F16})
+        for (int gn : {1, 2})
+          for (int kp : {-1, 0, 8, 16, 24, 32})
+            DARTKV_CUDA_OK(cudaFuncSetAttribute(fused_variant(dt, gn, kp), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)kFusedSmemBytes));
       if (device >= 0 && device < 64) ready[device].store(true, std::memory_order_release);
     }
   }
-  if (d->dtype == DARTKV_BF16) {
-    decode_fused32_kernel<DARTKV_BF16><<<grid, kThreads, kFusedSmemBytes, stream>>>(*d, a);
-  } else {
-    decode_fused32_kernel<DARTKV_F16><<<grid, kThreads, kFusedSmemBytes, stream>>>(*d, a);
-  }
+  const int promoted = d->key_mode == DARTKV_MIXED_PAGE ? d->promoted : 0;
+  const int kp = (promoted % 8 == 0 && promoted <= 32) ? promoted : -1;
+  fused_variant(d->dtype, d->value_groups, kp)<<<grid, kThreads, kFusedSmemBytes, stream>>>(*d, a);
   DARTKV_LAUNCH_OK("decode_fused32_kernel");
   return DARTKV_OK;
 }
