@@ -18,11 +18,14 @@
 //
 // Per page a warp never materializes K or V: packed 2-bit codes are turned into exactly rounded
 // 16-bit operands with one logic op and two packed fma/add per pair (mma_utils.cuh) and fed straight
-// into m16n8k16 MMAs.  A register of the quantized operand pairs two elements that share a
-// (scale, zero) -- two tokens of one channel for K, two channels of one token for V -- which is the
-// MMA's non-contraction direction; the contraction index is therefore doubled (k = (channel, j) for
-// K, (token, j) for V) against a block-diagonal query / probability operand whose columns are
-// (query head, j).  Algorithmic HBM bytes per page and (batch, kv head): 10880.
+// into m16n8k16 MMAs.  Keys: a register of the operand pairs two tokens of one channel (they share the
+// channel's scale and zero point), which is the MMA's non-contraction direction, so the contraction index is
+// doubled, k = (channel, j), against a block-diagonal query operand whose columns are (query head, j).
+// Values: the code words of two tokens are byte-interleaved so that a register pairs two TOKENS of one
+// channel, the contraction direction itself; each half of the packed arithmetic carries its own token's scale
+// and zero point, the probability operand is plain (p[a], p[b]), and its eight columns hold the high and the
+// low 16-bit parts of the four heads' probabilities, so one MMA accumulates both.
+// Algorithmic HBM bytes per page and (batch, kv head): 10880.
 
 #include <atomic>
 
@@ -41,7 +44,7 @@ namespace {
 #define PEROP_QK_UNROLL 8
 #endif
 #ifndef PEROP_PV_UNROLL
-#define PEROP_PV_UNROLL 8
+#define PEROP_PV_UNROLL 4
 #endif
 constexpr int kQkUnroll = PEROP_QK_UNROLL, kPvUnroll = PEROP_PV_UNROLL;
 
@@ -67,7 +70,7 @@ struct BlockSmem {
 template <int DT, int GN, int KP>
 __device__ __forceinline__ void page_half(const int HF, const int pair, const int lane, const dartkv_cache_desc& d, PairSmem& ps,
                                           const uint8_t* blob, uint16_t* prob, uint16_t* partner_prob, const uint8_t* q_thread, const CodeConsts<DT>& cc, int K, int prom_steps,
-                                          float scale2, int g, int c, int jp, int hq, int gv, float (&o_acc)[4][4],
+                                          float scale2, int g, int c, int jp, int hq, int gv, float (&o_acc)[8][4],
                                           float& m_run, float& l_run) {
   using H = Half2Ops<DT>;
   const uint8_t* low_thread = blob + 4 * g;   // + 32 * channel = this thread's word of the channel row
@@ -177,12 +180,16 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
       plo[li] = H::from_float(p - H::to_float(hi));
     }
   l_run = l_run * alpha + psum;
-  // the running maximum rarely moves after the first pages: skip the rescale when no lane needs it
+  // the running maximum rarely moves after the first pages: skip the rescale when no lane needs it.  This thread's
+  // accumulator columns belong to heads 2(c&1) and 2(c&1)+1, whose factors live in the lanes c' = head of its quad.
   if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+    const float alpha_even = __shfl_sync(0xffffffffu, alpha, (lane & ~3) | (2 * (c & 1)));
+    const float alpha_odd = __shfl_sync(0xffffffffu, alpha, (lane & ~3) | (2 * (c & 1) + 1));
 #pragma unroll
-    for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o_acc[mt][i] *= alpha;
+    for (int mt = 0; mt < 8; ++mt) {
+      o_acc[mt][0] *= alpha_even; o_acc[mt][1] *= alpha_odd;
+      o_acc[mt][2] *= alpha_even; o_acc[mt][3] *= alpha_odd;
+    }
   }
   {
     uint4 hv, lv;
@@ -195,46 +202,48 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
   }
   __syncwarp();
 
-  // ---- O[channel pair][(head, j')] += V^T P over the doubled contraction (token, j), this warp's tokens:
-  // step ks covers the eight tokens 16*ks + 4*HF + {0..3} and + 8
-  const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(blob + kOffVCodes) + g;
+  // ---- O[channel][(part, head)] += V^T P over this warp's 64 tokens, 16 per step.  A register of the value
+  // operand pairs two TOKENS of one channel (the contraction direction): the code words of the two tokens are
+  // byte-interleaved first (low halves together: channels 0..7 of both tokens; high halves: channels 8..15), so that
+  // the packed dequantization sees token a in the low half and token b in the high half, each with its own scale
+  // and zero point.  The probability operand then is just (p[a], p[b]), and its eight columns carry the high and
+  // the low parts of the four heads side by side, so one MMA does both.  Local token L of this warp (the order of
+  // the probability table) is page token 16*(L>>3) + 4*HF + (L&3) + 8*((L>>2)&1); m-tile mt, row g is channel
+  // 16g + mt, row g+8 channel 16g + 8 + mt.
+  const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(blob + kOffVCodes) + g;   // word g of a token row: + 8 * token
   const uint8_t* vmeta = blob + kOffVMeta;
-  const uint16_t* prob_hi = &prob[(0 * 4 + hq) * kPStride];
-  const uint16_t* prob_lo = &prob[(1 * 4 + hq) * kPStride];
-  const uint32_t shift = 16 * jp;
-  // byte selectors that duplicate the scale / zero of this thread's value group into both halves
-  const uint32_t sel_s = GN == 2 ? (gv ? 0x3232u : 0x1010u) : 0x1010u;
-  const uint32_t sel_z = GN == 2 ? (gv ? 0x3232u : 0x1010u) : 0x3232u;
+  const uint32_t* pb = reinterpret_cast<const uint32_t*>(&prob[((g >> 2) * 4 + (g & 3)) * kPStride]) + c;   // column n = g
+  const int tok_a = 4 * HF + ((2 * c) & 3) + 8 * (c >> 1);   // page token of local token 2c
+  // byte selectors that bring the scale (zero point) of this thread's value group of tokens a and b together
+  const uint32_t sel_s = GN == 2 ? (gv ? 0x7632u : 0x5410u) : 0x5410u;
+  const uint32_t sel_z = GN == 2 ? (gv ? 0x7632u : 0x5410u) : 0x7632u;
+  auto token_pair = [&](int ta, uint32_t (&r_lo)[8], uint32_t (&r_hi)[8]) {
+    const uint32_t wa = vcodes[ta * 8], wb = vcodes[ta * 8 + 8];
+    uint32_t ss, zz;
+    if (GN == 2) {
+      const uint2 ma = *reinterpret_cast<const uint2*>(vmeta + ta * 8);        // {s0,s1} {z0,z1}
+      const uint2 mb = *reinterpret_cast<const uint2*>(vmeta + ta * 8 + 8);
+      ss = prmt(ma.x, mb.x, sel_s);
+      zz = prmt(ma.y, mb.y, sel_z);
+    } else {
+      const uint32_t ma = *reinterpret_cast<const uint32_t*>(vmeta + ta * 4);   // {s0, z0}
+      const uint32_t mb = *reinterpret_cast<const uint32_t*>(vmeta + ta * 4 + 4);
+      ss = prmt(ma, mb, sel_s);
+      zz = prmt(ma, mb, sel_z);
+    }
+    const uint32_t ms0 = H::mul(ss, H::neg_magic(0)), ms1 = H::mul(ss, H::neg_magic(1)), ms2 = H::mul(ss, H::neg_magic(2));
+    dequant_word2<DT>(cc, prmt(wa, wb, 0x5410u), ss, zz, ms0, ms1, ms2, r_lo);
+    dequant_word2<DT>(cc, prmt(wa, wb, 0x7632u), ss, zz, ms0, ms1, ms2, r_hi);
+  };
 #if !defined(PEROP_SKIP_PV)
 #pragma unroll kPvUnroll
-  for (int ks = 0; ks < 8; ++ks) {
-    const int t0 = 16 * ks + 4 * HF + c, t1 = t0 + 8;
-    const uint32_t w0 = vcodes[t0 * 8], w1 = vcodes[t1 * 8];
-    uint32_t ss0, zz0, ss1, zz1;
-    if (GN == 2) {
-      const uint2 m0 = *reinterpret_cast<const uint2*>(vmeta + t0 * 8);   // {s0,s1} {z0,z1}
-      const uint2 m1 = *reinterpret_cast<const uint2*>(vmeta + t1 * 8);
-      ss0 = prmt(m0.x, m0.x, sel_s); zz0 = prmt(m0.y, m0.y, sel_z);
-      ss1 = prmt(m1.x, m1.x, sel_s); zz1 = prmt(m1.y, m1.y, sel_z);
-    } else {
-      const uint32_t m0 = *reinterpret_cast<const uint32_t*>(vmeta + t0 * 4);   // {s0, z0}
-      const uint32_t m1 = *reinterpret_cast<const uint32_t*>(vmeta + t1 * 4);
-      ss0 = prmt(m0, m0, sel_s); zz0 = prmt(m0, m0, sel_z);
-      ss1 = prmt(m1, m1, sel_s); zz1 = prmt(m1, m1, sel_z);
-    }
-    uint32_t r0[8], r1[8];
-    dequant_word2<DT>(cc, w0, ss0, zz0, H::mul(ss0, H::neg_magic(0)), H::mul(ss0, H::neg_magic(1)), H::mul(ss0, H::neg_magic(2)), r0);
-    dequant_word2<DT>(cc, w1, ss1, zz1, H::mul(ss1, H::neg_magic(0)), H::mul(ss1, H::neg_magic(1)), H::mul(ss1, H::neg_magic(2)), r1);
-    const int l0 = 8 * ks + c, l1 = l0 + 4;
-    const uint32_t ph0 = (uint32_t)prob_hi[l0] << shift, ph1 = (uint32_t)prob_hi[l1] << shift;
-    const uint32_t pl0 = (uint32_t)prob_lo[l0] << shift, pl1 = (uint32_t)prob_lo[l1] << shift;
-    // all hi-part MMAs first, then the lo parts: back-to-back MMAs never share an accumulator
+  for (int s = 0; s < 4; ++s) {
+    uint32_t r0_lo[8], r0_hi[8], r1_lo[8], r1_hi[8];
+    token_pair(32 * s + tok_a, r0_lo, r0_hi);          // local tokens 16s + 2c, 16s + 2c + 1
+    token_pair(32 * s + tok_a + 16, r1_lo, r1_hi);     // local tokens 16s + 2c + 8, 16s + 2c + 9
+    const uint32_t b0 = pb[8 * s], b1 = pb[8 * s + 4];
 #pragma unroll
-    for (int mt = 0; mt < 4; ++mt) PEROP_MMA(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], ph0, ph1);
-#if !defined(PEROP_SKIP_PVLO)
-#pragma unroll
-    for (int mt = 0; mt < 4; ++mt) PEROP_MMA(o_acc[mt], r0[2 * mt], r0[2 * mt + 1], r1[2 * mt], r1[2 * mt + 1], pl0, pl1);
-#endif
+    for (int mt = 0; mt < 8; ++mt) PEROP_MMA(o_acc[mt], r0_lo[mt], r0_hi[mt], r1_lo[mt], r1_hi[mt], b0, b1);
   }
 #endif   // PEROP_SKIP_PV
 }
@@ -330,9 +339,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     }
     __syncthreads();
 
-    float o_acc[4][4];   // [m-tile][c-reg]: head c, channel 16g + 2mt + r + 8j'
+    float o_acc[8][4];   // [m-tile][c-reg]: channel 16g + mt + 8(i>>1), head 2(c&1) + (i&1), high (c<2) or low part of P
 #pragma unroll
-    for (int mt = 0; mt < 4; ++mt)
+    for (int mt = 0; mt < 8; ++mt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) o_acc[mt][i] = 0.0f;
     float m_run = -INFINITY, l_run = 0.0f;   // head c, log2 domain
@@ -404,11 +413,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     __syncthreads();   // every warp is done with its stages: the staging memory becomes the merge buffer
     if (g == 0) { bs.merge_m[warp][c] = m_run; bs.merge_l[warp][c] = l_run; }
 #pragma unroll
-    for (int mt = 0; mt < 4; ++mt)
+    for (int mt = 0; mt < 8; ++mt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int ch = 16 * g + 2 * mt + (i >> 1) + 8 * (i & 1);
-        warp_out[(warp * 4 + c) * 128 + ch] = o_acc[mt][i];
+        // lanes c and c ^ 2 hold what the high and the low parts of the probabilities contributed
+        const float v = o_acc[mt][i] + __shfl_xor_sync(0xffffffffu, o_acc[mt][i], 2);
+        if (c < 2) warp_out[(warp * 4 + 2 * c + (i & 1)) * 128 + 16 * g + mt + 8 * (i >> 1)] = v;
       }
     __syncthreads();
     block_merge(a, bs, warp_out, bh / d.kv_heads, bh % d.kv_heads, rep,
