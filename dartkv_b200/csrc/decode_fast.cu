@@ -174,7 +174,7 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
     for (int i = 0; i < 4; ++i) {
       const float p = fast_exp2(s_sum[mt][i] - m_new);
       psum += p;
-      const int li = 2 * mt + (i >> 1) + 4 * (i & 1);   // local token index inside this thread's 8: pair + 4 j'
+      const int li = 4 * mt + i;   // table order inside this thread's 8 tokens: token offset (li >> 1) + 8 * (li & 1)
       const uint16_t hi = H::from_float(p);
       phi[li] = hi;
       plo[li] = H::from_float(p - H::to_float(hi));
@@ -213,21 +213,21 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
   const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(blob + kOffVCodes) + g;   // word g of a token row: + 8 * token
   const uint8_t* vmeta = blob + kOffVMeta;
   const uint32_t* pb = reinterpret_cast<const uint32_t*>(&prob[((g >> 2) * 4 + (g & 3)) * kPStride]) + c;   // column n = g
-  const int tok_a = 4 * HF + ((2 * c) & 3) + 8 * (c >> 1);   // page token of local token 2c
+  const int tok_a = 4 * HF + c;   // page token of local token 2c; local token 2c + 1 is page token tok_a + 8
   // byte selectors that bring the scale (zero point) of this thread's value group of tokens a and b together
   const uint32_t sel_s = GN == 2 ? (gv ? 0x7632u : 0x5410u) : 0x5410u;
   const uint32_t sel_z = GN == 2 ? (gv ? 0x7632u : 0x5410u) : 0x7632u;
   auto token_pair = [&](int ta, uint32_t (&r_lo)[8], uint32_t (&r_hi)[8]) {
-    const uint32_t wa = vcodes[ta * 8], wb = vcodes[ta * 8 + 8];
+    const uint32_t wa = vcodes[ta * 8], wb = vcodes[ta * 8 + 64];
     uint32_t ss, zz;
     if (GN == 2) {
       const uint2 ma = *reinterpret_cast<const uint2*>(vmeta + ta * 8);        // {s0,s1} {z0,z1}
-      const uint2 mb = *reinterpret_cast<const uint2*>(vmeta + ta * 8 + 8);
+      const uint2 mb = *reinterpret_cast<const uint2*>(vmeta + ta * 8 + 64);
       ss = prmt(ma.x, mb.x, sel_s);
       zz = prmt(ma.y, mb.y, sel_z);
     } else {
       const uint32_t ma = *reinterpret_cast<const uint32_t*>(vmeta + ta * 4);   // {s0, z0}
-      const uint32_t mb = *reinterpret_cast<const uint32_t*>(vmeta + ta * 4 + 4);
+      const uint32_t mb = *reinterpret_cast<const uint32_t*>(vmeta + ta * 4 + 32);
       ss = prmt(ma, mb, sel_s);
       zz = prmt(ma, mb, sel_z);
     }
@@ -239,8 +239,8 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
 #pragma unroll kPvUnroll
   for (int s = 0; s < 4; ++s) {
     uint32_t r0_lo[8], r0_hi[8], r1_lo[8], r1_hi[8];
-    token_pair(32 * s + tok_a, r0_lo, r0_hi);          // local tokens 16s + 2c, 16s + 2c + 1
-    token_pair(32 * s + tok_a + 16, r1_lo, r1_hi);     // local tokens 16s + 2c + 8, 16s + 2c + 9
+    token_pair(32 * s + tok_a, r0_lo, r0_hi);          // local tokens 16s + 2c, 16s + 2c + 1: page tokens a, a + 8
+    token_pair(32 * s + tok_a + 16, r1_lo, r1_hi);     // local tokens 16s + 2c + 8, 16s + 2c + 9: a + 16, a + 24
     const uint32_t b0 = pb[8 * s], b1 = pb[8 * s + 4];
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) PEROP_MMA(o_acc[mt], r0_lo[mt], r0_hi[mt], r1_lo[mt], r1_hi[mt], b0, b1);
