@@ -32,6 +32,7 @@ EXPORTS = (
     "dartkv_decode_attention", "dartkv_decode_plan", "dartkv_decode_status", "dartkv_builtin_scratch_bytes",
     "dartkv_decode_attention_builtin_scratch", "dartkv_shard_range", "dartkv_decode_split_override",
     "dartkv_lifecycle_plan", "dartkv_cache_append_step", "dartkv_decode_attention_scatter",
+    "dartkv_decode_attention_padded",
 )
 
 
@@ -135,6 +136,7 @@ def _load() -> ctypes.CDLL:
     lib.dartkv_decode_workspace_bytes.argtypes = [POINTER(CacheDesc), i32, i32]
     lib.dartkv_decode_workspace_bytes.restype = c_int64
     lib.dartkv_decode_attention.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, i64, p, p]
+    lib.dartkv_decode_attention_padded.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, p, i64, p, p]
     lib.dartkv_decode_attention_scatter.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, i64, p,
                                                     POINTER(PeerScatter), p]
     lib.dartkv_decode_status.argtypes = [p, POINTER(c_int), p]

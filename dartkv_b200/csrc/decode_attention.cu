@@ -46,6 +46,7 @@ struct GenericArgs {
   float* part_m;
   float* part_l;
   float* part_acc;
+  const int32_t* row_start;   // optional [batch] first live token of every batch row
 };
 
 __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cache_desc d, GenericArgs a) {
@@ -68,8 +69,10 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cach
   // tok_begin < 0: start where the tensor-core kernel stops (last full page packed on both sides)
   int begin = a.tok_begin;
   if (begin < 0) begin = dartkv_fast_range_end(d.sink_tokens, d.page_size, k_end, v_end, sink_filled);
-  const int lo = begin + split * a.chunk;
-  const int hi = (int)min((int64_t)lo + a.chunk, (int64_t)end);
+  const int first = begin + split * a.chunk;
+  const int hi = (int)min((int64_t)first + a.chunk, (int64_t)end);
+  // left padding: the tokens before the row's first live one get no weight (a split wholly before it stays empty)
+  const int lo = a.row_start ? max(first, a.row_start[b]) : first;
 
   for (int i = tid; i < rep * D; i += GEN_THREADS) {
     int r = i / D, c = i % D;
@@ -323,11 +326,13 @@ struct DecodeLayout {
 int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
 int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
                               int flavour, int quads, int stream_blocks, long long units, int total_splits,
-                              float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream);
+                              float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
+                              cudaStream_t stream);
 int dartkv_decode_fused32_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
 int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
                                  int flavour, int quads, int stream_blocks, long long units, int total_splits,
-                                 float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream);
+                                 float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
+                              cudaStream_t stream);
 
 static int dartkv_sm_count() {
   // per device: a process may drive GPUs of different sizes
@@ -486,7 +491,8 @@ extern "C" int dartkv_decode_status(const void* workspace, int* status_out, void
 
 static int decode_attention_impl(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads,
                                  float scale, int flavour, int tokens, void* workspace, int64_t workspace_bytes,
-                                 void* out, const dartkv_peer_scatter* peers, void* stream_) {
+                                 void* out, const dartkv_peer_scatter* peers, const int32_t* row_start,
+                                 void* stream_) {
   DARTKV_REQUIRE(d != nullptr, "null descriptor");
   DARTKV_REQUIRE(query && out && workspace, "decode_attention received a null pointer");
   DARTKV_REQUIRE(dartkv_valid_dtype(q_dtype), "query must be f32, f16 or bf16");
@@ -510,7 +516,7 @@ static int decode_attention_impl(const dartkv_cache_desc* d, const void* query, 
   if (L.fast) {
     int rc = (L.fast == 2 ? dartkv_decode_fused32_launch : dartkv_decode_fast_launch)(
         d, query, q_dtype, query_heads, scale, flavour, L.quads, L.stream_blocks, L.units, L.total_splits, part_m,
-        part_l, part_acc, status, stream);
+        part_l, part_acc, status, row_start, stream);
     if (rc) return rc;
   } else {
     size_t smem = ((size_t)rep * D + (size_t)GEN_TILE * (D + 1) + (size_t)rep * GEN_TILE + 3 * rep) * sizeof(float) +
@@ -519,6 +525,7 @@ static int decode_attention_impl(const dartkv_cache_desc* d, const void* query, 
     a.q = query; a.q_dt = q_dtype; a.query_heads = query_heads; a.flavour = flavour; a.scale = scale;
     a.total_splits = L.total_splits; a.part_m = part_m; a.part_l = part_l; a.part_acc = part_acc;
     a.tok_begin = 0; a.tok_end = -1; a.chunk = L.generic_chunk; a.split_base = 0;
+    a.row_start = row_start;
     if (smem > 48 * 1024)
       DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     DARTKV_REQUIRE(L.generic_splits <= 65535, "too many splits");
@@ -550,7 +557,15 @@ extern "C" int dartkv_decode_attention(const dartkv_cache_desc* d, const void* q
                                        float scale, int flavour, int tokens, void* workspace,
                                        int64_t workspace_bytes, void* out, void* stream) {
   return decode_attention_impl(d, query, q_dtype, query_heads, scale, flavour, tokens, workspace, workspace_bytes, out,
-                               nullptr, stream);
+                               nullptr, nullptr, stream);
+}
+
+extern "C" int dartkv_decode_attention_padded(const dartkv_cache_desc* d, const void* query, int q_dtype,
+                                              int query_heads, float scale, int flavour, int tokens,
+                                              const int32_t* row_start, void* workspace, int64_t workspace_bytes,
+                                              void* out, void* stream) {
+  return decode_attention_impl(d, query, q_dtype, query_heads, scale, flavour, tokens, workspace, workspace_bytes, out,
+                               nullptr, row_start, stream);
 }
 
 extern "C" int dartkv_decode_attention_scatter(const dartkv_cache_desc* d, const void* query, int q_dtype,
@@ -567,7 +582,7 @@ extern "C" int dartkv_decode_attention_scatter(const dartkv_cache_desc* d, const
   for (int p = 0; p < peers->world_size; ++p)
     DARTKV_REQUIRE(peers->out[p] != nullptr && peers->flags[p] != nullptr, "peer %d has a null pointer", p);
   return decode_attention_impl(d, query, q_dtype, query_heads, scale, flavour, tokens, workspace, workspace_bytes, out,
-                               peers, stream);
+                               peers, nullptr, stream);
 }
 
 // ---------------------------------------------------------------------------- built-in scratch variant

@@ -70,7 +70,8 @@ struct BlockSmem {
 template <int DT, int GN, int KP>
 __device__ __forceinline__ void page_half(const int HF, const int pair, const int lane, const dartkv_cache_desc& d, PairSmem& ps,
                                           const uint8_t* blob, uint16_t* prob, uint16_t* partner_prob, const uint8_t* q_thread, const CodeConsts<DT>& cc, int K, int prom_steps,
-                                          float scale2, int g, int c, int jp, int hq, int gv, float (&o_acc)[8][4],
+                                          float scale2, int g, int c, int jp, int hq, int gv, int mask_below,
+                                          float (&o_acc)[8][4],
                                           float& m_run, float& l_run) {
   using H = Half2Ops<DT>;
   const uint8_t* low_thread = blob + 4 * g;   // + 32 * channel = this thread's word of the channel row
@@ -153,6 +154,13 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
     }
     __syncwarp();   // every lane has read its message before any lane writes probabilities over it
   }
+  if (mask_below > 0) {   // the page that holds the row's first live token: the tokens before it drop out
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (16 * g + 4 * HF + 2 * mt + (i >> 1) + 8 * (i & 1) < mask_below) s_sum[mt][i] = -INFINITY;
+  }
 
   // ---- online softmax for head c over this warp's 64 tokens (this thread: 8 of them)
   float mx = -INFINITY;
@@ -164,7 +172,8 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
   const float m_new = fmaxf(m_run, mx);
-  const float alpha = fast_exp2(m_run - m_new);
+  const float m_ref = m_new == -INFINITY ? 0.0f : m_new;   // nothing live yet: every weight below comes out zero
+  const float alpha = fast_exp2(m_run - m_ref);
   m_run = m_new;
   float psum = 0.0f;
   uint16_t phi[8], plo[8];
@@ -172,7 +181,7 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float p = fast_exp2(s_sum[mt][i] - m_new);
+      const float p = fast_exp2(s_sum[mt][i] - m_ref);
       psum += p;
       const int li = 4 * mt + i;   // table order inside this thread's 8 tokens: token offset (li >> 1) + 8 * (li & 1)
       const uint16_t hi = H::from_float(p);
@@ -208,7 +217,7 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
   // the packed dequantization sees token a in the low half and token b in the high half, each with its own scale
   // and zero point.  The probability operand then is just (p[a], p[b]), and its eight columns carry the high and
   // the low parts of the four heads side by side, so one MMA does both.  Local token L of this warp (the order of
-  // the probability table) is page token 16*(L>>3) + 4*HF + (L&3) + 8*((L>>2)&1); m-tile mt, row g is channel
+  // the probability table) is page token 16*(L>>3) + 4*HF + ((L&7)>>1) + 8*(L&1); m-tile mt, row g is channel
   // 16g + mt, row g+8 channel 16g + 8 + mt.
   const uint32_t* vcodes = reinterpret_cast<const uint32_t*>(blob + kOffVCodes) + g;   // word g of a token row: + 8 * token
   const uint8_t* vmeta = blob + kOffVMeta;
@@ -317,7 +326,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     const int quad_begin = unit - bh * a.quads;
     const int quad_count = min(a.quads - quad_begin, unit_end - unit);
     unit += quad_count;
-    const int p_begin = 4 * quad_begin;
+    // tokens before the row's first live one get no weight: whole pages of them are not even fetched
+    const int row_first = a.row_start ? max(a.row_start[bh / d.kv_heads], 0) : 0;
+    const int p_begin = max(4 * quad_begin, row_first > d.sink_tokens ? (row_first - d.sink_tokens) >> 7 : 0);
     const int p_end = min(4 * (quad_begin + quad_count), total_pages);
 
     // the first two pages of this pair are requested before anything else, so their latency overlaps the
@@ -399,7 +410,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
       __syncwarp();
 
       page_half<DT, GN, KP>(hf, pair, lane, d, ps, blob, ps.prob[hf], ps.prob[hf ^ 1], q_thread, cc, K, prom_steps, scale2, g, c, jp,
-                            hq, gv, o_acc, m_run, l_run);
+                            hq, gv, row_first - (d.sink_tokens + 128 * pg), o_acc, m_run, l_run);
 
       pair_barrier(pair);
       // the stage is free again: prefetch the page two iterations ahead
@@ -469,9 +480,11 @@ static void launch_variant(int dtype, int value_groups, int kp, dim3 grid, cudaS
 
 int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
                               int flavour, int quads, int stream_blocks, long long units, int total_splits,
-                              float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream) {
+                              float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
+                              cudaStream_t stream) {
   (void)q_dtype;
-  FastArgs a{query, query_heads, scale, flavour, quads, stream_blocks, units, total_splits, part_m, part_l, part_acc, status};
+  FastArgs a{query, query_heads, scale, flavour, quads, stream_blocks, units, total_splits, part_m, part_l, part_acc, status,
+             row_start};
   dim3 grid(stream_blocks + d->batch * d->kv_heads);
   {
     // the shared-memory opt-in is per device and per kernel: ask once per device (the flags are atomic; two threads

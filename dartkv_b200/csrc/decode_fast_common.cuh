@@ -39,6 +39,8 @@ struct FastArgs {
   float* part_l;
   float* part_acc;
   int* status;
+  // optional [batch] first live token of every batch row (left padding): tokens before it get no weight
+  const int32_t* row_start;
 };
 
 __host__ __device__ __forceinline__ int fast_range_end(int sink_tokens, int page_size, int k_end, int v_end,
@@ -94,7 +96,7 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
   int tile_counter = 0;
   float* ptab = warp_out + 4096 + warp * 64;   // this warp's [16 tokens][4 heads] probabilities, beyond the merge buffer
   // segments: [0, sink_filled) then [fast_end, seen) cut at key page boundaries
-  int t = 0;
+  int t = a.row_start ? min(max(a.row_start[b], 0), seen) : 0;
 #ifdef DENSE_SKIP
   t = seen;
 #endif

@@ -109,7 +109,7 @@ struct WarpState {
 template <int DT, int GN>
 __device__ __forceinline__ void fused_page_half(const int HF, const int tb, const dartkv_cache_desc& d, FusedPairSmem& ps, const uint8_t* blob,
                                                 uint32_t* utab, int prom_steps, float scale2, float f_inv, int g, int c,
-                                                uint32_t sel_w, uint32_t mask_u, WarpState& st) {
+                                                uint32_t sel_w, uint32_t mask_u, int mask_below, WarpState& st) {
   // ---- logits: S[token pair][(head, j')] over the doubled contraction (channel, j).  Row g of m-tile mt
   // reads code position 2mt, row g+8 position 2mt+1.
   // Even and odd contraction steps use separate accumulators so consecutive MMAs are independent.
@@ -171,13 +171,16 @@ __device__ __forceinline__ void fused_page_half(const int HF, const int tb, cons
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       s_sum[mt][i] = fmaf(s_acc[mt][i] + s_odd[mt][i], cm[2 * mt + (i >> 1)], bias);
+      // the page that holds the row's first live token: the tokens before it drop out
+      if (mask_below > 0 && 16 * g + 4 * HF + 2 * mt + (i >> 1) + 8 * (i & 1) < mask_below) s_sum[mt][i] = -INFINITY;
       mx = fmaxf(mx, s_sum[mt][i]);
     }
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
   const float m_new = fmaxf(st.m_run, mx);
-  const float alpha = fast_exp2(st.m_run - m_new);
+  const float m_ref = m_new == -INFINITY ? 0.0f : m_new;   // nothing live yet: every weight below comes out zero
+  const float alpha = fast_exp2(st.m_run - m_ref);
   st.m_run = m_new;
 
   // value metadata of this thread's 8 tokens: token = 16g + 4HF + p + 8j', p = 2mt + (i >> 1), j' = i & 1
@@ -218,7 +221,7 @@ __device__ __forceinline__ void fused_page_half(const int HF, const int tb, cons
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int k = 4 * mt + i;
-      const float p = fast_exp2(s_sum[mt][i] - m_new);
+      const float p = fast_exp2(s_sum[mt][i] - m_ref);
       psum += p;
       const float pf = p * fv;
       const int li = 2 * mt + (i >> 1) + 4 * (i & 1);   // local token inside this thread's 8: position + 4 j'
@@ -346,7 +349,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
     const int quad_begin = unit - bh * a.quads;
     const int quad_count = min(a.quads - quad_begin, unit_end - unit);
     unit += quad_count;
-    const int p_begin = 4 * quad_begin;
+    // tokens before the row's first live one get no weight: whole pages of them are not even fetched
+    const int row_first = a.row_start ? max(a.row_start[bh / d.kv_heads], 0) : 0;
+    const int p_begin = max(4 * quad_begin, row_first > d.sink_tokens ? (row_first - d.sink_tokens) >> 7 : 0);
     const int p_end = min(4 * (quad_begin + quad_count), total_pages);
 
     // the first two pages of this pair are requested before anything else, so their latency overlaps the
@@ -453,7 +458,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
       pair_barrier(pair);
       if (issuer && pg != pg0 && pg + kPairs < p_end) issue(pg + kPairs, stage ^ 1);
 
-      fused_page_half<DT, GN>(hf, stage, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u, st);
+      fused_page_half<DT, GN>(hf, stage, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u,
+                              row_first - (d.sink_tokens + 128 * pg), st);
 
     }
 
@@ -525,9 +531,11 @@ static FusedKernel fused_variant(int dtype, int value_groups, int kp) {
 
 int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
                                  int flavour, int quads, int stream_blocks, long long units, int total_splits,
-                                 float* part_m, float* part_l, float* part_acc, int* status, cudaStream_t stream) {
+                                 float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
+                                 cudaStream_t stream) {
   (void)q_dtype;
-  FastArgs a{query, query_heads, scale, flavour, quads, stream_blocks, units, total_splits, part_m, part_l, part_acc, status};
+  FastArgs a{query, query_heads, scale, flavour, quads, stream_blocks, units, total_splits, part_m, part_l, part_acc, status,
+             row_start};
   dim3 grid(stream_blocks + d->batch * d->kv_heads);
   {
     // the shared-memory opt-in is per device and per kernel: ask once per device (the flags are atomic; two threads

@@ -21,8 +21,11 @@ from .page_table import DartPageRun, DartPageTable
 
 def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional[float] = None,
                      flavour: int = _lib.DEQUANT_PER_OP, out: Optional[torch.Tensor] = None,
-                     peer_gather=None) -> torch.Tensor:
+                     peer_gather=None, row_start: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One query token per (batch, query head): ``query`` and the result are ``[B, Hq, D]``.
+
+    ``row_start`` (``[B]`` integers, first live token of every batch row) serves left-padded batches: the tokens
+    before a row's first live one get no weight and the pages that hold only such tokens are not read.
 
     With ``peer_gather`` (a ``dartkv_b200.sharding.PeerGather``) the kernels also deliver this rank's rows to every
     rank of the node and the gathered tensor ``[B_total, Hq_total, D]`` of the step is returned instead.
@@ -42,6 +45,12 @@ def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional
         raise ValueError("query and cache must be on the same device")
     q = query.contiguous()
     rep = q.shape[1] // kv_heads
+    if row_start is not None:
+        if peer_gather is not None:
+            raise ValueError("row_start and peer_gather cannot be combined")
+        if row_start.shape != (batch,):
+            raise ValueError("row_start must have shape [batch]")
+        row_start = row_start.to(device=q.device, dtype=torch.int32).contiguous()
     if rep > 4 and peer_gather is None and _grouped_heads_pay_off(cache, q.dtype, kv_heads, flavour, seen):
         # The tensor-core kernels take up to four query heads per KV head.  Wider groups (5..16 heads per KV head)
         # are served four heads at a time: every pass streams the packed pages again, which is still far cheaper
@@ -51,7 +60,8 @@ def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional
         result_view = result.view(batch, kv_heads, rep, head_dim)
         for first in range(0, rep, 4):
             part = grouped[:, :, first:first + 4].reshape(batch, -1, head_dim)
-            result_view[:, :, first:first + 4] = decode_attention(part, cache, scale=scale, flavour=flavour).view(
+            result_view[:, :, first:first + 4] = decode_attention(part, cache, scale=scale, flavour=flavour,
+                                                                   row_start=row_start).view(
                 batch, kv_heads, -1, head_dim)
         return result
     if out is None:
@@ -65,6 +75,12 @@ def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional
                 ctypes.byref(cache.descriptor), ptr(q), _lib.DTYPE_CODE[q.dtype], q.shape[1], float(factor), flavour,
                 seen, ptr(workspace), workspace.numel(), ptr(out), ctypes.byref(peers), stream_ptr(device)))
         return gathered
+    if row_start is not None:
+        with device_guard(device):
+            check(LIB.dartkv_decode_attention_padded(
+                ctypes.byref(cache.descriptor), ptr(q), _lib.DTYPE_CODE[q.dtype], q.shape[1], float(factor), flavour,
+                seen, ptr(row_start), ptr(workspace), workspace.numel(), ptr(out), stream_ptr(device)))
+        return out
     with device_guard(device):
         check(LIB.dartkv_decode_attention(
             ctypes.byref(cache.descriptor), ptr(q), _lib.DTYPE_CODE[q.dtype], q.shape[1], float(factor), flavour,
@@ -90,6 +106,7 @@ def fused_dart_attention(
     page_table: Optional[DartPageTable] = None,
     page_runs: Optional[Sequence[DartPageRun]] = None,
     flavour: int = _lib.DEQUANT_PER_OP,
+    row_start: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Single-token page attention, ``query [B, Hq, 1, D] -> [B, Hq, 1, D]``.
 
@@ -102,6 +119,10 @@ def fused_dart_attention(
     per-token path, as in the reference); there is no CPU fallback.  ``page_table`` and
     ``page_runs`` are validated against the cache like the reference does and otherwise
     unused: the kernel reads the device-resident metadata.
+
+    ``row_start`` (``[B]`` integers, not in the reference) masks the tokens before every row's first live one:
+    left-padded batches of unequal prompts decode through the packed path instead of falling back to dense.
+    It applies to the single-token call only.
     """
 
     if query.ndim != 4:
@@ -136,7 +157,7 @@ def fused_dart_attention(
             if run.first_page_index < 0 or run.first_page_index + run.page_count > total:
                 raise ValueError("page_run is outside the current cache page range")
             starts.add(run.first_page_index)
-    return decode_attention(query[:, :, 0], cache, scale=scale, flavour=flavour).unsqueeze(2)
+    return decode_attention(query[:, :, 0], cache, scale=scale, flavour=flavour, row_start=row_start).unsqueeze(2)
 
 
 __all__ = ["fused_dart_attention", "decode_attention"]

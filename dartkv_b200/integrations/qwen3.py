@@ -23,6 +23,46 @@ def _qwen3_modules():
     return modules
 
 
+def decode_row_start(cache, attention_mask: Optional[torch.Tensor], kv_len: int):
+    """What a decode step's attention mask means for the packed path.
+
+    ``None``: nothing is masked.  An int32 ``[B]`` tensor: a left-padded batch, the first live token of every row
+    (what ``fused_dart_attention(row_start=...)`` takes).  ``False``: any other mask, which only the dense path
+    can honour.  The reference's adapter ignores the mask (``src/dart/integrations/qwen3.py:78-87``) and is
+    therefore limited to uniform-length batches.  Telling the cases apart costs one host read per decode step:
+    every layer of the step receives the same mask tensor, so the answer is kept on the cache object.
+    """
+
+    if attention_mask is None:
+        return None
+    key = (attention_mask.data_ptr(), tuple(attention_mask.shape), attention_mask._version)
+    memo = getattr(cache, "_decode_mask_memo", None)
+    if memo is not None and memo[0] == key:
+        return memo[1]
+    mask = attention_mask
+    result = False
+    if mask.ndim == 4:
+        mask = mask[:, 0, -1, :]
+    if mask.ndim == 2 and mask.shape[-1] >= kv_len:
+        mask = mask[:, :kv_len]
+        if mask.dtype == torch.bool:
+            live = mask
+        elif mask.dtype.is_floating_point:
+            live = mask > torch.finfo(mask.dtype).min / 2      # additive mask: 0 where live
+        else:
+            live = mask != 0
+        count = live.sum(-1)
+        first = live.int().argmax(-1)
+        unmasked, left_padded = torch.stack(
+            [(count == kv_len).all(), ((first + count == kv_len) & (count > 0)).all()]).tolist()
+        if unmasked:
+            result = None
+        elif left_padded:
+            result = first.to(torch.int32)
+    cache._decode_mask_memo = (key, result)
+    return result
+
+
 def build_dart_qwen3_attention_class():
     """Build the Qwen3 attention subclass against the installed Transformers."""
 
@@ -51,11 +91,19 @@ def build_dart_qwen3_attention_class():
                     key_states, value_states = cache.update(key_states, value_states, self.layer_idx)
 
             output_attentions = bool(kwargs.get("output_attentions", False))
-            if (use_dart_decode and not cache.last_update_was_prefill(self.layer_idx)
-                    and query_states.shape[-2] == 1 and not output_attentions):
-                # uniform-length batches only: like the reference, the fused path ignores attention_mask
+            fused_decode = (use_dart_decode and not cache.last_update_was_prefill(self.layer_idx)
+                            and query_states.shape[-2] == 1 and not output_attentions)
+            row_start = None
+            if fused_decode:
+                layer = cache.layer_for_attention(self.layer_idx)
+                row_start = decode_row_start(cache, attention_mask, layer.get_seq_length())
+                if row_start is False:
+                    # a mask the packed path cannot express: dense attention over the materialized layer
+                    fused_decode = False
+                    key_states, value_states = layer.get()
+            if fused_decode:
                 attn_output = fused_dart_attention(
-                    query_states, cache.layer_for_attention(self.layer_idx), scale=self.scaling, fallback=True,
+                    query_states, layer, scale=self.scaling, fallback=True, row_start=row_start,
                 ).transpose(1, 2).contiguous()
                 attn_weights = None
             else:
@@ -86,4 +134,4 @@ def attach_dart_fused_attention(model: nn.Module) -> nn.Module:
     return model
 
 
-__all__ = ["attach_dart_fused_attention", "build_dart_qwen3_attention_class"]
+__all__ = ["attach_dart_fused_attention", "build_dart_qwen3_attention_class", "decode_row_start"]

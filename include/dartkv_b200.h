@@ -225,6 +225,15 @@ int dartkv_decode_split_override(const char* spec);
 /* Copies the workspace status word to the host (synchronizes the stream): 0 = no bounded wait expired. */
 int dartkv_decode_status(const void* workspace, int* status_out, void* stream);
 
+/* Decode attention over a left-padded batch.  The reference's fused call takes no mask (its Qwen3 adapter serves
+ * uniform-length batches only, src/dart/integrations/qwen3.py:78-87); here `row_start` ([batch] int32 on the
+ * device, or NULL for none) gives the first live token of every batch row and the tokens before it get no weight,
+ * exactly as if the eager path had masked them with -inf.  Pages that lie wholly before a row's first live token
+ * are not read.  Every row needs at least one live token (row_start[b] < tokens). */
+int dartkv_decode_attention_padded(const dartkv_cache_desc* desc, const void* query, int q_dtype, int query_heads,
+                                   float scale, int flavour, int tokens, const int32_t* row_start, void* workspace,
+                                   int64_t workspace_bytes, void* out, void* stream);
+
 /* Decode attention for callers that cannot hand over scratch memory.  No counterpart in the
  * reference: this exists for hosts embedding the library where device allocation is off limits at
  * the call site -- a serving loop whose memory pool is sized and frozen at start-up, a plugin

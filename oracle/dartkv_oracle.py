@@ -728,8 +728,14 @@ def dense_attention(query: np.ndarray, keys: np.ndarray, values: np.ndarray, q_d
 
 
 def streamed_attention(query: np.ndarray, cache: OracleCache, q_dt: str, scale: Optional[float] = None,
-                       *, flavour: str = "cpu", return_f32: bool = False) -> np.ndarray:
-    """attention.py:32-87: per-segment dequantize + fp32 online softmax, GQA by contiguous head groups."""
+                       *, flavour: str = "cpu", return_f32: bool = False,
+                       row_start: Optional[np.ndarray] = None) -> np.ndarray:
+    """attention.py:32-87: per-segment dequantize + fp32 online softmax, GQA by contiguous head groups.
+
+    ``row_start`` ([B] ints) is not in the reference, whose streamed path takes no mask: tokens before a batch
+    row's first live one get logit -inf, the additive mask the model's dense attention would apply to a
+    left-padded batch.
+    """
 
     q = np.asarray(query, dtype=np.float32)
     if q.ndim != 4:
@@ -748,14 +754,21 @@ def streamed_attention(query: np.ndarray, cache: OracleCache, q_dt: str, scale: 
     run_max = np.full((b, h, rep, q.shape[2]), -np.inf, dtype=np.float32)
     run_sum = np.zeros_like(run_max)
     run_val = np.zeros((b, h, rep, q.shape[2], d), dtype=np.float32)
+    seen = 0
     for kseg, vseg in cache.iter_segments():
         k = materialize(kseg, flavour).astype(np.float32)
         v = materialize(vseg, flavour).astype(np.float32)
         logits = np.einsum("bhrqd,bhtd->bhrqt", qg, k, optimize=True).astype(np.float32) * factor
+        if row_start is not None:
+            positions = seen + np.arange(k.shape[2])
+            dead = positions[None, :] < np.asarray(row_start).reshape(b, 1)
+            logits = np.where(dead[:, None, None, None, :], np.float32(-np.inf), logits)
+        seen += k.shape[2]
         page_max = logits.max(axis=-1)
         new_max = np.maximum(run_max, page_max)
-        old_w = np.exp(run_max - new_max)
-        w = np.exp(logits - new_max[..., None])
+        ref_max = np.where(np.isneginf(new_max), np.float32(0), new_max)   # nothing live yet: all weights zero
+        old_w = np.exp(run_max - ref_max)
+        w = np.exp(logits - ref_max[..., None])
         run_val = run_val * old_w[..., None] + np.einsum("bhrqt,bhtd->bhrqd", w, v, optimize=True).astype(np.float32)
         run_sum = run_sum * old_w + w.sum(axis=-1)
         run_max = new_max

@@ -118,3 +118,51 @@ def test_decode_hook_greedy_tokens_equal_the_reference_hook():
     assert tokens.shape == (2, 13 + 20) and TINY_QWEN3["vocab_size"] == 128
     np.testing.assert_array_equal(tokens.cpu().numpy(), gold["tokens"])
     assert cache.get_seq_length() == 33
+
+
+def _padded_step(model, cache_cfg, prompt, mask, nxt):
+    positions = (mask.cumsum(-1) - 1).clamp(min=0)
+    cache = DartHFCache(cache_cfg)
+    model(prompt, attention_mask=mask, position_ids=positions, past_key_values=cache, use_cache=True)
+    step_mask = torch.cat((mask, torch.ones_like(mask[:, :1])), dim=1)
+    step_pos = positions[:, -1:] + 1
+    return model(nxt, attention_mask=step_mask, position_ids=step_pos, past_key_values=cache, use_cache=True).logits
+
+
+@pytest.mark.parametrize("hole", [False, True])
+def test_fused_hook_honours_the_attention_mask(hole, monkeypatch):
+    """Left-padded batch: the hook turns the mask into per-row first live tokens for the packed kernels.  A mask
+    with a hole is not a left padding and goes through the dense path.  Both equal the materializing path."""
+
+    from dartkv_b200.integrations import qwen3 as adapter
+
+    fused_calls = []
+    kernel_entry = adapter.fused_dart_attention
+
+    def counted(*args, **kwargs):
+        fused_calls.append(kwargs.get("row_start"))
+        return kernel_entry(*args, **kwargs)
+
+    monkeypatch.setattr(adapter, "fused_dart_attention", counted)
+    model = tiny_model(8, torch.float32)
+    cfg = dart.DartKVCacheConfig(bits=4, page_size=4, hold_partial_pages=True, key_group_size=4, value_group_size=8,
+                                 sink_tokens=1, promote_ratio=0.25, metadata_dtype=torch.float32)
+    torch.manual_seed(3)
+    prompt = torch.randint(0, 97, (3, 11)).cuda()
+    nxt = torch.randint(0, 97, (3, 1)).cuda()
+    mask = torch.ones(3, 11, dtype=torch.long).cuda()
+    mask[0, :5] = 0
+    mask[2, :1] = 0
+    if hole:
+        mask[1, 4] = 0
+    with torch.no_grad():
+        expected = _padded_step(model, cfg, prompt, mask, nxt)
+        unmasked = _padded_step(model, cfg, prompt, torch.ones_like(mask), nxt)
+        attach_dart_fused_attention(model)
+        got = _padded_step(model, cfg, prompt, mask, nxt)
+    torch.testing.assert_close(got, expected, rtol=2e-3, atol=2e-3)
+    assert (expected[0] - unmasked[0]).abs().max() > 1e-2          # the mask matters for the padded row
+    if hole:
+        assert fused_calls == []                                    # both layers took the dense path
+    else:
+        assert [starts.tolist() for starts in fused_calls] == [[5, 0, 1]] * 2      # one packed call per layer
