@@ -171,10 +171,18 @@ __device__ __forceinline__ void fused_page_half(const int HF, const int tb, cons
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       s_sum[mt][i] = fmaf(s_acc[mt][i] + s_odd[mt][i], cm[2 * mt + (i >> 1)], bias);
-      // the page that holds the row's first live token: the tokens before it drop out
-      if (mask_below > 0 && 16 * g + 4 * HF + 2 * mt + (i >> 1) + 8 * (i & 1) < mask_below) s_sum[mt][i] = -INFINITY;
-      mx = fmaxf(mx, s_sum[mt][i]);
     }
+  if (mask_below > 0) {   // the page that holds the row's first live token: the tokens before it drop out
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (16 * g + 4 * HF + 2 * mt + (i >> 1) + 8 * (i & 1) < mask_below) s_sum[mt][i] = -INFINITY;
+  }
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mx = fmaxf(mx, s_sum[mt][i]);
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
