@@ -16,7 +16,8 @@ import sys
 PACKAGE_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PACKAGE_DIR, "csrc")
 LIB_PATH = os.path.join(PACKAGE_DIR, "libdartkv_b200.so")
-SOURCES = ("quantize.cu", "cache_append.cu", "append_fast.cu", "decode_attention.cu", "decode_fast.cu", "decode_fused32.cu")
+SOURCES = ("quantize.cu", "cache_append.cu", "append_fast.cu", "decode_attention.cu", "decode_fast.cu", "decode_fused32.cu",
+           "decode_wide.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-O2",

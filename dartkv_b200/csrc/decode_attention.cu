@@ -334,6 +334,13 @@ int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, 
                                  float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
                               cudaStream_t stream);
 
+int dartkv_decode_wide_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
+int dartkv_decode_wide_blocks_per_sm(const dartkv_cache_desc* d);
+int dartkv_decode_wide_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
+                              int flavour, int quads, int stream_blocks, long long units, int total_splits,
+                              float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
+                              cudaStream_t stream);
+
 static int dartkv_sm_count() {
   // per device: a process may drive GPUs of different sizes
   static std::atomic<int> cached[64];
@@ -371,6 +378,8 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
   L.fast = 0;
   if (flavour == DARTKV_DEQUANT_PER_OP && dartkv_decode_fast_supported(d, q_dtype, query_heads)) L.fast = 1;
   if (flavour == DARTKV_DEQUANT_FUSED && dartkv_decode_fused32_supported(d, q_dtype, query_heads)) L.fast = 2;
+  // every other packed geometry with 128-token pages and head_dim 128, and the fp32 flavour of all of them
+  if (!L.fast && flavour != DARTKV_DEQUANT_FUSED && dartkv_decode_wide_supported(d, q_dtype, query_heads)) L.fast = 3;
   // the tensor-core kernels index (row, four-page unit) pairs with 32 bits
   if (L.fast && (long long)bh * ((max(1, (tokens - d->sink_tokens) / d->page_size) + 3) / 4) >= (1ll << 31)) L.fast = 0;
   if (L.fast) {
@@ -386,7 +395,7 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
     const int pages = max(1, (tokens - d->sink_tokens) / d->page_size);
     L.quads = (pages + 3) / 4;
     L.units = (long long)bh * L.quads;
-    const int resident = 2 * dartkv_sm_count();
+    const int resident = (L.fast == 3 ? dartkv_decode_wide_blocks_per_sm(d) : 2) * dartkv_sm_count();
     const double block_fixed = 1.75, dense_cost = 2.0;
     int best_pieces = 1;
     double best_cost = 1e30;
@@ -514,7 +523,7 @@ static int decode_attention_impl(const dartkv_cache_desc* d, const void* query, 
   const int bh = d->batch * d->kv_heads;
   const int D = d->head_dim;
   if (L.fast) {
-    int rc = (L.fast == 2 ? dartkv_decode_fused32_launch : dartkv_decode_fast_launch)(
+    int rc = (L.fast == 3 ? dartkv_decode_wide_launch : L.fast == 2 ? dartkv_decode_fused32_launch : dartkv_decode_fast_launch)(
         d, query, q_dtype, query_heads, scale, flavour, L.quads, L.stream_blocks, L.units, L.total_splits, part_m,
         part_l, part_acc, status, row_start, stream);
     if (rc) return rc;

@@ -53,6 +53,14 @@ __host__ __device__ __forceinline__ int fast_range_end(int sink_tokens, int page
 template <int DT>
 __device__ __forceinline__ float rnd16(float x) { return Half2Ops<DT>::to_float(Half2Ops<DT>::from_float(x)); }
 
+// code * scale + zero the way the chosen flavour rounds it (metadata dtype = cache dtype DT on these kernels)
+template <int DT>
+__device__ __forceinline__ float restore16(float code, float scale, float zero, int flavour) {
+  if (flavour == DARTKV_DEQUANT_FUSED) return __fmaf_rn(code, scale, zero);
+  if (flavour == DARTKV_DEQUANT_FP32) return rnd16<DT>(__fmaf_rn(code, scale, zero));
+  return rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn(code, scale)), zero));
+}
+
 // ------------------------------------------------------------------------------------------------
 // dense tokens (sink prefix, unpacked tail, and tokens packed on one side only).  Tokens whose key and value rows
 // are both dense go through 16-token tiles: logits by m16n8k16 MMAs straight from the rows, probabilities
@@ -82,7 +90,12 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
     for (int i = 0; i < 4; ++i) acc[r][i] = 0.0f;
   }
   const float scale2 = a.scale * kLog2e;
-  const bool fused = a.flavour == DARTKV_DEQUANT_FUSED;
+  const bool fused = a.flavour != DARTKV_DEQUANT_PER_OP;   // a page the other side cuts falls back to per-op
+  // geometry of the packed rows (any code width; the key rows of a page are packed continuously over its groups)
+  const int key_bits = d.key_mode == DARTKV_MIXED_PAGE ? 2 : d.key_bits;
+  const int key_row_bytes = d.page_size * key_bits / 8;
+  const int key_groups = d.page_size / d.key_group;
+  const uint32_t key_mask = (1u << key_bits) - 1u, value_mask = (1u << d.value_bits) - 1u;
   // MMA operand of the tiles: column n = g is query head g (zero past the last head), two channels per register
   const int g = lane >> 2, c = lane & 3;
   uint32_t qb[8][2];
@@ -224,15 +237,16 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
       float kv[4];
       if (kind == 1) {
         const int j = tok - page_first;
+        const int bit = j * key_bits, kg = j / d.key_group;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int ch = lane * 4 + i;
-          uint32_t code = (page[ch * 32 + j / 4] >> ((j % 4) * 2)) & 3u;
+          uint32_t code = (page[ch * key_row_bytes + (bit >> 3)] >> (bit & 7)) & key_mask;
           const int slot = bs.slot_map[ch];
-          if (slot >= 0) code |= ((page[d.key_off_high + slot * 32 + j / 4] >> ((j % 4) * 2)) & 3u) << 2;
-          const float s = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_scale)[ch]);
-          const float z = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_zero)[ch]);
-          kv[i] = fused_key ? __fmaf_rn((float)code, s, z) : rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn((float)code, s)), z));
+          if (slot >= 0) code |= ((page[d.key_off_high + slot * key_row_bytes + (bit >> 3)] >> (bit & 7)) & 3u) << 2;
+          const float s = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_scale)[ch * key_groups + kg]);
+          const float z = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_zero)[ch * key_groups + kg]);
+          kv[i] = restore16<DT>((float)code, s, z, fused_key ? a.flavour : DARTKV_DEQUANT_PER_OP);
         }
       } else {
         kv[0] = H::to_float((uint16_t)(k_raw.x & 0xFFFF)); kv[1] = H::to_float((uint16_t)(k_raw.x >> 16));
@@ -253,14 +267,17 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
       float vv[4];
       if (!value_dense(tok)) {
         const int64_t row = (int64_t)bh * d.max_value_tokens + (tok - d.sink_tokens);
-        const uint32_t byte = d.v_codes[row * 32 + lane];
+        // the lane's four channels: one byte of 2-bit codes, two of 4-bit codes, four of 8-bit codes
+        const uint8_t* packed = d.v_codes + row * d.value_row_bytes + lane * d.value_bits / 2;
+        uint32_t word = packed[0];
+        if (d.value_bits >= 4) word |= (uint32_t)packed[1] << 8;
+        if (d.value_bits == 8) word |= (uint32_t)packed[2] << 16 | (uint32_t)packed[3] << 24;
         const int g = (lane * 4) / d.value_group;
         const uint16_t* meta = reinterpret_cast<const uint16_t*>(d.v_meta) + row * 2 * d.value_groups;
         const float sc = H::to_float(meta[g]), z = H::to_float(meta[d.value_groups + g]);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          vv[i] = fused ? __fmaf_rn((float)((byte >> (2 * i)) & 3u), sc, z)
-                        : rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn((float)((byte >> (2 * i)) & 3u), sc)), z));
+          vv[i] = restore16<DT>((float)((word >> (d.value_bits * i)) & value_mask), sc, z, a.flavour);
       } else {
         vv[0] = H::to_float((uint16_t)(v_raw.x & 0xFFFF)); vv[1] = H::to_float((uint16_t)(v_raw.x >> 16));
         vv[2] = H::to_float((uint16_t)(v_raw.y & 0xFFFF)); vv[3] = H::to_float((uint16_t)(v_raw.y >> 16));

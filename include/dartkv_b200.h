@@ -204,7 +204,8 @@ int dartkv_decode_attention(const dartkv_cache_desc* desc, const void* query, in
                             void* out, void* stream);
 /* How dartkv_decode_attention would split a call; host arithmetic only, nothing is launched (no counterpart in
  * the reference: it exists so that integrators and tests can see the plan).  kernel: 0 generic, 1 tensor-core
- * per-op flavour, 2 tensor-core unrounded flavour.  On the tensor-core layouts one unit is four consecutive pages
+ * per-op flavour (2-bit pages), 2 tensor-core unrounded flavour (2-bit pages), 3 tensor-core kernel for every
+ * other packed geometry and the fp32 flavour.  On the tensor-core layouts one unit is four consecutive pages
  * of a (batch, kv head) row; block j of `stream_blocks` owns units [j*units/stream_blocks, (j+1)*units/stream_blocks)
  * and every row is touched by at most total_splits - 1 of them (plus its dense-token block). */
 typedef struct {
