@@ -74,15 +74,20 @@ def test_tensor_core_plans_stay_inside_their_partial_slots(flavour, split, decod
         assert LIB.dartkv_decode_workspace_bytes(ctypes.byref(d), 4 * heads, tokens) >= need
 
 
-def test_other_geometries_take_the_generic_kernel():
-    for kwargs in (dict(value_bits=4), dict(key_bits=4, promoted=0), dict(value_group=32)):
+def test_other_geometries_take_the_general_tensor_core_kernel():
+    for kwargs in (dict(value_bits=4), dict(key_bits=4, promoted=0), dict(value_group=32), dict(value_bits=8, key_bits=8, promoted=0)):
         d = make_desc(2, 2, **kwargs)
-        info = plan(d, _lib.BF16, 8, _lib.DEQUANT_PER_OP, 5000)
+        for flavour in (_lib.DEQUANT_PER_OP, _lib.DEQUANT_FP32):
+            info = plan(d, _lib.BF16, 8, flavour, 5000)
+            assert info.kernel == 3 and info.stream_blocks >= 1 and info.generic_splits == 0
+            assert info.quads == (max(1, (5000 - 32) // 128) + 3) // 4 and 2 <= info.total_splits <= 17
+        # the unrounded flavour of these geometries has no 16-bit tile to go through: CUDA-core kernel
+        info = plan(d, _lib.BF16, 8, _lib.DEQUANT_FUSED, 5000)
         assert info.kernel == 0 and info.stream_blocks == 0 and info.generic_splits >= 1
         assert info.total_splits == info.generic_splits
     d = make_desc(2, 2)
     assert plan(d, _lib.F32, 8, _lib.DEQUANT_PER_OP, 5000).kernel == 0      # query dtype differs from the cache dtype
-    assert plan(d, _lib.BF16, 8, _lib.DEQUANT_FP32, 5000).kernel == 0       # no tensor-core kernel for this flavour
+    assert plan(d, _lib.BF16, 8, _lib.DEQUANT_FP32, 5000).kernel == 3       # the fp32 flavour of the headline geometry
     assert plan(d, _lib.BF16, 16, _lib.DEQUANT_PER_OP, 5000).kernel == 0    # 8 query heads per kv head
 
 
