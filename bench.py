@@ -238,8 +238,9 @@ def workload_config(args, wl, world: int) -> dict:
             "page": GEOM["page"], "bits": "2-bit + 0.25 promotion", "key_group": GEOM["key_group"],
             "value_group": GEOM["value_group"], "sinks": GEOM["sinks"], "metadata": "bf16",
             "bytes_per_step": step_bytes(wl["batch"], wl["ctx"]),
-            "dequant": "per-op rounded (reference streamed path)" if args.flavour == "per_op"
-            else "unrounded fp32 (reference Triton kernels)",
+            "dequant": {"per_op": "per-op rounded (reference streamed path)",
+                        "fp32": "fp32 with one rounding (reference streamed path on CUDA)",
+                        "fused": "unrounded fp32 (reference Triton kernels)"}[args.flavour],
             "l2": f"per-GPU working set {local_bytes / 1e6:.0f} MB exceeds the 126 MB L2",
             "parallelism": (f"batch sharded over {world} GPU(s)" if head_groups == 1 else
                             f"batch x KV heads sharded over {world} GPU(s) ({head_groups} head groups)") +
@@ -450,7 +451,7 @@ def gpu_arm(args, wl) -> None:
         except Exception as exc:   # symmetric memory cannot be set up on this machine: NCCL does the gather
             gather_kind = f"nccl all_gather_into_tensor (peer stores unavailable: {type(exc).__name__}: {str(exc)[:120]})"
 
-    flavour = _lib.DEQUANT_FUSED if args.flavour == "fused" else _lib.DEQUANT_PER_OP
+    flavour = {"per_op": _lib.DEQUANT_PER_OP, "fp32": _lib.DEQUANT_FP32, "fused": _lib.DEQUANT_FUSED}[args.flavour]
 
     def decode():
         dart.decode_attention(q3, cache, out=out, flavour=flavour)
@@ -825,8 +826,9 @@ def main() -> None:
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
     parser.add_argument("--workload", choices=sorted(WORKLOADS) + ["config4"], default="config5")
     parser.add_argument("--skip-extras", action="store_true", help="skip the append microbench and the CPU baseline")
-    parser.add_argument("--flavour", choices=("per_op", "fused"), default="per_op",
-                        help="dequantization arithmetic of the timed decode call (default: the pinned per-op rounding)")
+    parser.add_argument("--flavour", choices=("per_op", "fp32", "fused"), default="per_op",
+                        help="dequantization arithmetic of the timed decode call (default: the pinned per-op rounding; "
+                             "fp32 runs the general tensor-core kernel that also serves 4/8-bit pages)")
     parser.add_argument("--gather", choices=("peer", "nccl"), default="peer",
                         help="multi-GPU output gather: peer stores from the decode kernels (default) or NCCL")
     parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (e.g. one rank's share)")

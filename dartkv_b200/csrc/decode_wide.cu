@@ -40,6 +40,7 @@ constexpr int kKeyRow = 48, kValueRow = 272;
 static_assert(16 * kValueRow <= kTileBytes, "the value tile shares the key tile's memory");
 
 struct WideBlockSmem {
+  uint16_t q16[8][136];   // query heads of the row's KV head (rows rep.. are zero); 272-byte rows keep a quad's loads apart
   float merge_m[kWarps][4];
   float merge_l[kWarps][4];
   int slot_map[128];
@@ -75,62 +76,80 @@ template <int DT> __device__ __forceinline__ constexpr float magic_value(int p) 
 
 // One (scale, zero point) pair made ready for a run of code pairs whose codes sit at bit position PA or PB of
 // their 16-bit halves.
-template <int DT, int PA, int PB>
+// two floats -> one register of two 16-bit numbers (round to nearest even), `lo` in the low half
+template <int DT> __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  uint32_t d;
+  if (DT == DARTKV_F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+// the two 16-bit numbers of a register as floats
+template <int DT> __device__ __forceinline__ void unpack16(uint32_t x, float& lo, float& hi) {
+  if (DT == DARTKV_F16) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&x));
+    lo = f.x; hi = f.y;
+  } else {
+    lo = __uint_as_float(x << 16); hi = __uint_as_float(x & 0xFFFF0000u);
+  }
+}
+
+// FP32 = false: fl(fl(code * scale) + zero) in the 16-bit metadata dtype; true: code * scale + zero in fp32,
+// rounded once to the 16-bit cache dtype
+template <int DT, bool FP32, int PA, int PB>
 struct Restore {
   using H = Half2Ops<DT>;
   uint32_t s2, z2, nms_a, nms_b;
   float sf, zf;
-  bool fp32;
   // fl(c * s) = fma(magic + c, s, -magic * s) needs magic * s exact: always in bf16; in fp16 magic 1024 could
   // overflow with scales above 63, so position 0 subtracts the magic first (one more packed operation)
   static constexpr bool kFmaA = !(DT == DARTKV_F16 && PA == 0), kFmaB = !(DT == DARTKV_F16 && PB == 0);
-  __device__ __forceinline__ void init(uint16_t s, uint16_t z, bool fp32_flavour) {
-    fp32 = fp32_flavour;
-    s2 = (uint32_t)s * 0x00010001u;
-    z2 = (uint32_t)z * 0x00010001u;
+  __device__ __forceinline__ void init(uint16_t s, uint16_t z) {
     const uint32_t neg_a = (magic16<DT>(PA) * 0x00010001u) | 0x80008000u, neg_b = (magic16<DT>(PB) * 0x00010001u) | 0x80008000u;
-    nms_a = kFmaA ? H::mul(s2, neg_a) : neg_a;
-    nms_b = kFmaB ? H::mul(s2, neg_b) : neg_b;
-    sf = H::to_float(s);
-    zf = H::to_float(z);
+    if (FP32) {
+      sf = H::to_float(s);
+      zf = H::to_float(z);
+      nms_a = neg_a;
+      nms_b = neg_b;
+    } else {
+      s2 = (uint32_t)s * 0x00010001u;
+      z2 = (uint32_t)z * 0x00010001u;
+      nms_a = kFmaA ? H::mul(s2, neg_a) : neg_a;
+      nms_b = kFmaB ? H::mul(s2, neg_b) : neg_b;
+    }
   }
   // x: two codes, each OR-ed into the magic number of its half at position PA (SECOND = false) or PB
   template <bool SECOND>
   __device__ __forceinline__ uint32_t from_magic(uint32_t x) const {
-    constexpr int P = SECOND ? PB : PA;
     constexpr bool fma_form = SECOND ? kFmaB : kFmaA;
     const uint32_t nms = SECOND ? nms_b : nms_a;
-    if (!fp32) {
+    if (!FP32) {
       if (fma_form) return H::add(H::fma(x, s2, nms), z2);   // fl(fl(c * s) + z)
       return H::add(H::mul(H::add(x, nms), s2), z2);         // nms holds -magic here: x - magic = c exactly
     }
-    const float m = magic_value<DT>(P);
-    const float c0 = H::to_float((uint16_t)(x & 0xFFFFu)) - m, c1 = H::to_float((uint16_t)(x >> 16)) - m;
-    return (uint32_t)H::from_float(__fmaf_rn(c0, sf, zf)) | ((uint32_t)H::from_float(__fmaf_rn(c1, sf, zf)) << 16);
+    float c0, c1;
+    unpack16<DT>(H::add(x, nms), c0, c1);                    // nms holds -magic here: the codes, exactly
+    return pack16<DT>(__fmaf_rn(c0, sf, zf), __fmaf_rn(c1, sf, zf));
   }
   // two codes as exact floats
   __device__ __forceinline__ uint32_t from_codes(float c0, float c1) const {
-    if (!fp32) {
-      const uint32_t c2 = (uint32_t)H::from_float(c0) | ((uint32_t)H::from_float(c1) << 16);   // small integers: exact
-      return H::add(H::mul(c2, s2), z2);
-    }
-    return (uint32_t)H::from_float(__fmaf_rn(c0, sf, zf)) | ((uint32_t)H::from_float(__fmaf_rn(c1, sf, zf)) << 16);
+    if (!FP32) return H::add(H::mul(pack16<DT>(c0, c1), s2), z2);   // small integers: exact in 16 bits
+    return pack16<DT>(__fmaf_rn(c0, sf, zf), __fmaf_rn(c1, sf, zf));
   }
 };
 
 // code positions per width: plain 2-bit codes sit at bits 2 and 6 of a byte in fp16 (magics 256 and 16) and at
 // bits 0 and 4 in bf16; 4-bit codes at bit 4 in fp16 and bit 0 in bf16; two planes (a 4-bit code) at bits 0 and
 // 4 in fp16 and at bit 0 only in bf16, whose 7 mantissa bits cannot hold a 4-bit code from bit 4 on
-template <int DT> using Restore2 = Restore<DT, DT == DARTKV_F16 ? 2 : 0, DT == DARTKV_F16 ? 6 : 4>;
-template <int DT> using Restore22 = Restore<DT, 0, DT == DARTKV_F16 ? 4 : 0>;
-template <int DT> using Restore4 = Restore<DT, DT == DARTKV_F16 ? 4 : 0, DT == DARTKV_F16 ? 4 : 0>;
-template <int DT> using Restore8 = Restore<DT, 0, 0>;
+template <int DT, bool FP32> using Restore2 = Restore<DT, FP32, DT == DARTKV_F16 ? 2 : 0, DT == DARTKV_F16 ? 6 : 4>;
+template <int DT, bool FP32> using Restore22 = Restore<DT, FP32, 0, DT == DARTKV_F16 ? 4 : 0>;
+template <int DT, bool FP32> using Restore4 = Restore<DT, FP32, DT == DARTKV_F16 ? 4 : 0, DT == DARTKV_F16 ? 4 : 0>;
+template <int DT, bool FP32> using Restore8 = Restore<DT, FP32, 0, 0>;
 
 __device__ __forceinline__ constexpr uint32_t byte_pair_selector(int j) { return j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12); }
 
 // Sixteen 2-bit codes of a word -> 8 registers, register i = elements (2i, 2i+1).
-template <int DT>
-__device__ __forceinline__ void restore_2bit(uint32_t w, const Restore2<DT>& r, uint32_t (&out)[8]) {
+template <int DT, bool FP32>
+__device__ __forceinline__ void restore_2bit(uint32_t w, const Restore2<DT, FP32>& r, uint32_t (&out)[8]) {
   // byte j of `lo` / `hi` feeds the low / high halves: elements 4j and 4j+2 (low), 4j+1 and 4j+3 (high) at the same bits
   const uint32_t lo = DT == DARTKV_F16 ? w << 2 : w, hi = DT == DARTKV_F16 ? w : w >> 2;
   constexpr uint32_t mask_a = DT == DARTKV_F16 ? 0x000C000Cu : 0x00030003u, mask_b = mask_a << 4;
@@ -144,8 +163,8 @@ __device__ __forceinline__ void restore_2bit(uint32_t w, const Restore2<DT>& r, 
 }
 
 // Sixteen codes of two 2-bit planes (code = low | high << 2) -> 8 registers of adjacent elements.
-template <int DT>
-__device__ __forceinline__ void restore_2plus2(uint32_t w, uint32_t high, const Restore22<DT>& r, uint32_t (&out)[8]) {
+template <int DT, bool FP32>
+__device__ __forceinline__ void restore_2plus2(uint32_t w, uint32_t high, const Restore22<DT, FP32>& r, uint32_t (&out)[8]) {
   const uint32_t t = w >> 2, hs = high << 2;
   const uint32_t m0 = magic16<DT>(0) * 0x00010001u, m4 = magic16<DT>(4) * 0x00010001u;
 #pragma unroll
@@ -162,8 +181,8 @@ __device__ __forceinline__ void restore_2plus2(uint32_t w, uint32_t high, const 
 }
 
 // Eight 4-bit codes of a word -> 4 registers of adjacent elements.
-template <int DT>
-__device__ __forceinline__ void restore_4bit(uint32_t w, const Restore4<DT>& r, uint32_t* out) {
+template <int DT, bool FP32>
+__device__ __forceinline__ void restore_4bit(uint32_t w, const Restore4<DT, FP32>& r, uint32_t* out) {
   const uint32_t lo = DT == DARTKV_F16 ? w << 4 : w, hi = DT == DARTKV_F16 ? w : w >> 4;
   constexpr uint32_t mask = DT == DARTKV_F16 ? 0x00F000F0u : 0x000F000Fu;
   const uint32_t m = magic16<DT>(DT == DARTKV_F16 ? 4 : 0) * 0x00010001u;
@@ -172,8 +191,8 @@ __device__ __forceinline__ void restore_4bit(uint32_t w, const Restore4<DT>& r, 
 }
 
 // Four 8-bit codes of a word -> 2 registers of adjacent elements.
-template <int DT>
-__device__ __forceinline__ void restore_8bit(uint32_t w, const Restore8<DT>& r, uint32_t* out) {
+template <int DT, bool FP32>
+__device__ __forceinline__ void restore_8bit(uint32_t w, const Restore8<DT, FP32>& r, uint32_t* out) {
   if (DT == DARTKV_F16) {
     // 1024 + code: the code byte is the low byte of the half, 0x64 its high byte
 #pragma unroll
@@ -190,7 +209,95 @@ __device__ __forceinline__ void restore_8bit(uint32_t w, const Restore8<DT>& r, 
   }
 }
 
-template <int DT>
+// Keys of a staged chunk -> tile[channel][16 tokens] (rows of kKeyRow bytes).  KIND: 2, 4, 8 or 22 (two planes).
+template <int DT, bool FP32, int KIND>
+__device__ __forceinline__ void keys_to_tile(const uint8_t* st, const WideGeom& w, const uint8_t* slot_of, uint8_t* tile,
+                                             int lane, int kg) {
+  const uint16_t* kscale = reinterpret_cast<const uint16_t*>(st + w.k_scale);
+  const uint16_t* kzero = reinterpret_cast<const uint16_t*>(st + w.k_zero);
+#pragma unroll 2
+  for (int r = 0; r < 4; ++r) {
+    const int ch = lane + 32 * r;
+    const uint16_t sc = kscale[ch * w.key_groups + kg], zr = kzero[ch * w.key_groups + kg];
+    uint32_t out[8];
+    if (KIND == 22) {
+      Restore22<DT, FP32> rs;
+      rs.init(sc, zr);
+      const uint32_t low = *reinterpret_cast<const uint32_t*>(st + ch * 4);
+      const int slot = slot_of[ch];
+      const uint32_t high = slot != 0xFF ? *reinterpret_cast<const uint32_t*>(st + w.k_high + slot * 4) : 0u;
+      restore_2plus2<DT, FP32>(low, high, rs, out);
+    } else if (KIND == 2) {
+      Restore2<DT, FP32> rs;
+      rs.init(sc, zr);
+      restore_2bit<DT, FP32>(*reinterpret_cast<const uint32_t*>(st + ch * 4), rs, out);
+    } else if (KIND == 4) {
+      Restore4<DT, FP32> rs;
+      rs.init(sc, zr);
+      const uint2 words = *reinterpret_cast<const uint2*>(st + ch * 8);
+      restore_4bit<DT, FP32>(words.x, rs, out);
+      restore_4bit<DT, FP32>(words.y, rs, out + 4);
+    } else {
+      Restore8<DT, FP32> rs;
+      rs.init(sc, zr);
+      const uint4 words = *reinterpret_cast<const uint4*>(st + ch * 16);
+      restore_8bit<DT, FP32>(words.x, rs, out);
+      restore_8bit<DT, FP32>(words.y, rs, out + 2);
+      restore_8bit<DT, FP32>(words.z, rs, out + 4);
+      restore_8bit<DT, FP32>(words.w, rs, out + 6);
+    }
+    uint4* row = reinterpret_cast<uint4*>(tile + ch * kKeyRow);
+    row[0] = make_uint4(out[0], out[1], out[2], out[3]);
+    row[1] = make_uint4(out[4], out[5], out[6], out[7]);
+  }
+}
+
+// Values of a staged chunk -> tile[16 tokens][128 channels] (rows of kValueRow bytes).  A lane takes 64 channels
+// of one token: 16 * BITS / 2 bytes, i.e. BITS / 2 pieces of 16 bytes.
+template <int DT, bool FP32, int BITS>
+__device__ __forceinline__ void values_to_tile(const uint8_t* st, const WideGeom& w, uint8_t* tile, int lane, int vrb,
+                                               int vgroups, int value_group) {
+  const int tok = lane & 15, half = lane >> 4;
+  const uint8_t* codes = st + w.v_codes + tok * vrb + half * (vrb >> 1);
+  const uint16_t* meta = reinterpret_cast<const uint16_t*>(st + w.v_meta) + tok * 2 * vgroups;
+  uint8_t* row = tile + tok * kValueRow + half * 128;
+  constexpr int kPieces = BITS / 2, kChannelsPerWord = 32 / BITS;
+#pragma unroll
+  for (int p = 0; p < kPieces; ++p) {
+    const int q = (p + tok) & (kPieces - 1);   // lanes start at different pieces: fewer bank conflicts
+    const uint4 words = *reinterpret_cast<const uint4*>(codes + 16 * q);
+    const uint32_t ws[4] = {words.x, words.y, words.z, words.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int ch_local = (4 * q + k) * kChannelsPerWord;   // first channel of the word among this lane's 64
+      const int group = (64 * half + ch_local) / value_group;
+      const uint16_t sc = meta[group], zr = meta[vgroups + group];
+      uint8_t* dst = row + ch_local * 2;
+      if (BITS == 2) {
+        Restore2<DT, FP32> rs;
+        rs.init(sc, zr);
+        uint32_t out[8];
+        restore_2bit<DT, FP32>(ws[k], rs, out);
+        reinterpret_cast<uint4*>(dst)[0] = make_uint4(out[0], out[1], out[2], out[3]);
+        reinterpret_cast<uint4*>(dst)[1] = make_uint4(out[4], out[5], out[6], out[7]);
+      } else if (BITS == 4) {
+        Restore4<DT, FP32> rs;
+        rs.init(sc, zr);
+        uint32_t out[4];
+        restore_4bit<DT, FP32>(ws[k], rs, out);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(out[0], out[1], out[2], out[3]);
+      } else {
+        Restore8<DT, FP32> rs;
+        rs.init(sc, zr);
+        uint32_t out[2];
+        restore_8bit<DT, FP32>(ws[k], rs, out);
+        *reinterpret_cast<uint2*>(dst) = make_uint2(out[0], out[1]);
+      }
+    }
+  }
+}
+
+template <int DT, bool FP32>
 __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_desc d, FastArgs a, WideGeom w) {
   using H = Half2Ops<DT>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -220,7 +327,6 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
   const int k_end = d.state[2], v_end = d.state[3], sink_filled = d.state[4];
   const int fast_end = fast_range_end(d.sink_tokens, d.page_size, k_end, v_end, sink_filled);
   const int total_pages = fast_end > d.sink_tokens ? (fast_end - d.sink_tokens) / 128 : 0;
-  const bool fp32_flavour = a.flavour == DARTKV_DEQUANT_FP32;
   const float scale2 = a.scale * kLog2e;
   const int vrb = d.value_row_bytes, vgroups = d.value_groups, vbits = d.value_bits;
   const int key_row_bytes = w.key_kind == 22 ? 32 : 16 * w.key_kind;
@@ -277,15 +383,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
     issue(0);
     issue(1);
 
-    // A operand of the logits: rows = query heads (rows rep.. are zero), two channels per register
-    uint32_t qa[8][2];
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks)
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-        qa[ks][j] = g < rep ? *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(a.q) +
-                                  ((int64_t)b * a.query_heads + hkv * rep + g) * 128 + 16 * ks + 8 * j + 2 * c)
-                            : 0u;
+    // A operand of the logits: rows = query heads (rows rep.. are zero); kept in shared memory, the registers
+    // are needed by the accumulators
+    for (int i = tid; i < 8 * 128; i += kThreads) {
+      const int r = i >> 7, ch = i & 127;
+      bs.q16[r][ch] = r < rep ? reinterpret_cast<const uint16_t*>(a.q)[((int64_t)b * a.query_heads + hkv * rep + r) * 128 + ch] : (uint16_t)0;
+    }
+    __syncthreads();
+    const uint16_t* q_lane = &bs.q16[g][2 * c];
 
     float o_acc[16][4];   // [n-tile: channels 8n..8n+7][c-reg]: (head g, channels 8n+2c, +1) from the high (0,1) / low (2,3) parts of P
 #pragma unroll
@@ -309,44 +414,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
         for (int k = lane; k < promoted; k += 32) slot_of[index[k] & 127] = (uint8_t)k;
         __syncwarp();
       }
-      {
-        const uint16_t* kscale = reinterpret_cast<const uint16_t*>(st + w.k_scale);
-        const uint16_t* kzero = reinterpret_cast<const uint16_t*>(st + w.k_zero);
-#pragma unroll 1
-        for (int r = 0; r < 4; ++r) {
-          const int ch = lane + 32 * r;
-          const uint16_t sc = kscale[ch * w.key_groups + kg], zr = kzero[ch * w.key_groups + kg];
-          uint32_t out[8];
-          if (w.key_kind == 22) {
-            Restore22<DT> rs;
-            rs.init(sc, zr, fp32_flavour);
-            const uint32_t low = *reinterpret_cast<const uint32_t*>(st + ch * 4);
-            const int slot = slot_of[ch];
-            const uint32_t high = slot != 0xFF ? *reinterpret_cast<const uint32_t*>(st + w.k_high + slot * 4) : 0u;
-            restore_2plus2<DT>(low, high, rs, out);
-          } else if (w.key_kind == 2) {
-            Restore2<DT> rs;
-            rs.init(sc, zr, fp32_flavour);
-            restore_2bit<DT>(*reinterpret_cast<const uint32_t*>(st + ch * 4), rs, out);
-          } else if (w.key_kind == 4) {
-            Restore4<DT> rs;
-            rs.init(sc, zr, fp32_flavour);
-            const uint2 words = *reinterpret_cast<const uint2*>(st + ch * 8);
-            restore_4bit<DT>(words.x, rs, out);
-            restore_4bit<DT>(words.y, rs, out + 4);
-          } else {
-            Restore8<DT> rs;
-            rs.init(sc, zr, fp32_flavour);
-            const uint4 words = *reinterpret_cast<const uint4*>(st + ch * 16);
-            restore_8bit<DT>(words.x, rs, out);
-            restore_8bit<DT>(words.y, rs, out + 2);
-            restore_8bit<DT>(words.z, rs, out + 4);
-            restore_8bit<DT>(words.w, rs, out + 6);
-          }
-          uint4* row = reinterpret_cast<uint4*>(tile + ch * kKeyRow);
-          row[0] = make_uint4(out[0], out[1], out[2], out[3]);
-          row[1] = make_uint4(out[4], out[5], out[6], out[7]);
-        }
+      switch (w.key_kind) {
+        case 22: keys_to_tile<DT, FP32, 22>(st, w, slot_of, tile, lane, kg); break;
+        case 2: keys_to_tile<DT, FP32, 2>(st, w, slot_of, tile, lane, kg); break;
+        case 4: keys_to_tile<DT, FP32, 4>(st, w, slot_of, tile, lane, kg); break;
+        default: keys_to_tile<DT, FP32, 8>(st, w, slot_of, tile, lane, kg); break;
       }
       __syncwarp();
 
@@ -359,53 +431,19 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
         for (int ks = 0; ks < 8; ++ks) {
           uint32_t kb[4];
           ldmatrix_x4_trans(kb, lane_row + 16 * ks * kKeyRow);
-          H::mma(s_acc[0], qa[ks][0], 0u, qa[ks][1], 0u, kb[0], kb[1]);
-          H::mma(s_acc[1], qa[ks][0], 0u, qa[ks][1], 0u, kb[2], kb[3]);
+          const uint32_t qa0 = *reinterpret_cast<const uint32_t*>(q_lane + 16 * ks);
+          const uint32_t qa1 = *reinterpret_cast<const uint32_t*>(q_lane + 16 * ks + 8);
+          H::mma(s_acc[0], qa0, 0u, qa1, 0u, kb[0], kb[1]);
+          H::mma(s_acc[1], qa0, 0u, qa1, 0u, kb[2], kb[3]);
         }
       }
       __syncwarp();   // every lane has its logits: the tile may take the values
 
       // ---- values of the chunk -> tile[16 tokens][128 channels]
-      {
-        const int tok = lane & 15, half = lane >> 4;           // 64 channels of one token per lane
-        const uint8_t* codes = st + w.v_codes + tok * vrb + half * (vrb >> 1);
-        const uint16_t* meta = reinterpret_cast<const uint16_t*>(st + w.v_meta) + tok * 2 * vgroups;
-        uint8_t* row = tile + tok * kValueRow + half * 128;
-        const int pieces = vrb >> 5;                            // 16-byte pieces of this lane's 64 channels: 1, 2 or 4
-        const int ch_per_piece = 64 / pieces;
-#pragma unroll 1
-        for (int p = 0; p < pieces; ++p) {
-          const int q = (p + tok) & (pieces - 1);               // lanes start at different pieces: fewer bank conflicts
-          const uint4 words = *reinterpret_cast<const uint4*>(codes + 16 * q);
-          const uint32_t ws[4] = {words.x, words.y, words.z, words.w};
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int ch_local = q * ch_per_piece + k * (ch_per_piece >> 2);   // first channel of the word, of this lane's 64
-            const int group = (64 * half + ch_local) / d.value_group;
-            const uint16_t sc = meta[group], zr = meta[vgroups + group];
-            uint8_t* dst = row + ch_local * 2;
-            if (vbits == 2) {
-              Restore2<DT> rs;
-              rs.init(sc, zr, fp32_flavour);
-              uint32_t out[8];
-              restore_2bit<DT>(ws[k], rs, out);
-              reinterpret_cast<uint4*>(dst)[0] = make_uint4(out[0], out[1], out[2], out[3]);
-              reinterpret_cast<uint4*>(dst)[1] = make_uint4(out[4], out[5], out[6], out[7]);
-            } else if (vbits == 4) {
-              Restore4<DT> rs;
-              rs.init(sc, zr, fp32_flavour);
-              uint32_t out[4];
-              restore_4bit<DT>(ws[k], rs, out);
-              *reinterpret_cast<uint4*>(dst) = make_uint4(out[0], out[1], out[2], out[3]);
-            } else {
-              Restore8<DT> rs;
-              rs.init(sc, zr, fp32_flavour);
-              uint32_t out[2];
-              restore_8bit<DT>(ws[k], rs, out);
-              *reinterpret_cast<uint2*>(dst) = make_uint2(out[0], out[1]);
-            }
-          }
-        }
+      switch (vbits) {
+        case 2: values_to_tile<DT, FP32, 2>(st, w, tile, lane, vrb, vgroups, d.value_group); break;
+        case 4: values_to_tile<DT, FP32, 4>(st, w, tile, lane, vrb, vgroups, d.value_group); break;
+        default: values_to_tile<DT, FP32, 8>(st, w, tile, lane, vrb, vgroups, d.value_group); break;
       }
       __syncwarp();
       issue(idx + 2);   // the stage has been read by every lane
@@ -509,6 +547,12 @@ static size_t wide_smem_bytes(const WideGeom& w) {
   return (sizeof(WideBlockSmem) + 127) / 128 * 128 + (streaming > merge ? streaming : merge);
 }
 
+using WideKernel = void (*)(dartkv_cache_desc, FastArgs, WideGeom);
+static WideKernel wide_variant(int dtype, bool fp32) {
+  if (dtype == DARTKV_BF16) return fp32 ? decode_wide_kernel<DARTKV_BF16, true> : decode_wide_kernel<DARTKV_BF16, false>;
+  return fp32 ? decode_wide_kernel<DARTKV_F16, true> : decode_wide_kernel<DARTKV_F16, false>;
+}
+
 }  // namespace
 
 int dartkv_decode_wide_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads) {
@@ -548,13 +592,13 @@ int dartkv_decode_wide_launch(const dartkv_cache_desc* d, const void* query, int
     int device = 0;
     DARTKV_CUDA_OK(cudaGetDevice(&device));
     if (device < 0 || device >= 64 || !ready[device].load(std::memory_order_acquire)) {
-      DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_wide_kernel<DARTKV_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-      DARTKV_CUDA_OK(cudaFuncSetAttribute(decode_wide_kernel<DARTKV_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+      for (int dt : {DARTKV_BF16, DARTKV_F16})
+        for (int fp32 : {0, 1})
+          DARTKV_CUDA_OK(cudaFuncSetAttribute(wide_variant(dt, fp32 != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
       if (device >= 0 && device < 64) ready[device].store(true, std::memory_order_release);
     }
   }
-  if (d->dtype == DARTKV_BF16) decode_wide_kernel<DARTKV_BF16><<<grid, kThreads, smem, stream>>>(*d, a, w);
-  else decode_wide_kernel<DARTKV_F16><<<grid, kThreads, smem, stream>>>(*d, a, w);
+  wide_variant(d->dtype, flavour == DARTKV_DEQUANT_FP32)<<<grid, kThreads, smem, stream>>>(*d, a, w);
   DARTKV_LAUNCH_OK("decode_wide_kernel");
   return DARTKV_OK;
 }
