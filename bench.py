@@ -41,6 +41,7 @@ NCU_CONFIG3 = {"algorithmic": 192774144, "dram_read": 192.73e6, "dram_write": 4.
 # loading the package or its CUDA library; the GPU arm asserts that the two agree)
 GEOM = dict(query_heads=32, kv_heads=8, head_dim=128, page=128, key_group=128, value_group=64, sinks=32,
             promote_ratio=0.25, bits=2)
+HEADLINE = dict(GEOM)   # --bits / --promote / --value-group change GEOM for runs off the headline geometry
 
 
 def cache_kwargs():
@@ -56,7 +57,24 @@ def bytes_per_bh(ctx: int) -> int:
     pages = (ctx - GEOM["sinks"]) // GEOM["page"]
     tail = ctx - GEOM["sinks"] - pages * GEOM["page"]
     d = GEOM["head_dim"]
-    return GEOM["sinks"] * d * 2 * 2 + pages * (5760 + 5120) + tail * d * 2 * 2
+    return GEOM["sinks"] * d * 2 * 2 + pages * page_bytes() + tail * d * 2 * 2
+
+
+def page_bytes() -> int:
+    """Packed bytes of one 128-token page of one (batch row, KV head), 16-bit metadata: 5760 + 5120 on the headline
+    geometry.  Keys: code rows (2-bit rows plus a 2-bit plane and int32 indices for the promoted channels, or
+    `bits`-wide rows), a scale and a zero point per channel and key group.  Values: code rows, a scale and a zero
+    point per token and value group."""
+
+    d, page = GEOM["head_dim"], GEOM["page"]
+    promoted = min(d, int(d * GEOM["promote_ratio"] + 1e-6))
+    key_meta = 2 * d * (page // GEOM["key_group"]) * 2
+    if promoted:
+        key = d * page // 4 + promoted * page // 4 + promoted * 4 + key_meta
+    else:
+        key = d * page * GEOM["bits"] // 8 + key_meta
+    value = page * d * GEOM["bits"] // 8 + page * 2 * (d // GEOM["value_group"]) * 2
+    return key + value
 
 
 def step_bytes(batch: int, ctx: int) -> int:
@@ -75,9 +93,12 @@ def build_device_cache(rows, ctx: int, seed: int, device: torch.device, keep_inp
 
     from dartkv_b200.synthetic import HEADLINE_GEOMETRY, build_headline_cache
 
-    assert HEADLINE_GEOMETRY == GEOM
+    assert HEADLINE_GEOMETRY == HEADLINE
+    overrides = {{"bits": "bits", "promote_ratio": "promote_ratio", "value_group": "value_group_size"}[k]: GEOM[k]
+                 for k in ("bits", "promote_ratio", "value_group") if GEOM[k] != HEADLINE[k]}
     rows = list(rows)
-    got = build_headline_cache(rows, ctx, seed, device, heads=heads, keep_rows=rows if keep_inputs else None)
+    got = build_headline_cache(rows, ctx, seed, device, heads=heads, keep_rows=rows if keep_inputs else None,
+                               cache_overrides=overrides)
     return got if keep_inputs else got[:2]
 
 
@@ -235,7 +256,11 @@ def workload_config(args, wl, world: int) -> dict:
     local_bytes = step_bytes(local_batch, wl["ctx"]) // head_groups
     return {"workload": args.workload, "batch": wl["batch"], "context": wl["ctx"], "per_gpu_batch": local_batch,
             "query_heads": GEOM["query_heads"], "kv_heads": GEOM["kv_heads"], "head_dim": GEOM["head_dim"],
-            "page": GEOM["page"], "bits": "2-bit + 0.25 promotion", "key_group": GEOM["key_group"],
+            "page": GEOM["page"],
+            "bits": f"{GEOM['bits']}-bit values, " + (f"2+2-bit keys ({GEOM['promote_ratio']} promoted)" if GEOM["promote_ratio"] > 0
+                                                       else f"{GEOM['bits']}-bit keys")
+            if GEOM != HEADLINE else "2-bit + 0.25 promotion",
+            "key_group": GEOM["key_group"],
             "value_group": GEOM["value_group"], "sinks": GEOM["sinks"], "metadata": "bf16",
             "bytes_per_step": step_bytes(wl["batch"], wl["ctx"]),
             "dequant": {"per_op": "per-op rounded (reference streamed path)",
@@ -370,6 +395,48 @@ def append_microbench(device: torch.device, steps: int, warmup: int) -> dict:
     out["bulk"] = out["v2_mixed"]["bulk"]
     out["bytes"] = {"read": read, "written": out["v2_mixed"]["bytes_written"]}
     return out
+
+
+def other_geometry_decode(device: torch.device, steps: int, peak: float) -> list:
+    """Decode steps of the general tensor-core kernel on config 3's shape (batch 32, context 8192, same data) with
+    other code widths and group sizes, and the fp32 flavour of the headline geometry: what a cache off the 2-bit
+    headline geometry gets."""
+
+    import dartkv_b200 as dart
+    from dartkv_b200 import _lib
+
+    saved = dict(GEOM)
+    results = []
+    variants = [("4-bit keys and values", dict(bits=4, promote_ratio=0.0), _lib.DEQUANT_PER_OP),
+                ("2+2-bit keys, 4-bit values", dict(bits=4), _lib.DEQUANT_PER_OP),
+                ("8-bit keys and values", dict(bits=8, promote_ratio=0.0), _lib.DEQUANT_PER_OP),
+                ("headline widths, value groups of 32", dict(value_group=32), _lib.DEQUANT_PER_OP),
+                ("headline geometry, fp32 flavour", dict(), _lib.DEQUANT_FP32)]
+    start_evt, stop_evt = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    try:
+        for name, change, flavour in variants:
+            GEOM.update(saved)
+            GEOM.update(change)
+            cache, query = build_device_cache(range(32), 8192, WORKLOADS["config3"]["seed"], device)
+            q3 = query[:, :, 0].contiguous()
+            out = torch.empty_like(q3)
+            for _ in range(3):
+                dart.decode_attention(q3, cache, out=out, flavour=flavour)
+            torch.cuda.synchronize(device)
+            start_evt.record()
+            for _ in range(steps):
+                dart.decode_attention(q3, cache, out=out, flavour=flavour)
+            stop_evt.record()
+            torch.cuda.synchronize(device)
+            us = start_evt.elapsed_time(stop_evt) / steps * 1e3
+            nbytes = step_bytes(32, 8192)
+            results.append({"geometry": name, "us_per_step": us, "bytes_per_step": nbytes, "value": nbytes / us / 1e3,
+                            "unit": "GB/s", "frac": nbytes / us / 1e3 / peak, "decode_status": cache.decode_status()})
+            del cache
+            torch.cuda.empty_cache()
+    finally:
+        GEOM.update(saved)
+    return results
 
 
 def reference_gpu_decode(wl, device: torch.device, steps: int) -> dict:
@@ -538,6 +605,8 @@ def gpu_arm(args, wl) -> None:
     # DRAM traffic of one decode launch from the ncu capture of config 3; it grows with the pages processed, so
     # other workloads scale it by their algorithmic bytes
     traffic = int(round(local_bytes * (NCU_CONFIG3["dram_read"] + NCU_CONFIG3["dram_write"]) / NCU_CONFIG3["algorithmic"]))
+    if GEOM != HEADLINE or args.flavour != "per_op":
+        traffic = None   # the capture is of the headline geometry's per-op kernel
 
     # end to end through host buffers.  Every step copies its query from pinned host memory to the device, runs
     # the decode call (and the gather), and copies its output rows back to pinned host memory, all inside the timed
@@ -644,6 +713,8 @@ def gpu_arm(args, wl) -> None:
         torch.cuda.empty_cache()
         extra["reference_gpu"] = reference_gpu_decode(wl, device, args.steps)
         torch.cuda.empty_cache()
+        if GEOM == HEADLINE:
+            extra["other_geometries"] = other_geometry_decode(device, args.steps, peak)
         extra["append"] = append_microbench(device, steps=3, warmup=1)
         cpu = CpuDecode(wl["ctx"], wl["seed"], rows=1)
         step_s = cpu.time_steps(3, 1)
@@ -829,11 +900,21 @@ def main() -> None:
     parser.add_argument("--flavour", choices=("per_op", "fp32", "fused"), default="per_op",
                         help="dequantization arithmetic of the timed decode call (default: the pinned per-op rounding; "
                              "fp32 runs the general tensor-core kernel that also serves 4/8-bit pages)")
+    parser.add_argument("--bits", type=int, choices=(2, 4, 8), default=0, help="code width off the headline geometry")
+    parser.add_argument("--promote", type=float, default=None, help="promoted key channel ratio off the headline geometry")
+    parser.add_argument("--value-group", type=int, choices=(16, 32, 64, 128), default=0,
+                        help="value group size off the headline geometry")
     parser.add_argument("--gather", choices=("peer", "nccl"), default="peer",
                         help="multi-GPU output gather: peer stores from the decode kernels (default) or NCCL")
     parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (e.g. one rank's share)")
     parser.add_argument("--context", type=int, default=0, help="override the workload's context length")
     args = parser.parse_args()
+    if args.bits:
+        GEOM["bits"] = args.bits
+    if args.promote is not None:
+        GEOM["promote_ratio"] = args.promote
+    if args.value_group:
+        GEOM["value_group"] = args.value_group
     if args.workload == "config4":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "config4 needs the GPU model run; the CPU arm covers config5/config3"}))

@@ -111,8 +111,8 @@ struct Restore {
       nms_a = neg_a;
       nms_b = neg_b;
     } else {
-      s2 = (uint32_t)s * 0x00010001u;
-      z2 = (uint32_t)z * 0x00010001u;
+      s2 = prmt(s, s, 0x1010);   // both halves
+      z2 = prmt(z, z, 0x1010);
       nms_a = kFmaA ? H::mul(s2, neg_a) : neg_a;
       nms_b = kFmaB ? H::mul(s2, neg_b) : neg_b;
     }
@@ -157,8 +157,8 @@ __device__ __forceinline__ void restore_2bit(uint32_t w, const Restore2<DT, FP32
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const uint32_t x = prmt(lo, hi, byte_pair_selector(j));
-    out[2 * j] = r.template from_magic<false>(and_or(x, mask_a, m_a));
-    out[2 * j + 1] = r.template from_magic<true>(and_or(x, mask_b, m_b));
+    out[2 * j] = r.template from_magic<false>((x & mask_a) | m_a);
+    out[2 * j + 1] = r.template from_magic<true>((x & mask_b) | m_b);
   }
 }
 
@@ -171,11 +171,11 @@ __device__ __forceinline__ void restore_2plus2(uint32_t w, uint32_t high, const 
   for (int j = 0; j < 4; ++j) {
     const uint32_t x = prmt(w, t, byte_pair_selector(j));       // low plane at bits 0 and 4 of both halves
     const uint32_t y = prmt(hs, high, byte_pair_selector(j));   // high plane of the same elements at bits 2 and 6
-    out[2 * j] = r.template from_magic<false>(and_or(y, 0x000C000Cu, and_or(x, 0x00030003u, m0)));
+    out[2 * j] = r.template from_magic<false>((y & 0x000C000Cu) | ((x & 0x00030003u) | m0));
     if (DT == DARTKV_F16) {
-      out[2 * j + 1] = r.template from_magic<true>(and_or(y, 0x00C000C0u, and_or(x, 0x00300030u, m4)));
+      out[2 * j + 1] = r.template from_magic<true>((y & 0x00C000C0u) | ((x & 0x00300030u) | m4));
     } else {
-      out[2 * j + 1] = r.template from_magic<true>(and_or(y >> 4, 0x000C000Cu, and_or(x >> 4, 0x00030003u, m0)));
+      out[2 * j + 1] = r.template from_magic<true>(((y >> 4) & 0x000C000Cu) | (((x >> 4) & 0x00030003u) | m0));
     }
   }
 }
@@ -187,7 +187,7 @@ __device__ __forceinline__ void restore_4bit(uint32_t w, const Restore4<DT, FP32
   constexpr uint32_t mask = DT == DARTKV_F16 ? 0x00F000F0u : 0x000F000Fu;
   const uint32_t m = magic16<DT>(DT == DARTKV_F16 ? 4 : 0) * 0x00010001u;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) out[j] = r.template from_magic<false>(and_or(prmt(lo, hi, byte_pair_selector(j)), mask, m));
+  for (int j = 0; j < 4; ++j) out[j] = r.template from_magic<false>((prmt(lo, hi, byte_pair_selector(j)) & mask) | m);
 }
 
 // Four 8-bit codes of a word -> 2 registers of adjacent elements.
@@ -220,18 +220,18 @@ __device__ __forceinline__ void keys_to_tile(const uint8_t* st, const WideGeom& 
     const int ch = lane + 32 * r;
     const uint16_t sc = kscale[ch * w.key_groups + kg], zr = kzero[ch * w.key_groups + kg];
     uint32_t out[8];
-    if (KIND == 22) {
+    if constexpr (KIND == 22) {
       Restore22<DT, FP32> rs;
       rs.init(sc, zr);
       const uint32_t low = *reinterpret_cast<const uint32_t*>(st + ch * 4);
       const int slot = slot_of[ch];
       const uint32_t high = slot != 0xFF ? *reinterpret_cast<const uint32_t*>(st + w.k_high + slot * 4) : 0u;
       restore_2plus2<DT, FP32>(low, high, rs, out);
-    } else if (KIND == 2) {
+    } else if constexpr (KIND == 2) {
       Restore2<DT, FP32> rs;
       rs.init(sc, zr);
       restore_2bit<DT, FP32>(*reinterpret_cast<const uint32_t*>(st + ch * 4), rs, out);
-    } else if (KIND == 4) {
+    } else if constexpr (KIND == 4) {
       Restore4<DT, FP32> rs;
       rs.init(sc, zr);
       const uint2 words = *reinterpret_cast<const uint2*>(st + ch * 8);
@@ -254,14 +254,23 @@ __device__ __forceinline__ void keys_to_tile(const uint8_t* st, const WideGeom& 
 
 // Values of a staged chunk -> tile[16 tokens][128 channels] (rows of kValueRow bytes).  A lane takes 64 channels
 // of one token: 16 * BITS / 2 bytes, i.e. BITS / 2 pieces of 16 bytes.
+template <int DT, bool FP32, int BITS> struct ValueRestore;
+template <int DT, bool FP32> struct ValueRestore<DT, FP32, 2> { using type = Restore2<DT, FP32>; };
+template <int DT, bool FP32> struct ValueRestore<DT, FP32, 4> { using type = Restore4<DT, FP32>; };
+template <int DT, bool FP32> struct ValueRestore<DT, FP32, 8> { using type = Restore8<DT, FP32>; };
+
 template <int DT, bool FP32, int BITS>
 __device__ __forceinline__ void values_to_tile(const uint8_t* st, const WideGeom& w, uint8_t* tile, int lane, int vrb,
-                                               int vgroups, int value_group) {
+                                               int vgroups, int group_shift) {
   const int tok = lane & 15, half = lane >> 4;
   const uint8_t* codes = st + w.v_codes + tok * vrb + half * (vrb >> 1);
   const uint16_t* meta = reinterpret_cast<const uint16_t*>(st + w.v_meta) + tok * 2 * vgroups;
   uint8_t* row = tile + tok * kValueRow + half * 128;
   constexpr int kPieces = BITS / 2, kChannelsPerWord = 32 / BITS;
+  typename ValueRestore<DT, FP32, BITS>::type rs;
+  // a 16-byte piece holds 64 / kPieces channels: one group, unless the groups are smaller than that (then every
+  // word, which never straddles groups of 16 channels or more, looks its group up)
+  const bool group_per_word = (64 / kPieces) >> group_shift;
 #pragma unroll
   for (int p = 0; p < kPieces; ++p) {
     const int q = (p + tok) & (kPieces - 1);   // lanes start at different pieces: fewer bank conflicts
@@ -270,25 +279,21 @@ __device__ __forceinline__ void values_to_tile(const uint8_t* st, const WideGeom
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int ch_local = (4 * q + k) * kChannelsPerWord;   // first channel of the word among this lane's 64
-      const int group = (64 * half + ch_local) / value_group;
-      const uint16_t sc = meta[group], zr = meta[vgroups + group];
+      if (k == 0 || group_per_word) {
+        const int group = (64 * half + ch_local) >> group_shift;
+        rs.init(meta[group], meta[vgroups + group]);
+      }
       uint8_t* dst = row + ch_local * 2;
-      if (BITS == 2) {
-        Restore2<DT, FP32> rs;
-        rs.init(sc, zr);
+      if constexpr (BITS == 2) {
         uint32_t out[8];
         restore_2bit<DT, FP32>(ws[k], rs, out);
         reinterpret_cast<uint4*>(dst)[0] = make_uint4(out[0], out[1], out[2], out[3]);
         reinterpret_cast<uint4*>(dst)[1] = make_uint4(out[4], out[5], out[6], out[7]);
-      } else if (BITS == 4) {
-        Restore4<DT, FP32> rs;
-        rs.init(sc, zr);
+      } else if constexpr (BITS == 4) {
         uint32_t out[4];
         restore_4bit<DT, FP32>(ws[k], rs, out);
         *reinterpret_cast<uint4*>(dst) = make_uint4(out[0], out[1], out[2], out[3]);
       } else {
-        Restore8<DT, FP32> rs;
-        rs.init(sc, zr);
         uint32_t out[2];
         restore_8bit<DT, FP32>(ws[k], rs, out);
         *reinterpret_cast<uint2*>(dst) = make_uint2(out[0], out[1]);
@@ -329,6 +334,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
   const int total_pages = fast_end > d.sink_tokens ? (fast_end - d.sink_tokens) / 128 : 0;
   const float scale2 = a.scale * kLog2e;
   const int vrb = d.value_row_bytes, vgroups = d.value_groups, vbits = d.value_bits;
+  const int vg_shift = 31 - __clz(d.value_group), kg_shift = 31 - __clz(d.key_group);   // group sizes are powers of two
   const int key_row_bytes = w.key_kind == 22 ? 32 : 16 * w.key_kind;
   const int promoted = w.key_kind == 22 ? d.promoted : 0;
 
@@ -404,7 +410,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
       __syncwarp();
       const uint8_t* st = stage_mem + (idx & 1) * w.stage_bytes;
       const int pg = pg0 + 4 * (idx >> 2), t0 = 64 * hf + 16 * (idx & 3);
-      const int kg = t0 / d.key_group;
+      const int kg = t0 >> kg_shift;
 
       // ---- keys of the chunk -> tile[channel][16 tokens]
       if (promoted) {
@@ -441,9 +447,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
 
       // ---- values of the chunk -> tile[16 tokens][128 channels]
       switch (vbits) {
-        case 2: values_to_tile<DT, FP32, 2>(st, w, tile, lane, vrb, vgroups, d.value_group); break;
-        case 4: values_to_tile<DT, FP32, 4>(st, w, tile, lane, vrb, vgroups, d.value_group); break;
-        default: values_to_tile<DT, FP32, 8>(st, w, tile, lane, vrb, vgroups, d.value_group); break;
+        case 2: values_to_tile<DT, FP32, 2>(st, w, tile, lane, vrb, vgroups, vg_shift); break;
+        case 4: values_to_tile<DT, FP32, 4>(st, w, tile, lane, vrb, vgroups, vg_shift); break;
+        default: values_to_tile<DT, FP32, 8>(st, w, tile, lane, vrb, vgroups, vg_shift); break;
       }
       __syncwarp();
       issue(idx + 2);   // the stage has been read by every lane

@@ -67,7 +67,7 @@ def outlier_channels(seed: int, kv_heads: int, head_dim: int, fraction: float = 
 
 
 def build_headline_cache(rows, ctx: int, seed: int, device: torch.device, *, heads=None, keep_rows=None,
-                         metadata_dtype: torch.dtype = torch.bfloat16):
+                         metadata_dtype: torch.dtype = torch.bfloat16, cache_overrides=None):
     """Fill a ``DartKVCache`` on ``device`` with ``ctx`` tokens of bf16 K/V for the global batch rows ``rows``.
 
     Every batch row has its own device generator, seeded from the workload seed and the row's global index, so
@@ -75,6 +75,8 @@ def build_headline_cache(rows, ctx: int, seed: int, device: torch.device, *, hea
     carries the 32 sink tokens, the rest arrive 1024 tokens at a time.  ``heads = (first, end)`` keeps only those
     KV heads of every row (and the query heads that attend to them).  Returns ``(cache, query [B,Hq,1,D])`` and,
     when ``keep_rows`` lists global rows, also their K and V ``[len(keep_rows), H, ctx, D]`` as generated.
+    ``cache_overrides`` replaces fields of the cache configuration (code width, promotion ratio, group sizes) for
+    runs of the same data off the headline geometry.
     """
 
     from .cache import DartKVCache, DartKVCacheConfig
@@ -84,7 +86,9 @@ def build_headline_cache(rows, ctx: int, seed: int, device: torch.device, *, hea
     h0, h1 = heads if heads is not None else (0, g["kv_heads"])
     rep = g["query_heads"] // g["kv_heads"]
     keep = [rows.index(r) for r in keep_rows] if keep_rows is not None else []
-    cache = DartKVCache(DartKVCacheConfig(metadata_dtype=metadata_dtype, **headline_cache_kwargs()), max_tokens=ctx + 256)
+    config = headline_cache_kwargs()
+    config.update(cache_overrides or {})
+    cache = DartKVCache(DartKVCacheConfig(metadata_dtype=metadata_dtype, **config), max_tokens=ctx + 256)
     gens = [torch.Generator(device=device).manual_seed(seed * 1000003 + 17 * row) for row in rows]
     mult = torch.ones(g["kv_heads"], g["head_dim"], device=device)
     mult.scatter_(1, outlier_channels(seed, g["kv_heads"], g["head_dim"]).to(device), 10.0)
