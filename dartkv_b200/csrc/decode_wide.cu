@@ -157,8 +157,8 @@ __device__ __forceinline__ void restore_2bit(uint32_t w, const Restore2<DT, FP32
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const uint32_t x = prmt(lo, hi, byte_pair_selector(j));
-    out[2 * j] = r.template from_magic<false>((x & mask_a) | m_a);
-    out[2 * j + 1] = r.template from_magic<true>((x & mask_b) | m_b);
+    out[2 * j] = r.template from_magic<false>(and_or(x, mask_a, m_a));
+    out[2 * j + 1] = r.template from_magic<true>(and_or(x, mask_b, m_b));
   }
 }
 
@@ -171,11 +171,11 @@ __device__ __forceinline__ void restore_2plus2(uint32_t w, uint32_t high, const 
   for (int j = 0; j < 4; ++j) {
     const uint32_t x = prmt(w, t, byte_pair_selector(j));       // low plane at bits 0 and 4 of both halves
     const uint32_t y = prmt(hs, high, byte_pair_selector(j));   // high plane of the same elements at bits 2 and 6
-    out[2 * j] = r.template from_magic<false>((y & 0x000C000Cu) | ((x & 0x00030003u) | m0));
+    out[2 * j] = r.template from_magic<false>(and_or(y, 0x000C000Cu, and_or(x, 0x00030003u, m0)));
     if (DT == DARTKV_F16) {
-      out[2 * j + 1] = r.template from_magic<true>((y & 0x00C000C0u) | ((x & 0x00300030u) | m4));
+      out[2 * j + 1] = r.template from_magic<true>(and_or(y, 0x00C000C0u, and_or(x, 0x00300030u, m4)));
     } else {
-      out[2 * j + 1] = r.template from_magic<true>(((y >> 4) & 0x000C000Cu) | (((x >> 4) & 0x00030003u) | m0));
+      out[2 * j + 1] = r.template from_magic<true>(and_or(y >> 4, 0x000C000Cu, and_or(x >> 4, 0x00030003u, m0)));
     }
   }
 }
@@ -187,7 +187,7 @@ __device__ __forceinline__ void restore_4bit(uint32_t w, const Restore4<DT, FP32
   constexpr uint32_t mask = DT == DARTKV_F16 ? 0x00F000F0u : 0x000F000Fu;
   const uint32_t m = magic16<DT>(DT == DARTKV_F16 ? 4 : 0) * 0x00010001u;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) out[j] = r.template from_magic<false>((prmt(lo, hi, byte_pair_selector(j)) & mask) | m);
+  for (int j = 0; j < 4; ++j) out[j] = r.template from_magic<false>(and_or(prmt(lo, hi, byte_pair_selector(j)), mask, m));
 }
 
 // Four 8-bit codes of a word -> 2 registers of adjacent elements.
