@@ -61,7 +61,7 @@ class DecodePlanInfo(Structure):
 
     _fields_ = [
         ("kernel", c_int32), ("quads", c_int32), ("stream_blocks", c_int32), ("total_splits", c_int32),
-        ("units", c_int64), ("generic_splits", c_int32), ("generic_chunk", c_int32), ("dense_units", c_int32),
+        ("units", c_int64), ("generic_splits", c_int32), ("generic_chunk", c_int32),
     ]
 
 

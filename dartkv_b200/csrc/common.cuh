@@ -115,42 +115,4 @@ __host__ __device__ __forceinline__ int dartkv_block_of_unit(int64_t x, int bloc
   return (int)j;
 }
 
-// system-scope flag accesses of the peer delivery (plain stores and loads over NVLink, no multicast)
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// Arguments of the tensor-core decode kernels.
-// Work split: one unit = four consecutive pages of one (batch, kv head) (one page per warp pair).  A row has
-// `quads` units: its `page_quads` four-page units followed by `quads - page_quads` units that stand for its dense
-// tokens (sink prefix, unpacked tail, tokens packed on one side only); the block whose share holds unit
-// `page_quads` of a row also processes those tokens.  The units of all rows are dealt out evenly to `stream_blocks`
-// blocks, so a block may finish one row and start the next.  Partial slot 0 of a row belongs to its dense tokens,
-// slot 1 + k to the k-th block that touches the row.  The last block to deliver its partials of a row (counted in
-// `arrivals`, which it leaves at zero) combines them, normalizes, casts and stores the row's outputs, also into the
-// peers' gathered tensors when there are peers.
-struct dartkv_fast_args {
-  const void* q;
-  int query_heads;
-  float scale;
-  int flavour;
-  int quads, page_quads, stream_blocks;
-  long long units;
-  int total_splits;
-  float* part_m;
-  float* part_l;
-  float* part_acc;
-  int* status;
-  const int32_t* row_start;   // optional [batch] first live token of every batch row (left padding)
-  int* arrivals;              // [batch * kv_heads]
-  void* out;                  // [batch, query_heads, head_dim] in the query dtype
-  unsigned int* done_counter; // rows finished (peer delivery)
-  dartkv_peer_scatter peers;  // world_size <= 1: no peers
-};
-
 static inline int dartkv_gcd(int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; }

@@ -243,6 +243,14 @@ __global__ void __launch_bounds__(GEN_THREADS) decode_generic_kernel(dartkv_cach
 // stores through peer-mapped pointers over NVLink), and the block that finishes last publishes this rank's arrival
 // flag on every peer and then waits, with a bound, for every peer's flag on this rank: when the kernel ends, the
 // gathered tensor of this rank is complete.  Nothing here waits on another kernel of the same GPU.
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 __global__ void decode_merge_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
                                     const float* __restrict__ part_acc, int total_splits, int D, void* out, int out_dt,
@@ -310,19 +318,28 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_m, const floa
 struct DecodeLayout {
   int generic_splits, generic_chunk;   // generic kernel over the whole range (fallback)
   int fast;                            // tensor-core kernel for the packed pages: 1 per-op rounded, 2 unrounded fp32
-  int quads, stream_blocks;            // tensor-core layouts: units per (batch, kv head), stream blocks
-  int page_quads;                      // the four-page units among them (the rest stand for the row's dense tokens)
+  int quads, stream_blocks;            // tensor-core layouts: four-page units per (batch, kv head), stream blocks
   long long units;
   int total_splits;
 };
 
 int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
-int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const dartkv_fast_args* args, cudaStream_t stream);
+int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
+                              int flavour, int quads, int stream_blocks, long long units, int total_splits,
+                              float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
+                              cudaStream_t stream);
 int dartkv_decode_fused32_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
-int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const dartkv_fast_args* args, cudaStream_t stream);
+int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
+                                 int flavour, int quads, int stream_blocks, long long units, int total_splits,
+                                 float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
+                              cudaStream_t stream);
+
 int dartkv_decode_wide_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads);
 int dartkv_decode_wide_blocks_per_sm(const dartkv_cache_desc* d);
-int dartkv_decode_wide_launch(const dartkv_cache_desc* d, const dartkv_fast_args* args, cudaStream_t stream);
+int dartkv_decode_wide_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
+                              int flavour, int quads, int stream_blocks, long long units, int total_splits,
+                              float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
+                              cudaStream_t stream);
 
 static int dartkv_sm_count() {
   // per device: a process may drive GPUs of different sizes
@@ -364,25 +381,22 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
   // every other packed geometry with 128-token pages and head_dim 128, and the fp32 flavour of all of them
   if (!L.fast && flavour != DARTKV_DEQUANT_FUSED && dartkv_decode_wide_supported(d, q_dtype, query_heads)) L.fast = 3;
   // the tensor-core kernels index (row, four-page unit) pairs with 32 bits
-  if (L.fast && (long long)bh * ((max(1, (tokens - d->sink_tokens) / d->page_size) + 3) / 4 + 4) >= (1ll << 31)) L.fast = 0;
+  if (L.fast && (long long)bh * ((max(1, (tokens - d->sink_tokens) / d->page_size) + 3) / 4) >= (1ll << 31)) L.fast = 0;
   if (L.fast) {
-    // One unit = four consecutive pages of a (batch, kv head) (a block hands them to its four warp pairs); a row's
-    // dense tokens (sink prefix, unpacked tail, tokens packed on one side only) count as one unit per 128 of them
-    // after its page units, and the block whose share holds the first of these processes them.  The units of all
-    // rows are dealt out evenly to `stream_blocks` blocks.  Two families of splits are compared with a cost model
-    // in units of one page per pair (a block costs its units plus 1.75 per row it touches: query load, first-page
-    // latency, merge of its eight warps; blocks run in waves of two per SM; constants fitted to B200 timings):
+    // One unit = four consecutive pages of a (batch, kv head) (a block hands them to its four warp pairs).  The
+    // units of all rows are dealt out evenly to `stream_blocks` blocks.  Two families of splits are compared with a
+    // cost model in units of one page per pair (a block costs its pages per pair plus 1.75 per row it touches:
+    // query load, first-page latency, merge of its eight warps; the dense block of a row about 2; blocks run in
+    // waves of two per SM; constants fitted to B200 timings):
     //   aligned    rows * s blocks, s = 1..16 pieces per row;
     //   unaligned  one block per resident slot, a block may finish one row and start the next (at most 16 blocks
     //              touch a row); measured ~3 % slower per unit than aligned blocks, but it fills every slot when
     //              the rows do not (e.g. 256 rows on 296 slots: 9 % faster at context 32768).
     const int pages = max(1, (tokens - d->sink_tokens) / d->page_size);
-    const int dense_tokens = tokens - (tokens > d->sink_tokens ? (tokens - d->sink_tokens) / d->page_size * d->page_size : 0);
-    L.page_quads = (pages + 3) / 4;
-    L.quads = L.page_quads + min(4, max(1, (dense_tokens + 127) / 128));
+    L.quads = (pages + 3) / 4;
     L.units = (long long)bh * L.quads;
     const int resident = (L.fast == 3 ? dartkv_decode_wide_blocks_per_sm(d) : 2) * dartkv_sm_count();
-    const double block_fixed = 1.75;
+    const double block_fixed = 1.75, dense_cost = 2.0;
     int best_pieces = 1;
     double best_cost = 1e30;
     for (int q = max(1, (L.quads + 15) / 16); q <= L.quads; ++q) {
@@ -390,7 +404,7 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
       const long long blocks = (long long)bh * pieces;
       const long long waves = (blocks + resident - 1) / resident;
       const double by_waves = (double)waves * (q + block_fixed);
-      const double by_work = (double)bh * (pieces * (q + block_fixed)) / resident;
+      const double by_work = (double)bh * (pieces * (q + block_fixed) + dense_cost) / resident;
       const double cost = by_waves > by_work ? by_waves : by_work;
       if (cost < best_cost - 1e-9) { best_cost = cost; best_pieces = pieces; }
     }
@@ -411,7 +425,7 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
       }
       if (blocks >= 1 && !force_aligned) {
         const double share = (double)L.units / blocks;
-        const double cost = 1.03 * (share + block_fixed * (share / L.quads + 1.0));
+        const double cost = 1.03 * (share + block_fixed * (share / L.quads + 1.0)) + (double)bh * dense_cost / resident;
         if (cost < best_cost || force_unaligned) {
           const long long w = L.units / blocks;   // smallest share of a block
           L.stream_blocks = (int)blocks;
@@ -431,15 +445,9 @@ static DecodeLayout decode_layout(const dartkv_cache_desc* d, int q_dtype, int q
   return L;
 }
 
-// Workspace: status word, finished-row counter (peer delivery), 8 spare bytes; one arrival counter per (batch, kv
-// head) (zero between calls); the split partials m, l, acc.  The counters sit at a fixed place for a given cache,
-// whatever kernel or split a call uses, so that no call's partials ever land on them.
-static int64_t partials_offset(const dartkv_cache_desc* d) {
-  return 16 + ((int64_t)d->batch * d->kv_heads * 4 + 15) / 16 * 16;
-}
 static int64_t layout_bytes(const dartkv_cache_desc* d, int query_heads, const DecodeLayout& L) {
   int64_t rows = (int64_t)d->batch * query_heads * L.total_splits;
-  return partials_offset(d) + rows * (2 + d->head_dim) * (int64_t)sizeof(float);
+  return 16 + rows * (2 + d->head_dim) * (int64_t)sizeof(float);
 }
 
 extern "C" int64_t dartkv_decode_workspace_bytes(const dartkv_cache_desc* d, int query_heads, int max_tokens) {
@@ -475,7 +483,6 @@ extern "C" int dartkv_decode_plan(const dartkv_cache_desc* d, int q_dtype, int q
   const DecodeLayout L = decode_layout(d, q_dtype, query_heads, flavour, tokens);
   out->kernel = L.fast;
   out->quads = L.fast ? L.quads : 0;
-  out->dense_units = L.fast ? L.quads - L.page_quads : 0;
   out->stream_blocks = L.fast ? L.stream_blocks : 0;
   out->total_splits = L.total_splits;
   out->units = L.fast ? L.units : 0;
@@ -510,24 +517,16 @@ static int decode_attention_impl(const dartkv_cache_desc* d, const void* query, 
   DARTKV_REQUIRE(workspace_bytes >= layout_bytes(d, query_heads, L), "decode workspace too small: need %lld bytes",
                  (long long)layout_bytes(d, query_heads, L));
   int* status = reinterpret_cast<int*>(workspace);
-  int* arrivals = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + 16);
-  unsigned int* done_counter = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(workspace) + 4);
-  float* part_m = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + partials_offset(d));
+  float* part_m = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 16);
   float* part_l = part_m + rows;
   float* part_acc = part_l + rows;
   const int bh = d->batch * d->kv_heads;
   const int D = d->head_dim;
   if (L.fast) {
-    // the tensor-core kernels finish their rows themselves (the last block of a row merges its partials)
-    dartkv_fast_args args{};
-    args.q = query; args.query_heads = query_heads; args.scale = scale; args.flavour = flavour;
-    args.quads = L.quads; args.page_quads = L.page_quads; args.stream_blocks = L.stream_blocks; args.units = L.units;
-    args.total_splits = L.total_splits; args.part_m = part_m; args.part_l = part_l; args.part_acc = part_acc;
-    args.status = status; args.row_start = row_start; args.arrivals = arrivals; args.out = out;
-    args.done_counter = done_counter;
-    if (peers) args.peers = *peers;
-    return (L.fast == 3 ? dartkv_decode_wide_launch : L.fast == 2 ? dartkv_decode_fused32_launch : dartkv_decode_fast_launch)(
-        d, &args, stream);
+    int rc = (L.fast == 3 ? dartkv_decode_wide_launch : L.fast == 2 ? dartkv_decode_fused32_launch : dartkv_decode_fast_launch)(
+        d, query, q_dtype, query_heads, scale, flavour, L.quads, L.stream_blocks, L.units, L.total_splits, part_m,
+        part_l, part_acc, status, row_start, stream);
+    if (rc) return rc;
   } else {
     size_t smem = ((size_t)rep * D + (size_t)GEN_TILE * (D + 1) + (size_t)rep * GEN_TILE + 3 * rep) * sizeof(float) +
                   (size_t)D * sizeof(int);
@@ -553,9 +552,10 @@ static int decode_attention_impl(const dartkv_cache_desc* d, const void* query, 
     config.attrs = &attribute;
     config.numAttrs = 1;
     dartkv_peer_scatter none{};
+    unsigned int* done_counter = reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(workspace) + 4);
     DARTKV_CUDA_OK(cudaLaunchKernelEx(&config, decode_merge_kernel, (const float*)part_m, (const float*)part_l,
                                       (const float*)part_acc, L.total_splits, D, out, q_dtype,
-                                      0, (int64_t)0, 0, query_heads, d->kv_heads,
+                                      L.fast ? L.stream_blocks : 0, (int64_t)L.units, L.quads, query_heads, d->kv_heads,
                                       peers ? *peers : none, status, done_counter));
   }
   DARTKV_LAUNCH_OK("decode_merge_kernel");

@@ -23,7 +23,25 @@ __device__ __forceinline__ void pair_barrier(int pair) {
   asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
 }
 
-using FastArgs = dartkv_fast_args;
+struct FastArgs {
+  const void* q;
+  int query_heads;
+  float scale;
+  int flavour;
+  // Work split: one unit = four consecutive pages of one (batch, kv head) (one page per warp pair); the units of
+  // all (batch, kv head) rows, `quads` each, are dealt out evenly to `stream_blocks` blocks, so a block may finish
+  // one row and start the next.  Partial slot 0 of a row belongs to its dense-token block, slot 1 + k to the
+  // k-th stream block that touches the row.
+  int quads, stream_blocks;
+  long long units;
+  int total_splits;
+  float* part_m;
+  float* part_l;
+  float* part_acc;
+  int* status;
+  // optional [batch] first live token of every batch row (left padding): tokens before it get no weight
+  const int32_t* row_start;
+};
 
 __host__ __device__ __forceinline__ int fast_range_end(int sink_tokens, int page_size, int k_end, int v_end,
                                                        int sink_filled) {
@@ -320,84 +338,6 @@ __device__ __forceinline__ void block_merge(const FastArgs& a, const BS& bs, con
     }
     a.part_acc[row * 128 + ch] = acc;
   }
-}
-
-// Called by every thread of a block once the block's partials of row (b, hkv) are stored.  The row's blocks count
-// themselves in; the one that arrives last reads all partial slots of the row's query heads (slot 0: dense tokens,
-// slots 1..: the stream blocks), combines them, normalizes, casts and stores the outputs, and, with peers, stores
-// the rows into every rank's gathered tensor too (plain stores through peer-mapped pointers).  The block that
-// finishes the last row of the launch then publishes this rank's arrival flag on every peer and waits, with a bound,
-// for every peer's flag on this rank; nothing here waits on another block or kernel of the same GPU.
-// BS needs `int finish[2]`.
-template <class BS>
-__device__ __forceinline__ void finish_row(const dartkv_cache_desc& d, const FastArgs& a, BS& bs, int b, int hkv, int rep) {
-  const int tid = threadIdx.x;
-  const int bh = b * d.kv_heads + hkv;
-  __threadfence();   // this thread's partial stores are visible device-wide before the block counts itself in
-  __syncthreads();
-  if (tid == 0) {
-    const int blocks = 1 + dartkv_block_of_unit((int64_t)bh * a.quads + a.quads - 1, a.stream_blocks, a.units) -
-                       dartkv_block_of_unit((int64_t)bh * a.quads, a.stream_blocks, a.units);
-    const int arrived = atomicAdd(&a.arrivals[bh], 1) + 1;
-    bs.finish[0] = arrived == blocks;
-    bs.finish[1] = blocks + 1;              // valid partial slots of the row
-    if (arrived == blocks) a.arrivals[bh] = 0;   // ready for the next call on this stream
-  }
-  __syncthreads();
-  if (!bs.finish[0]) return;
-  __threadfence();   // the other blocks' partials are read after their arrivals were seen
-  const int splits = bs.finish[1];
-  const int ch = tid & 127;
-  const bool gathered = a.peers.world_size >= 1, peers = a.peers.world_size > 1;
-  for (int r = tid >> 7; r < rep; r += kThreads / 128) {
-    const int head = hkv * rep + r;
-    const int64_t row = ((int64_t)b * a.query_heads + head) * a.total_splits;
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, __ldcg(a.part_m + row + s));
-    float l = 0.0f, acc = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = __ldcg(a.part_m + row + s);
-      if (ms != -INFINITY) {
-        const float wgt = expf(ms - m);
-        l += __ldcg(a.part_l + row + s) * wgt;
-        acc += __ldcg(a.part_acc + (row + s) * 128 + ch) * wgt;
-      }
-    }
-    const float value = acc * (1.0f / fmaxf(l, 1e-20f));
-    store_f(a.out, d.dtype, ((int64_t)b * a.query_heads + head) * 128 + ch, value);
-    if (gathered) {
-      const int64_t peer_row = (int64_t)(a.peers.dst_row_begin + b) * a.peers.dst_heads_total + a.peers.dst_head_begin + head;
-      for (int p = 0; p < a.peers.world_size; ++p) store_f(a.peers.out[p], d.dtype, peer_row * 128 + ch, value);
-    }
-  }
-  if (peers) {
-    __threadfence_system();   // this thread's peer stores are visible system-wide before the row is reported
-    __syncthreads();
-    if (tid == 0) {
-      const unsigned int ticket = atomicAdd(a.done_counter, 1u);
-      if (ticket == (unsigned int)(d.batch * d.kv_heads) - 1u) {
-        *a.done_counter = 0;    // ready for the next call on this stream
-        __threadfence_system();
-        for (int p = 0; p < a.peers.world_size; ++p) st_release_sys(a.peers.flags[p] + a.peers.rank, a.peers.epoch);
-        // every peer's rows have landed here once its flag shows this step (or a later one)
-        bool ok = true;
-        for (int p = 0; p < a.peers.world_size && ok; ++p) {
-          ok = false;
-          for (int spin = 0; spin < (1 << 21); ++spin) {   // about half a second with the sleep below
-            if ((int)(ld_acquire_sys(a.peers.flags[a.peers.rank] + p) - a.peers.epoch) >= 0) { ok = true; break; }
-            __nanosleep(200);
-          }
-        }
-        if (!ok) atomicExch(a.status, 2);
-      }
-    }
-  }
-  __syncthreads();
-}
-
-// Whether the share [quad_begin, quad_begin + quad_count) of a row holds the unit that stands for its dense tokens.
-__device__ __forceinline__ bool share_has_dense_unit(const FastArgs& a, int quad_begin, int quad_count) {
-  return quad_begin <= a.page_quads && a.page_quads < quad_begin + quad_count;
 }
 
 }  // namespace

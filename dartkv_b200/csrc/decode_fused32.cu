@@ -57,7 +57,6 @@ struct FusedBlockSmem {
   float merge_l[kWarps][4];
   int slot_map[128];
   float q_absmax;
-  int finish[2];
 };
 
 template <int DT>
@@ -303,6 +302,16 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
   const int g = lane >> 2, c = lane & 3;
   const int rep = a.query_heads / d.kv_heads;
 
+  if ((int)blockIdx.x >= a.stream_blocks) {
+    // dense tokens of one (batch, kv head): partial slot 0.  These short blocks come last in launch order and fill
+    // the slots the stream blocks leave.
+    const int bh = blockIdx.x - a.stream_blocks;
+    dense_block<DT>(d, a, bs, warp_out, bh);
+    __syncthreads();
+    block_merge(a, bs, warp_out, bh / d.kv_heads, bh % d.kv_heads, rep, 0);
+    return;
+  }
+
   // ---- stream block: an even share of all (row, four-page unit) work, possibly spanning several rows
   const int sb = blockIdx.x;
   int unit = (int)((int64_t)sb * a.units / a.stream_blocks);   // the host keeps the unit count below 2^31
@@ -488,15 +497,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
     __syncthreads();
     block_merge(a, bs, warp_out, bh / d.kv_heads, bh % d.kv_heads, rep,
                 1 + sb - dartkv_block_of_unit((int64_t)bh * a.quads, a.stream_blocks, a.units));
-    __syncthreads();
-    if (share_has_dense_unit(a, quad_begin, quad_count)) {
-      // the row's dense tokens (sink prefix, unpacked tail, tokens packed on one side only): partial slot 0
-      dense_block<DT>(d, a, bs, warp_out, bh);
-      __syncthreads();
-      block_merge(a, bs, warp_out, bh / d.kv_heads, bh % d.kv_heads, rep, 0);
-    }
-    finish_row(d, a, bs, bh / d.kv_heads, bh % d.kv_heads, rep);   // ends with a block barrier: the merge buffer is
-                                                                    // staging memory again, the query table may be overwritten
+    __syncthreads();   // the merge buffer is staging memory again, the query table may be overwritten
   }
   if (!ok && lane == 0) atomicExch(a.status, 1);
 }
@@ -536,10 +537,14 @@ static FusedKernel fused_variant(int dtype, int value_groups, int kp) {
   return value_groups == 2 ? fused_variant_kp<DARTKV_F16, 2>(kp) : fused_variant_kp<DARTKV_F16, 1>(kp);
 }
 
-int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const dartkv_fast_args* args, cudaStream_t stream) {
-  const FastArgs& a = *args;
-  const int stream_blocks = a.stream_blocks;
-  dim3 grid(stream_blocks);
+int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
+                                 int flavour, int quads, int stream_blocks, long long units, int total_splits,
+                                 float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
+                                 cudaStream_t stream) {
+  (void)q_dtype;
+  FastArgs a{query, query_heads, scale, flavour, quads, stream_blocks, units, total_splits, part_m, part_l, part_acc, status,
+             row_start};
+  dim3 grid(stream_blocks + d->batch * d->kv_heads);
   {
     // the shared-memory opt-in is per device and per kernel: ask once per device (the flags are atomic; two threads
     // that race on a device's first call both set the attribute, which is harmless)

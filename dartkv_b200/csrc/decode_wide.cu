@@ -44,7 +44,6 @@ struct WideBlockSmem {
   float merge_m[kWarps][4];
   float merge_l[kWarps][4];
   int slot_map[128];
-  int finish[2];
 };
 
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
@@ -314,6 +313,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
   const int g = lane >> 2, c = lane & 3;
   const int rep = a.query_heads / d.kv_heads;
 
+  if ((int)blockIdx.x >= a.stream_blocks) {
+    const int bh = blockIdx.x - a.stream_blocks;
+    dense_block<DT>(d, a, bs, warp_out, bh);
+    __syncthreads();
+    block_merge(a, bs, warp_out, bh / d.kv_heads, bh % d.kv_heads, rep, 0);
+    return;
+  }
+
   const int sb = blockIdx.x;
   int unit = (int)((int64_t)sb * a.units / a.stream_blocks);
   const int unit_end = (int)((int64_t)(sb + 1) * a.units / a.stream_blocks);
@@ -511,14 +518,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
     __syncthreads();
     block_merge(a, bs, warp_out, b, hkv, rep,
                 1 + sb - dartkv_block_of_unit((int64_t)bh * a.quads, a.stream_blocks, a.units));
-    __syncthreads();
-    if (share_has_dense_unit(a, quad_begin, quad_count)) {
-      // the row's dense tokens (sink prefix, unpacked tail, tokens packed on one side only): partial slot 0
-      dense_block<DT>(d, a, bs, warp_out, bh);
-      __syncthreads();
-      block_merge(a, bs, warp_out, b, hkv, rep, 0);
-    }
-    finish_row(d, a, bs, b, hkv, rep);   // ends with a block barrier: the merge buffer is streaming memory again
+    __syncthreads();   // the merge buffer is streaming memory again
   }
 }
 
@@ -582,12 +582,16 @@ int dartkv_decode_wide_blocks_per_sm(const dartkv_cache_desc* d) {
   return 2 * (wide_smem_bytes(wide_geometry(d)) + 1024) <= 228 * 1024 ? 2 : 1;
 }
 
-int dartkv_decode_wide_launch(const dartkv_cache_desc* d, const dartkv_fast_args* args, cudaStream_t stream) {
-  const FastArgs& a = *args;
-  const int stream_blocks = a.stream_blocks;
+int dartkv_decode_wide_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
+                              int flavour, int quads, int stream_blocks, long long units, int total_splits,
+                              float* part_m, float* part_l, float* part_acc, int* status, const int32_t* row_start,
+                              cudaStream_t stream) {
+  (void)q_dtype;
+  FastArgs a{query, query_heads, scale, flavour, quads, stream_blocks, units, total_splits, part_m, part_l, part_acc, status,
+             row_start};
   const WideGeom w = wide_geometry(d);
   const size_t smem = wide_smem_bytes(w);
-  dim3 grid(stream_blocks);
+  dim3 grid(stream_blocks + d->batch * d->kv_heads);
   {
     // the shared-memory opt-in is per device and per kernel: ask once per device
     static std::atomic<bool> ready[64];
@@ -600,7 +604,7 @@ int dartkv_decode_wide_launch(const dartkv_cache_desc* d, const dartkv_fast_args
       if (device >= 0 && device < 64) ready[device].store(true, std::memory_order_release);
     }
   }
-  wide_variant(d->dtype, a.flavour == DARTKV_DEQUANT_FP32)<<<grid, kThreads, smem, stream>>>(*d, a, w);
+  wide_variant(d->dtype, flavour == DARTKV_DEQUANT_FP32)<<<grid, kThreads, smem, stream>>>(*d, a, w);
   DARTKV_LAUNCH_OK("decode_wide_kernel");
   return DARTKV_OK;
 }

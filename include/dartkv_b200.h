@@ -205,11 +205,9 @@ int dartkv_decode_attention(const dartkv_cache_desc* desc, const void* query, in
 /* How dartkv_decode_attention would split a call; host arithmetic only, nothing is launched (no counterpart in
  * the reference: it exists so that integrators and tests can see the plan).  kernel: 0 generic, 1 tensor-core
  * per-op flavour (2-bit pages), 2 tensor-core unrounded flavour (2-bit pages), 3 tensor-core kernel for every
- * other packed geometry and the fp32 flavour.  On the tensor-core layouts a (batch, kv head) row has `quads` units:
- * one per four consecutive pages, then `dense_units` that stand for its dense tokens; block j of `stream_blocks` owns
- * units [j*units/stream_blocks, (j+1)*units/stream_blocks) and every row is touched by at most total_splits - 1 of
- * them (one more partial slot holds the dense tokens' share).  The block that delivers a row's last partial combines
- * them and writes the row's outputs: these kernels need no merge launch. */
+ * other packed geometry and the fp32 flavour.  On the tensor-core layouts one unit is four consecutive pages
+ * of a (batch, kv head) row; block j of `stream_blocks` owns units [j*units/stream_blocks, (j+1)*units/stream_blocks)
+ * and every row is touched by at most total_splits - 1 of them (plus its dense-token block). */
 typedef struct {
   int32_t kernel;
   int32_t quads;          /* units per row */
@@ -218,7 +216,6 @@ typedef struct {
   int64_t units;          /* rows * quads */
   int32_t generic_splits; /* generic kernel only */
   int32_t generic_chunk;
-  int32_t dense_units;    /* the last units of a row: they stand for its dense tokens (sinks, unpacked tail) */
 } dartkv_decode_plan_info;
 int dartkv_decode_plan(const dartkv_cache_desc* desc, int q_dtype, int query_heads, int flavour, int tokens,
                        dartkv_decode_plan_info* out);

@@ -55,9 +55,7 @@ def test_tensor_core_plans_stay_inside_their_partial_slots(flavour, split, decod
         assert info.kernel == (1 if flavour == _lib.DEQUANT_PER_OP else 2)
         rows = batch * heads
         pages = max(1, (tokens - 32) // 128)
-        dense = tokens - (max(0, tokens - 32) // 128) * 128        # sinks + unpacked tail
-        assert info.dense_units == min(4, max(1, -(-dense // 128)))
-        assert info.quads == (pages + 3) // 4 + info.dense_units
+        assert info.quads == (pages + 3) // 4
         assert info.units == rows * info.quads
         assert 1 <= info.stream_blocks <= info.units
         assert 2 <= info.total_splits <= 17
@@ -82,7 +80,7 @@ def test_other_geometries_take_the_general_tensor_core_kernel():
         for flavour in (_lib.DEQUANT_PER_OP, _lib.DEQUANT_FP32):
             info = plan(d, _lib.BF16, 8, flavour, 5000)
             assert info.kernel == 3 and info.stream_blocks >= 1 and info.generic_splits == 0
-            assert info.quads == (max(1, (5000 - 32) // 128) + 3) // 4 + info.dense_units and 2 <= info.total_splits <= 17
+            assert info.quads == (max(1, (5000 - 32) // 128) + 3) // 4 and 2 <= info.total_splits <= 17
         # the unrounded flavour of these geometries has no 16-bit tile to go through: CUDA-core kernel
         info = plan(d, _lib.BF16, 8, _lib.DEQUANT_FUSED, 5000)
         assert info.kernel == 0 and info.stream_blocks == 0 and info.generic_splits >= 1
