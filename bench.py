@@ -36,7 +36,7 @@ WORKLOADS = {
 }
 # DRAM bytes of ONE decode launch at config 3 measured with ncu (dram__bytes_read.sum / dram__bytes_write.sum of the
 # tensor-core decode kernel, per-op flavour) next to that launch's algorithmic bytes
-NCU_CONFIG3 = {"algorithmic": 192774144, "dram_read": 192.73e6, "dram_write": 4.11e6}
+NCU_CONFIG3 = {"algorithmic": 192774144, "dram_read": 192.75e6, "dram_write": 6.55e6}
 # the same numbers as dartkv_b200.synthetic.HEADLINE_GEOMETRY (kept here so that the CPU reference arm runs without
 # loading the package or its CUDA library; the GPU arm asserts that the two agree)
 GEOM = dict(query_heads=32, kv_heads=8, head_dim=128, page=128, key_group=128, value_group=64, sinks=32,
