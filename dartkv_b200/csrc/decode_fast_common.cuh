@@ -53,12 +53,14 @@ __host__ __device__ __forceinline__ int fast_range_end(int sink_tokens, int page
 template <int DT>
 __device__ __forceinline__ float rnd16(float x) { return Half2Ops<DT>::to_float(Half2Ops<DT>::from_float(x)); }
 
-// code * scale + zero the way the chosen flavour rounds it (metadata dtype = cache dtype DT on these kernels)
-template <int DT>
+// code * scale + zero the way the chosen flavour rounds it: per-op in the metadata dtype MD and then cast to the
+// cache dtype DT, or fp32 with one rounding to DT, or not rounded at all
+template <int DT, int MD>
 __device__ __forceinline__ float restore16(float code, float scale, float zero, int flavour) {
   if (flavour == DARTKV_DEQUANT_FUSED) return __fmaf_rn(code, scale, zero);
   if (flavour == DARTKV_DEQUANT_FP32) return rnd16<DT>(__fmaf_rn(code, scale, zero));
-  return rnd16<DT>(__fadd_rn(rnd16<DT>(__fmul_rn(code, scale)), zero));
+  const float md = rnd16<MD>(__fadd_rn(rnd16<MD>(__fmul_rn(code, scale)), zero));
+  return MD == DT ? md : rnd16<DT>(md);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -67,9 +69,11 @@ __device__ __forceinline__ float restore16(float code, float scale, float zero, 
 // through a small shared table, P.V on CUDA cores with four channels per lane.  Tokens packed on one side only
 // (Kitty lifecycle) take one warp per token, four channels per lane, fp32 math.
 // BS: the kernel's block-level shared struct (needs slot_map[128], merge_m / merge_l [kWarps][4])
-template <int DT, class BS>
+// MD: metadata dtype of the packed tokens (the tensor-core kernels for 2-bit pages only take MD = DT)
+template <int DT, int MD = DT, class BS>
 __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& bs, float* warp_out, int bh) {
   using H = Half2Ops<DT>;
+  using HM = Half2Ops<MD>;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rep = a.query_heads / d.kv_heads;
   const int seen = d.state[0], pages = d.state[1], k_end = d.state[2], v_end = d.state[3], sink_filled = d.state[4];
@@ -244,9 +248,9 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
           uint32_t code = (page[ch * key_row_bytes + (bit >> 3)] >> (bit & 7)) & key_mask;
           const int slot = bs.slot_map[ch];
           if (slot >= 0) code |= ((page[d.key_off_high + slot * key_row_bytes + (bit >> 3)] >> (bit & 7)) & 3u) << 2;
-          const float s = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_scale)[ch * key_groups + kg]);
-          const float z = H::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_zero)[ch * key_groups + kg]);
-          kv[i] = restore16<DT>((float)code, s, z, fused_key ? a.flavour : DARTKV_DEQUANT_PER_OP);
+          const float s = HM::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_scale)[ch * key_groups + kg]);
+          const float z = HM::to_float(reinterpret_cast<const uint16_t*>(page + d.key_off_zero)[ch * key_groups + kg]);
+          kv[i] = restore16<DT, MD>((float)code, s, z, fused_key ? a.flavour : DARTKV_DEQUANT_PER_OP);
         }
       } else {
         kv[0] = H::to_float((uint16_t)(k_raw.x & 0xFFFF)); kv[1] = H::to_float((uint16_t)(k_raw.x >> 16));
@@ -274,10 +278,10 @@ __device__ void dense_block(const dartkv_cache_desc& d, const FastArgs& a, BS& b
         if (d.value_bits == 8) word |= (uint32_t)packed[2] << 16 | (uint32_t)packed[3] << 24;
         const int g = (lane * 4) / d.value_group;
         const uint16_t* meta = reinterpret_cast<const uint16_t*>(d.v_meta) + row * 2 * d.value_groups;
-        const float sc = H::to_float(meta[g]), z = H::to_float(meta[d.value_groups + g]);
+        const float sc = HM::to_float(meta[g]), z = HM::to_float(meta[d.value_groups + g]);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          vv[i] = restore16<DT>((float)((word >> (d.value_bits * i)) & value_mask), sc, z, a.flavour);
+          vv[i] = restore16<DT, MD>((float)((word >> (d.value_bits * i)) & value_mask), sc, z, a.flavour);
       } else {
         vv[0] = H::to_float((uint16_t)(v_raw.x & 0xFFFF)); vv[1] = H::to_float((uint16_t)(v_raw.x >> 16));
         vv[2] = H::to_float((uint16_t)(v_raw.y & 0xFFFF)); vv[3] = H::to_float((uint16_t)(v_raw.y >> 16));

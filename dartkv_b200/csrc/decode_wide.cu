@@ -93,9 +93,18 @@ template <int DT> __device__ __forceinline__ void unpack16(uint32_t x, float& lo
   }
 }
 
-// FP32 = false: fl(fl(code * scale) + zero) in the 16-bit metadata dtype; true: code * scale + zero in fp32,
-// rounded once to the 16-bit cache dtype
-template <int DT, bool FP32, int PA, int PB>
+// one register of two 16-bit numbers of dtype FROM as dtype TO (round to nearest even; the cast of the dequantized
+// value from the metadata dtype to the cache dtype when the two differ)
+template <int FROM, int TO> __device__ __forceinline__ uint32_t cast16(uint32_t x) {
+  if (FROM == TO) return x;
+  float lo, hi;
+  unpack16<FROM>(x, lo, hi);
+  return pack16<TO>(lo, hi);
+}
+
+// FP32 = false: fl(fl(code * scale) + zero) in the 16-bit metadata dtype DT, then cast to the cache dtype OUT;
+// true: code * scale + zero in fp32, rounded once to the cache dtype
+template <int DT, int OUT, bool FP32, int PA, int PB>
 struct Restore {
   using H = Half2Ops<DT>;
   uint32_t s2, z2, nms_a, nms_b;
@@ -123,33 +132,33 @@ struct Restore {
     constexpr bool fma_form = SECOND ? kFmaB : kFmaA;
     const uint32_t nms = SECOND ? nms_b : nms_a;
     if (!FP32) {
-      if (fma_form) return H::add(H::fma(x, s2, nms), z2);   // fl(fl(c * s) + z)
-      return H::add(H::mul(H::add(x, nms), s2), z2);         // nms holds -magic here: x - magic = c exactly
+      if (fma_form) return cast16<DT, OUT>(H::add(H::fma(x, s2, nms), z2));   // fl(fl(c * s) + z)
+      return cast16<DT, OUT>(H::add(H::mul(H::add(x, nms), s2), z2));         // nms holds -magic here: x - magic = c exactly
     }
     float c0, c1;
     unpack16<DT>(H::add(x, nms), c0, c1);                    // nms holds -magic here: the codes, exactly
-    return pack16<DT>(__fmaf_rn(c0, sf, zf), __fmaf_rn(c1, sf, zf));
+    return pack16<OUT>(__fmaf_rn(c0, sf, zf), __fmaf_rn(c1, sf, zf));
   }
   // two codes as exact floats
   __device__ __forceinline__ uint32_t from_codes(float c0, float c1) const {
-    if (!FP32) return H::add(H::mul(pack16<DT>(c0, c1), s2), z2);   // small integers: exact in 16 bits
-    return pack16<DT>(__fmaf_rn(c0, sf, zf), __fmaf_rn(c1, sf, zf));
+    if (!FP32) return cast16<DT, OUT>(H::add(H::mul(pack16<DT>(c0, c1), s2), z2));   // small integers: exact in 16 bits
+    return pack16<OUT>(__fmaf_rn(c0, sf, zf), __fmaf_rn(c1, sf, zf));
   }
 };
 
 // code positions per width: plain 2-bit codes sit at bits 2 and 6 of a byte in fp16 (magics 256 and 16) and at
 // bits 0 and 4 in bf16; 4-bit codes at bit 4 in fp16 and bit 0 in bf16; two planes (a 4-bit code) at bits 0 and
 // 4 in fp16 and at bit 0 only in bf16, whose 7 mantissa bits cannot hold a 4-bit code from bit 4 on
-template <int DT, bool FP32> using Restore2 = Restore<DT, FP32, DT == DARTKV_F16 ? 2 : 0, DT == DARTKV_F16 ? 6 : 4>;
-template <int DT, bool FP32> using Restore22 = Restore<DT, FP32, 0, DT == DARTKV_F16 ? 4 : 0>;
-template <int DT, bool FP32> using Restore4 = Restore<DT, FP32, DT == DARTKV_F16 ? 4 : 0, DT == DARTKV_F16 ? 4 : 0>;
-template <int DT, bool FP32> using Restore8 = Restore<DT, FP32, 0, 0>;
+template <int DT, int OUT, bool FP32> using Restore2 = Restore<DT, OUT, FP32, DT == DARTKV_F16 ? 2 : 0, DT == DARTKV_F16 ? 6 : 4>;
+template <int DT, int OUT, bool FP32> using Restore22 = Restore<DT, OUT, FP32, 0, DT == DARTKV_F16 ? 4 : 0>;
+template <int DT, int OUT, bool FP32> using Restore4 = Restore<DT, OUT, FP32, DT == DARTKV_F16 ? 4 : 0, DT == DARTKV_F16 ? 4 : 0>;
+template <int DT, int OUT, bool FP32> using Restore8 = Restore<DT, OUT, FP32, 0, 0>;
 
 __device__ __forceinline__ constexpr uint32_t byte_pair_selector(int j) { return j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12); }
 
 // Sixteen 2-bit codes of a word -> 8 registers, register i = elements (2i, 2i+1).
-template <int DT, bool FP32>
-__device__ __forceinline__ void restore_2bit(uint32_t w, const Restore2<DT, FP32>& r, uint32_t (&out)[8]) {
+template <int DT, int OUT, bool FP32>
+__device__ __forceinline__ void restore_2bit(uint32_t w, const Restore2<DT, OUT, FP32>& r, uint32_t (&out)[8]) {
   // byte j of `lo` / `hi` feeds the low / high halves: elements 4j and 4j+2 (low), 4j+1 and 4j+3 (high) at the same bits
   const uint32_t lo = DT == DARTKV_F16 ? w << 2 : w, hi = DT == DARTKV_F16 ? w : w >> 2;
   constexpr uint32_t mask_a = DT == DARTKV_F16 ? 0x000C000Cu : 0x00030003u, mask_b = mask_a << 4;
@@ -163,8 +172,8 @@ __device__ __forceinline__ void restore_2bit(uint32_t w, const Restore2<DT, FP32
 }
 
 // Sixteen codes of two 2-bit planes (code = low | high << 2) -> 8 registers of adjacent elements.
-template <int DT, bool FP32>
-__device__ __forceinline__ void restore_2plus2(uint32_t w, uint32_t high, const Restore22<DT, FP32>& r, uint32_t (&out)[8]) {
+template <int DT, int OUT, bool FP32>
+__device__ __forceinline__ void restore_2plus2(uint32_t w, uint32_t high, const Restore22<DT, OUT, FP32>& r, uint32_t (&out)[8]) {
   const uint32_t t = w >> 2, hs = high << 2;
   const uint32_t m0 = magic16<DT>(0) * 0x00010001u, m4 = magic16<DT>(4) * 0x00010001u;
 #pragma unroll
@@ -181,8 +190,8 @@ __device__ __forceinline__ void restore_2plus2(uint32_t w, uint32_t high, const 
 }
 
 // Eight 4-bit codes of a word -> 4 registers of adjacent elements.
-template <int DT, bool FP32>
-__device__ __forceinline__ void restore_4bit(uint32_t w, const Restore4<DT, FP32>& r, uint32_t* out) {
+template <int DT, int OUT, bool FP32>
+__device__ __forceinline__ void restore_4bit(uint32_t w, const Restore4<DT, OUT, FP32>& r, uint32_t* out) {
   const uint32_t lo = DT == DARTKV_F16 ? w << 4 : w, hi = DT == DARTKV_F16 ? w : w >> 4;
   constexpr uint32_t mask = DT == DARTKV_F16 ? 0x00F000F0u : 0x000F000Fu;
   const uint32_t m = magic16<DT>(DT == DARTKV_F16 ? 4 : 0) * 0x00010001u;
@@ -191,8 +200,8 @@ __device__ __forceinline__ void restore_4bit(uint32_t w, const Restore4<DT, FP32
 }
 
 // Four 8-bit codes of a word -> 2 registers of adjacent elements.
-template <int DT, bool FP32>
-__device__ __forceinline__ void restore_8bit(uint32_t w, const Restore8<DT, FP32>& r, uint32_t* out) {
+template <int DT, int OUT, bool FP32>
+__device__ __forceinline__ void restore_8bit(uint32_t w, const Restore8<DT, OUT, FP32>& r, uint32_t* out) {
   if (DT == DARTKV_F16) {
     // 1024 + code: the code byte is the low byte of the half, 0x64 its high byte
 #pragma unroll
@@ -210,7 +219,7 @@ __device__ __forceinline__ void restore_8bit(uint32_t w, const Restore8<DT, FP32
 }
 
 // Keys of a staged chunk -> tile[channel][16 tokens] (rows of kKeyRow bytes).  KIND: 2, 4, 8 or 22 (two planes).
-template <int DT, bool FP32, int KIND>
+template <int DT, int MD, bool FP32, int KIND>
 __device__ __forceinline__ void keys_to_tile(const uint8_t* st, const WideGeom& w, const uint8_t* slot_of, uint8_t* tile,
                                              int lane, int kg) {
   const uint16_t* kscale = reinterpret_cast<const uint16_t*>(st + w.k_scale);
@@ -221,30 +230,30 @@ __device__ __forceinline__ void keys_to_tile(const uint8_t* st, const WideGeom& 
     const uint16_t sc = kscale[ch * w.key_groups + kg], zr = kzero[ch * w.key_groups + kg];
     uint32_t out[8];
     if constexpr (KIND == 22) {
-      Restore22<DT, FP32> rs;
+      Restore22<MD, DT, FP32> rs;
       rs.init(sc, zr);
       const uint32_t low = *reinterpret_cast<const uint32_t*>(st + ch * 4);
       const int slot = slot_of[ch];
       const uint32_t high = slot != 0xFF ? *reinterpret_cast<const uint32_t*>(st + w.k_high + slot * 4) : 0u;
-      restore_2plus2<DT, FP32>(low, high, rs, out);
+      restore_2plus2<MD, DT, FP32>(low, high, rs, out);
     } else if constexpr (KIND == 2) {
-      Restore2<DT, FP32> rs;
+      Restore2<MD, DT, FP32> rs;
       rs.init(sc, zr);
-      restore_2bit<DT, FP32>(*reinterpret_cast<const uint32_t*>(st + ch * 4), rs, out);
+      restore_2bit<MD, DT, FP32>(*reinterpret_cast<const uint32_t*>(st + ch * 4), rs, out);
     } else if constexpr (KIND == 4) {
-      Restore4<DT, FP32> rs;
+      Restore4<MD, DT, FP32> rs;
       rs.init(sc, zr);
       const uint2 words = *reinterpret_cast<const uint2*>(st + ch * 8);
-      restore_4bit<DT, FP32>(words.x, rs, out);
-      restore_4bit<DT, FP32>(words.y, rs, out + 4);
+      restore_4bit<MD, DT, FP32>(words.x, rs, out);
+      restore_4bit<MD, DT, FP32>(words.y, rs, out + 4);
     } else {
-      Restore8<DT, FP32> rs;
+      Restore8<MD, DT, FP32> rs;
       rs.init(sc, zr);
       const uint4 words = *reinterpret_cast<const uint4*>(st + ch * 16);
-      restore_8bit<DT, FP32>(words.x, rs, out);
-      restore_8bit<DT, FP32>(words.y, rs, out + 2);
-      restore_8bit<DT, FP32>(words.z, rs, out + 4);
-      restore_8bit<DT, FP32>(words.w, rs, out + 6);
+      restore_8bit<MD, DT, FP32>(words.x, rs, out);
+      restore_8bit<MD, DT, FP32>(words.y, rs, out + 2);
+      restore_8bit<MD, DT, FP32>(words.z, rs, out + 4);
+      restore_8bit<MD, DT, FP32>(words.w, rs, out + 6);
     }
     uint4* row = reinterpret_cast<uint4*>(tile + ch * kKeyRow);
     row[0] = make_uint4(out[0], out[1], out[2], out[3]);
@@ -254,12 +263,12 @@ __device__ __forceinline__ void keys_to_tile(const uint8_t* st, const WideGeom& 
 
 // Values of a staged chunk -> tile[16 tokens][128 channels] (rows of kValueRow bytes).  A lane takes 64 channels
 // of one token: 16 * BITS / 2 bytes, i.e. BITS / 2 pieces of 16 bytes.
-template <int DT, bool FP32, int BITS> struct ValueRestore;
-template <int DT, bool FP32> struct ValueRestore<DT, FP32, 2> { using type = Restore2<DT, FP32>; };
-template <int DT, bool FP32> struct ValueRestore<DT, FP32, 4> { using type = Restore4<DT, FP32>; };
-template <int DT, bool FP32> struct ValueRestore<DT, FP32, 8> { using type = Restore8<DT, FP32>; };
+template <int MD, int OUT, bool FP32, int BITS> struct ValueRestore;
+template <int MD, int OUT, bool FP32> struct ValueRestore<MD, OUT, FP32, 2> { using type = Restore2<MD, OUT, FP32>; };
+template <int MD, int OUT, bool FP32> struct ValueRestore<MD, OUT, FP32, 4> { using type = Restore4<MD, OUT, FP32>; };
+template <int MD, int OUT, bool FP32> struct ValueRestore<MD, OUT, FP32, 8> { using type = Restore8<MD, OUT, FP32>; };
 
-template <int DT, bool FP32, int BITS>
+template <int DT, int MD, bool FP32, int BITS>
 __device__ __forceinline__ void values_to_tile(const uint8_t* st, const WideGeom& w, uint8_t* tile, int lane, int vrb,
                                                int vgroups, int group_shift) {
   const int tok = lane & 15, half = lane >> 4;
@@ -267,7 +276,7 @@ __device__ __forceinline__ void values_to_tile(const uint8_t* st, const WideGeom
   const uint16_t* meta = reinterpret_cast<const uint16_t*>(st + w.v_meta) + tok * 2 * vgroups;
   uint8_t* row = tile + tok * kValueRow + half * 128;
   constexpr int kPieces = BITS / 2, kChannelsPerWord = 32 / BITS;
-  typename ValueRestore<DT, FP32, BITS>::type rs;
+  typename ValueRestore<MD, DT, FP32, BITS>::type rs;
   // a 16-byte piece holds 64 / kPieces channels: one group, unless the groups are smaller than that (then every
   // word, which never straddles groups of 16 channels or more, looks its group up)
   const bool group_per_word = (64 / kPieces) >> group_shift;
@@ -286,23 +295,23 @@ __device__ __forceinline__ void values_to_tile(const uint8_t* st, const WideGeom
       uint8_t* dst = row + ch_local * 2;
       if constexpr (BITS == 2) {
         uint32_t out[8];
-        restore_2bit<DT, FP32>(ws[k], rs, out);
+        restore_2bit<MD, DT, FP32>(ws[k], rs, out);
         reinterpret_cast<uint4*>(dst)[0] = make_uint4(out[0], out[1], out[2], out[3]);
         reinterpret_cast<uint4*>(dst)[1] = make_uint4(out[4], out[5], out[6], out[7]);
       } else if constexpr (BITS == 4) {
         uint32_t out[4];
-        restore_4bit<DT, FP32>(ws[k], rs, out);
+        restore_4bit<MD, DT, FP32>(ws[k], rs, out);
         *reinterpret_cast<uint4*>(dst) = make_uint4(out[0], out[1], out[2], out[3]);
       } else {
         uint32_t out[2];
-        restore_8bit<DT, FP32>(ws[k], rs, out);
+        restore_8bit<MD, DT, FP32>(ws[k], rs, out);
         *reinterpret_cast<uint2*>(dst) = make_uint2(out[0], out[1]);
       }
     }
   }
 }
 
-template <int DT, bool FP32>
+template <int DT, int MD, bool FP32>
 __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_desc d, FastArgs a, WideGeom w) {
   using H = Half2Ops<DT>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -315,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
 
   if ((int)blockIdx.x >= a.stream_blocks) {
     const int bh = blockIdx.x - a.stream_blocks;
-    dense_block<DT>(d, a, bs, warp_out, bh);
+    dense_block<DT, MD>(d, a, bs, warp_out, bh);
     __syncthreads();
     block_merge(a, bs, warp_out, bh / d.kv_heads, bh % d.kv_heads, rep, 0);
     return;
@@ -421,10 +430,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
         __syncwarp();
       }
       switch (w.key_kind) {
-        case 22: keys_to_tile<DT, FP32, 22>(st, w, slot_of, tile, lane, kg); break;
-        case 2: keys_to_tile<DT, FP32, 2>(st, w, slot_of, tile, lane, kg); break;
-        case 4: keys_to_tile<DT, FP32, 4>(st, w, slot_of, tile, lane, kg); break;
-        default: keys_to_tile<DT, FP32, 8>(st, w, slot_of, tile, lane, kg); break;
+        case 22: keys_to_tile<DT, MD, FP32, 22>(st, w, slot_of, tile, lane, kg); break;
+        case 2: keys_to_tile<DT, MD, FP32, 2>(st, w, slot_of, tile, lane, kg); break;
+        case 4: keys_to_tile<DT, MD, FP32, 4>(st, w, slot_of, tile, lane, kg); break;
+        default: keys_to_tile<DT, MD, FP32, 8>(st, w, slot_of, tile, lane, kg); break;
       }
       __syncwarp();
 
@@ -447,9 +456,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_wide_kernel(dartkv_cache_d
 
       // ---- values of the chunk -> tile[16 tokens][128 channels]
       switch (vbits) {
-        case 2: values_to_tile<DT, FP32, 2>(st, w, tile, lane, vrb, vgroups, vg_shift); break;
-        case 4: values_to_tile<DT, FP32, 4>(st, w, tile, lane, vrb, vgroups, vg_shift); break;
-        default: values_to_tile<DT, FP32, 8>(st, w, tile, lane, vrb, vgroups, vg_shift); break;
+        case 2: values_to_tile<DT, MD, FP32, 2>(st, w, tile, lane, vrb, vgroups, vg_shift); break;
+        case 4: values_to_tile<DT, MD, FP32, 4>(st, w, tile, lane, vrb, vgroups, vg_shift); break;
+        default: values_to_tile<DT, MD, FP32, 8>(st, w, tile, lane, vrb, vgroups, vg_shift); break;
       }
       __syncwarp();
       issue(idx + 2);   // the stage has been read by every lane
@@ -554,9 +563,13 @@ static size_t wide_smem_bytes(const WideGeom& w) {
 }
 
 using WideKernel = void (*)(dartkv_cache_desc, FastArgs, WideGeom);
-static WideKernel wide_variant(int dtype, bool fp32) {
-  if (dtype == DARTKV_BF16) return fp32 ? decode_wide_kernel<DARTKV_BF16, true> : decode_wide_kernel<DARTKV_BF16, false>;
-  return fp32 ? decode_wide_kernel<DARTKV_F16, true> : decode_wide_kernel<DARTKV_F16, false>;
+template <int DT>
+static WideKernel wide_variant_of(int md, bool fp32) {
+  if (md == DARTKV_BF16) return fp32 ? decode_wide_kernel<DT, DARTKV_BF16, true> : decode_wide_kernel<DT, DARTKV_BF16, false>;
+  return fp32 ? decode_wide_kernel<DT, DARTKV_F16, true> : decode_wide_kernel<DT, DARTKV_F16, false>;
+}
+static WideKernel wide_variant(int dtype, int md, bool fp32) {
+  return dtype == DARTKV_BF16 ? wide_variant_of<DARTKV_BF16>(md, fp32) : wide_variant_of<DARTKV_F16>(md, fp32);
 }
 
 }  // namespace
@@ -564,7 +577,7 @@ static WideKernel wide_variant(int dtype, bool fp32) {
 int dartkv_decode_wide_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads) {
   if (d->head_dim != 128 || d->page_size != 128 || !d->regular_pages) return 0;
   if (d->dtype != DARTKV_F16 && d->dtype != DARTKV_BF16) return 0;
-  if (d->md_dtype != d->dtype || q_dtype != d->dtype) return 0;
+  if ((d->md_dtype != DARTKV_F16 && d->md_dtype != DARTKV_BF16) || q_dtype != d->dtype) return 0;
   if (d->key_group < 16 || d->key_group > 128 || (d->key_group & (d->key_group - 1))) return 0;
   if (d->value_group < 16 || d->value_group > 128 || (d->value_group & (d->value_group - 1))) return 0;
   if (d->value_bits != 2 && d->value_bits != 4 && d->value_bits != 8) return 0;
@@ -599,12 +612,13 @@ int dartkv_decode_wide_launch(const dartkv_cache_desc* d, const void* query, int
     DARTKV_CUDA_OK(cudaGetDevice(&device));
     if (device < 0 || device >= 64 || !ready[device].load(std::memory_order_acquire)) {
       for (int dt : {DARTKV_BF16, DARTKV_F16})
-        for (int fp32 : {0, 1})
-          DARTKV_CUDA_OK(cudaFuncSetAttribute(wide_variant(dt, fp32 != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        for (int md : {DARTKV_BF16, DARTKV_F16})
+          for (int fp32 : {0, 1})
+            DARTKV_CUDA_OK(cudaFuncSetAttribute(wide_variant(dt, md, fp32 != 0), cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
       if (device >= 0 && device < 64) ready[device].store(true, std::memory_order_release);
     }
   }
-  wide_variant(d->dtype, flavour == DARTKV_DEQUANT_FP32)<<<grid, kThreads, smem, stream>>>(*d, a, w);
+  wide_variant(d->dtype, d->md_dtype, flavour == DARTKV_DEQUANT_FP32)<<<grid, kThreads, smem, stream>>>(*d, a, w);
   DARTKV_LAUNCH_OK("decode_wide_kernel");
   return DARTKV_OK;
 }

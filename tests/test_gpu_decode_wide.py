@@ -27,13 +27,14 @@ def plan_kernel(cache, dtype, hq, flavour):
 
 
 def run_case(dtype, *, batch=2, heads=2, hq=8, tokens=32 + 5 * 128 + 77, chunks=None, seed=0, flavour=_lib.DEQUANT_PER_OP,
-             row_start=None, expect_kernel=3, **cfg):
+             row_start=None, expect_kernel=3, metadata=None, **cfg):
     tag = DT_TAG[dtype]
+    metadata = metadata or dtype
     keys, values, query = make_kvq(seed, batch, heads, tokens, 128, query_heads=hq, dtype=dtype, outlier_fraction=0.05)
     base = dict(bits=2, page_size=128, key_group_size=128, value_group_size=64, sink_tokens=32, hold_partial_pages=True)
     base.update(cfg)
-    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=dtype, **base))
-    oracle = orc.OracleCache(orc.CacheConfig(metadata_dtype=tag, **base), tag)
+    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=metadata, **base))
+    oracle = orc.OracleCache(orc.CacheConfig(metadata_dtype=DT_TAG[metadata], **base), tag)
     start = 0
     for chunk in chunks or [tokens]:
         cache.append(keys[:, :, start:start + chunk].cuda(), values[:, :, start:start + chunk].cuda())
@@ -122,6 +123,15 @@ def test_left_padding():
 @pytest.mark.parametrize("hq", [2, 4, 8])
 def test_query_group_sizes(hq):
     run_case(torch.bfloat16, bits=4, seed=90 + hq, hq=hq)
+
+
+@pytest.mark.parametrize("dtype,metadata", [(torch.bfloat16, torch.float16), (torch.float16, torch.bfloat16)])
+@pytest.mark.parametrize("cfg", [dict(promote_ratio=0.25), dict(bits=4), dict(bits=8, promote_ratio=0.25), dict(bits=8)])
+def test_metadata_dtype_differs_from_the_cache_dtype(dtype, metadata, cfg):
+    # the reference's scripts keep fp16 metadata beside bf16 models (its default metadata dtype): the dequantized
+    # value is rounded in the metadata dtype and then cast to the cache dtype
+    run_case(dtype, metadata=metadata, seed=100, chunks=[32 + 2 * 128 + 40, 3 * 128 + 37], **cfg)
+    run_case(dtype, metadata=metadata, seed=101, flavour=_lib.DEQUANT_FP32, **cfg)
 
 
 def test_headline_geometry_keeps_its_own_kernels():
