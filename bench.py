@@ -98,7 +98,8 @@ def build_device_cache(rows, ctx: int, seed: int, device: torch.device, keep_inp
                  for k in ("bits", "promote_ratio", "value_group") if GEOM[k] != HEADLINE[k]}
     rows = list(rows)
     got = build_headline_cache(rows, ctx, seed, device, heads=heads, keep_rows=rows if keep_inputs else None,
-                               cache_overrides=overrides)
+                               cache_overrides=overrides,
+                               metadata_dtype=torch.float16 if GEOM.get("metadata") == "fp16" else torch.bfloat16)
     return got if keep_inputs else got[:2]
 
 
@@ -214,7 +215,8 @@ class CpuDecode:
         t0 = time.perf_counter()
         if dart is not None:
             self.kind = "reference"
-            cfg = dart.DartKVCacheConfig(metadata_dtype=torch.bfloat16, **cache_kwargs())
+            cfg = dart.DartKVCacheConfig(metadata_dtype=torch.float16 if GEOM.get("metadata") == "fp16" else torch.bfloat16,
+                                         **cache_kwargs())
             cache = dart.DartKVCache(cfg)
             cache.append(keys[:, :, : GEOM["sinks"]], values[:, :, : GEOM["sinks"]])
             cache.append(keys[:, :, GEOM["sinks"]:], values[:, :, GEOM["sinks"]:])
@@ -227,7 +229,8 @@ class CpuDecode:
 
             self.kind = "port"
             self._limits = threadpool_limits(limits=self.cores)
-            cache = orc.OracleCache(orc.CacheConfig(metadata_dtype="bf16", **cache_kwargs()), "bf16")
+            cache = orc.OracleCache(orc.CacheConfig(metadata_dtype="f16" if GEOM.get("metadata") == "fp16" else "bf16",
+                                                    **cache_kwargs()), "bf16")
             k32, v32, q32 = keys.float().numpy(), values.float().numpy(), query.float().numpy()
             cache.append(k32[:, :, : GEOM["sinks"]], v32[:, :, : GEOM["sinks"]])
             cache.append(k32[:, :, GEOM["sinks"]:], v32[:, :, GEOM["sinks"]:])
@@ -261,7 +264,7 @@ def workload_config(args, wl, world: int) -> dict:
                                                        else f"{GEOM['bits']}-bit keys")
             if GEOM != HEADLINE else "2-bit + 0.25 promotion",
             "key_group": GEOM["key_group"],
-            "value_group": GEOM["value_group"], "sinks": GEOM["sinks"], "metadata": "bf16",
+            "value_group": GEOM["value_group"], "sinks": GEOM["sinks"], "metadata": GEOM.get("metadata", "bf16"),
             "bytes_per_step": step_bytes(wl["batch"], wl["ctx"]),
             "dequant": {"per_op": "per-op rounded (reference streamed path)",
                         "fp32": "fp32 with one rounding (reference streamed path on CUDA)",
@@ -411,10 +414,13 @@ def other_geometry_decode(device: torch.device, steps: int, peak: float) -> list
                 ("2+2-bit keys, 4-bit values", dict(bits=4), _lib.DEQUANT_PER_OP),
                 ("8-bit keys and values", dict(bits=8, promote_ratio=0.0), _lib.DEQUANT_PER_OP),
                 ("headline widths, value groups of 32", dict(value_group=32), _lib.DEQUANT_PER_OP),
-                ("headline geometry, fp32 flavour", dict(), _lib.DEQUANT_FP32)]
+                ("headline geometry, fp32 flavour", dict(), _lib.DEQUANT_FP32),
+                ("headline geometry, fp16 metadata beside the bf16 cache (the reference scripts' setting)",
+                 dict(metadata="fp16"), _lib.DEQUANT_PER_OP)]
     start_evt, stop_evt = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     try:
         for name, change, flavour in variants:
+            GEOM.clear()
             GEOM.update(saved)
             GEOM.update(change)
             cache, query = build_device_cache(range(32), 8192, WORKLOADS["config3"]["seed"], device)
@@ -435,6 +441,7 @@ def other_geometry_decode(device: torch.device, steps: int, peak: float) -> list
             del cache
             torch.cuda.empty_cache()
     finally:
+        GEOM.clear()
         GEOM.update(saved)
     return results
 
@@ -904,6 +911,8 @@ def main() -> None:
     parser.add_argument("--promote", type=float, default=None, help="promoted key channel ratio off the headline geometry")
     parser.add_argument("--value-group", type=int, choices=(16, 32, 64, 128), default=0,
                         help="value group size off the headline geometry")
+    parser.add_argument("--metadata", choices=("bf16", "fp16"), default="bf16",
+                        help="dtype of scales and zero points (fp16 beside the bf16 cache: general tensor-core kernel)")
     parser.add_argument("--gather", choices=("peer", "nccl"), default="peer",
                         help="multi-GPU output gather: peer stores from the decode kernels (default) or NCCL")
     parser.add_argument("--batch", type=int, default=0, help="override the workload's batch (e.g. one rank's share)")
@@ -915,6 +924,8 @@ def main() -> None:
         GEOM["promote_ratio"] = args.promote
     if args.value_group:
         GEOM["value_group"] = args.value_group
+    if args.metadata == "fp16":
+        GEOM["metadata"] = "fp16"
     if args.workload == "config4":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "config4 needs the GPU model run; the CPU arm covers config5/config3"}))
