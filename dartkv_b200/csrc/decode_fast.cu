@@ -37,7 +37,7 @@ namespace {
 #if defined(PEROP_SKIP_MMA)
 #define PEROP_MMA(acc, a0, a1, a2, a3, b0, b1) ((acc)[0] += __uint_as_float((a0) ^ (a1) ^ (a2) ^ (a3) ^ (b0) ^ (b1)))
 #else
-#define PEROP_MMA(acc, a0, a1, a2, a3, b0, b1) H::mma(acc, a0, a1, a2, a3, b0, b1)
+#define PEROP_MMA(acc, a0, a1, a2, a3, b0, b1) HO::mma(acc, a0, a1, a2, a3, b0, b1)
 #endif
 
 #ifndef PEROP_QK_UNROLL
@@ -65,15 +65,27 @@ struct BlockSmem {
   int slot_map[128];
 };
 
+// the dequantized registers of a code word, from the metadata dtype to the cache dtype (nothing when they agree)
+template <int DT, int OUT>
+__device__ __forceinline__ void cast_registers(uint32_t (&r)[8]) {
+  if (DT != OUT) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] = cast16<DT, OUT>(r[i]);
+  }
+}
+
 // One warp's share of a staged page: QK over its 64 tokens, online softmax, PV over the same tokens.
+// DT = metadata dtype (the arithmetic of the dequantization), OUT = cache dtype (the MMA operands): when they differ
+// every dequantized register is cast, as the reference casts its dequantized pages (src/dart/quantization.py:103-106).
 // GN = value groups per token (1 or 2).
-template <int DT, int GN, int KP>
+template <int DT, int OUT, int GN, int KP>
 __device__ __forceinline__ void page_half(const int HF, const int pair, const int lane, const dartkv_cache_desc& d, PairSmem& ps,
                                           const uint8_t* blob, uint16_t* prob, uint16_t* partner_prob, const uint8_t* q_thread, const CodeConsts<DT>& cc, int K, int prom_steps,
                                           float scale2, int g, int c, int jp, int hq, int gv, int mask_below,
                                           float (&o_acc)[8][4],
                                           float& m_run, float& l_run) {
   using H = Half2Ops<DT>;
+  using HO = Half2Ops<OUT>;
   const uint8_t* low_thread = blob + 4 * g;   // + 32 * channel = this thread's word of the channel row
   const uint32_t* high = reinterpret_cast<const uint32_t*>(blob + d.key_off_high);
 
@@ -101,6 +113,8 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
     uint32_t r0[8], r1[8];
     dequant_word4<DT>(cc, w0, h0, a0.x, a0.y, a0.z, a0.w, r0);
     dequant_word4<DT>(cc, w1, h1, a1.x, a1.y, a1.z, a1.w, r1);
+    cast_registers<DT, OUT>(r0);
+    cast_registers<DT, OUT>(r1);
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
 #pragma unroll
@@ -121,6 +135,8 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
     uint32_t r0[8], r1[8];
     dequant_word2<DT>(cc, w0, a0.x, a0.y, a0.z, a0.w, o0.x, r0);
     dequant_word2<DT>(cc, w1, a1.x, a1.y, a1.z, a1.w, o1.x, r1);
+    cast_registers<DT, OUT>(r0);
+    cast_registers<DT, OUT>(r1);
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(q_thread + o0.y);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(q_thread + o1.y);
 #pragma unroll
@@ -184,9 +200,9 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
       const float p = fast_exp2(s_sum[mt][i] - m_ref);
       psum += p;
       const int li = 4 * mt + i;   // table order inside this thread's 8 tokens: token offset (li >> 1) + 8 * (li & 1)
-      const uint16_t hi = H::from_float(p);
+      const uint16_t hi = HO::from_float(p);
       phi[li] = hi;
-      plo[li] = H::from_float(p - H::to_float(hi));
+      plo[li] = HO::from_float(p - HO::to_float(hi));
     }
   l_run = l_run * alpha + psum;
   // the running maximum rarely moves after the first pages: skip the rescale when no lane needs it.  This thread's
@@ -243,6 +259,8 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
     const uint32_t ms0 = H::mul(ss, H::neg_magic(0)), ms1 = H::mul(ss, H::neg_magic(1)), ms2 = H::mul(ss, H::neg_magic(2));
     dequant_word2<DT>(cc, prmt(wa, wb, 0x5410u), ss, zz, ms0, ms1, ms2, r_lo);
     dequant_word2<DT>(cc, prmt(wa, wb, 0x7632u), ss, zz, ms0, ms1, ms2, r_hi);
+    cast_registers<DT, OUT>(r_lo);
+    cast_registers<DT, OUT>(r_hi);
   };
 #if !defined(PEROP_SKIP_PV)
 #pragma unroll kPvUnroll
@@ -260,9 +278,10 @@ __device__ __forceinline__ void page_half(const int HF, const int pair, const in
 // GN: value groups per token (1 or 2).  KP: promoted channels per page when that is a multiple of eight known to
 // the host (0, 8, 16, 24, 32), else -1 (read from the descriptor): with the count fixed the logits loops have
 // constant trip counts and no per-position "is this slot promoted" test.
-template <int DT, int GN, int KP>
+template <int DT, int OUT, int GN, int KP>
 __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_desc d, FastArgs a) {
   using H = Half2Ops<DT>;
+  using HO = Half2Ops<OUT>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   PairSmem* psm_all = reinterpret_cast<PairSmem*>(smem_raw);
   BlockSmem& bs = *reinterpret_cast<BlockSmem*>(smem_raw + sizeof(PairSmem) * kPairs);
@@ -276,7 +295,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
     // dense tokens of one (batch, kv head): partial slot 0.  These short blocks come last in launch order and fill
     // the slots the stream blocks leave.
     const int bh = blockIdx.x - a.stream_blocks;
-    dense_block<DT>(d, a, bs, warp_out, bh);
+    dense_block<OUT, DT>(d, a, bs, warp_out, bh);
     __syncthreads();
     block_merge(a, bs, warp_out, bh / d.kv_heads, bh % d.kv_heads, rep, 0);
     return;
@@ -409,7 +428,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fast_kernel(dartkv_cache_d
 #endif
       __syncwarp();
 
-      page_half<DT, GN, KP>(hf, pair, lane, d, ps, blob, ps.prob[hf], ps.prob[hf ^ 1], q_thread, cc, K, prom_steps, scale2, g, c, jp,
+      page_half<DT, OUT, GN, KP>(hf, pair, lane, d, ps, blob, ps.prob[hf], ps.prob[hf ^ 1], q_thread, cc, K, prom_steps, scale2, g, c, jp,
                             hq, gv, row_first - (d.sink_tokens + 128 * pg), o_acc, m_run, l_run);
 
       pair_barrier(pair);
@@ -446,7 +465,7 @@ constexpr size_t kSmemBytes = sizeof(PairSmem) * kPairs + sizeof(BlockSmem);
 int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads) {
   if (d->head_dim != 128 || d->page_size != 128 || d->key_group != 128 || !d->regular_pages) return 0;
   if (d->dtype != DARTKV_F16 && d->dtype != DARTKV_BF16) return 0;
-  if (d->md_dtype != d->dtype || q_dtype != d->dtype) return 0;
+  if ((d->md_dtype != DARTKV_F16 && d->md_dtype != DARTKV_BF16) || q_dtype != d->dtype) return 0;
   if (d->value_bits != 2 || (d->value_group != 64 && d->value_group != 128)) return 0;
   if (d->key_mode == DARTKV_QUANTIZED_PAGE && d->key_bits != 2) return 0;
   if (d->key_page_bytes % 16 || d->key_page_bytes > kPageBytesK) return 0;   // at most 32 promoted channels
@@ -456,26 +475,40 @@ int dartkv_decode_fast_supported(const dartkv_cache_desc* d, int q_dtype, int qu
   return 1;
 }
 
-// every (dtype, value groups, promoted count) variant of the kernel
+// every (metadata dtype, cache dtype, value groups, promoted count) variant of the kernel; a cache whose metadata
+// dtype differs from its dtype gets the promoted counts 0 and 32 specialized, the others read the count at run time
 using FastKernel = void (*)(dartkv_cache_desc, FastArgs);
 template <int DT, int GN>
 static FastKernel fast_variant_kp(int kp) {
   switch (kp) {
-    case 0: return decode_fast_kernel<DT, GN, 0>;
-    case 8: return decode_fast_kernel<DT, GN, 8>;
-    case 16: return decode_fast_kernel<DT, GN, 16>;
-    case 24: return decode_fast_kernel<DT, GN, 24>;
-    case 32: return decode_fast_kernel<DT, GN, 32>;
-    default: return decode_fast_kernel<DT, GN, -1>;
+    case 0: return decode_fast_kernel<DT, DT, GN, 0>;
+    case 8: return decode_fast_kernel<DT, DT, GN, 8>;
+    case 16: return decode_fast_kernel<DT, DT, GN, 16>;
+    case 24: return decode_fast_kernel<DT, DT, GN, 24>;
+    case 32: return decode_fast_kernel<DT, DT, GN, 32>;
+    default: return decode_fast_kernel<DT, DT, GN, -1>;
   }
 }
-static FastKernel fast_variant(int dtype, int value_groups, int kp) {
-  if (dtype == DARTKV_BF16) return value_groups == 2 ? fast_variant_kp<DARTKV_BF16, 2>(kp) : fast_variant_kp<DARTKV_BF16, 1>(kp);
-  return value_groups == 2 ? fast_variant_kp<DARTKV_F16, 2>(kp) : fast_variant_kp<DARTKV_F16, 1>(kp);
+template <int DT, int OUT, int GN>
+static FastKernel mixed_variant_kp(int kp) {
+  switch (kp) {
+    case 0: return decode_fast_kernel<DT, OUT, GN, 0>;
+    case 32: return decode_fast_kernel<DT, OUT, GN, 32>;
+    default: return decode_fast_kernel<DT, OUT, GN, -1>;
+  }
 }
-static void launch_variant(int dtype, int value_groups, int kp, dim3 grid, cudaStream_t stream, const dartkv_cache_desc& d,
-                           const FastArgs& a) {
-  fast_variant(dtype, value_groups, kp)<<<grid, kThreads, kSmemBytes, stream>>>(d, a);
+static FastKernel fast_variant(int md, int dtype, int value_groups, int kp) {
+  if (md == dtype) {
+    if (dtype == DARTKV_BF16) return value_groups == 2 ? fast_variant_kp<DARTKV_BF16, 2>(kp) : fast_variant_kp<DARTKV_BF16, 1>(kp);
+    return value_groups == 2 ? fast_variant_kp<DARTKV_F16, 2>(kp) : fast_variant_kp<DARTKV_F16, 1>(kp);
+  }
+  if (md == DARTKV_F16)
+    return value_groups == 2 ? mixed_variant_kp<DARTKV_F16, DARTKV_BF16, 2>(kp) : mixed_variant_kp<DARTKV_F16, DARTKV_BF16, 1>(kp);
+  return value_groups == 2 ? mixed_variant_kp<DARTKV_BF16, DARTKV_F16, 2>(kp) : mixed_variant_kp<DARTKV_BF16, DARTKV_F16, 1>(kp);
+}
+static void launch_variant(int md, int dtype, int value_groups, int kp, dim3 grid, cudaStream_t stream,
+                           const dartkv_cache_desc& d, const FastArgs& a) {
+  fast_variant(md, dtype, value_groups, kp)<<<grid, kThreads, kSmemBytes, stream>>>(d, a);
 }
 
 int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
@@ -493,17 +526,18 @@ int dartkv_decode_fast_launch(const dartkv_cache_desc* d, const void* query, int
     int device = 0;
     DARTKV_CUDA_OK(cudaGetDevice(&device));
     if (device < 0 || device >= 64 || !ready[device].load(std::memory_order_acquire)) {
-      for (int dt : {DARTKV_BF16, DARTKV_F16})
-        for (int gn : {1, 2})
-          for (int kp : {-1, 0, 8, 16, 24, 32})
-            DARTKV_CUDA_OK(cudaFuncSetAttribute(fast_variant(dt, gn, kp), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                (int)kSmemBytes));
+      for (int md : {DARTKV_BF16, DARTKV_F16})
+        for (int dt : {DARTKV_BF16, DARTKV_F16})
+          for (int gn : {1, 2})
+            for (int kp : {-1, 0, 8, 16, 24, 32})
+              DARTKV_CUDA_OK(cudaFuncSetAttribute(fast_variant(md, dt, gn, kp), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)kSmemBytes));
       if (device >= 0 && device < 64) ready[device].store(true, std::memory_order_release);
     }
   }
   const int promoted = d->key_mode == DARTKV_MIXED_PAGE ? d->promoted : 0;
   const int kp = (promoted % 8 == 0 && promoted <= 32) ? promoted : -1;
-  launch_variant(d->dtype, d->value_groups, kp, grid, stream, *d, a);
+  launch_variant(d->md_dtype, d->dtype, d->value_groups, kp, grid, stream, *d, a);
   DARTKV_LAUNCH_OK("decode_fast_kernel");
   return DARTKV_OK;
 }

@@ -76,32 +76,6 @@ template <int DT> __device__ __forceinline__ constexpr float magic_value(int p) 
 
 // One (scale, zero point) pair made ready for a run of code pairs whose codes sit at bit position PA or PB of
 // their 16-bit halves.
-// two floats -> one register of two 16-bit numbers (round to nearest even), `lo` in the low half
-template <int DT> __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
-  uint32_t d;
-  if (DT == DARTKV_F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-  else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-  return d;
-}
-// the two 16-bit numbers of a register as floats
-template <int DT> __device__ __forceinline__ void unpack16(uint32_t x, float& lo, float& hi) {
-  if (DT == DARTKV_F16) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&x));
-    lo = f.x; hi = f.y;
-  } else {
-    lo = __uint_as_float(x << 16); hi = __uint_as_float(x & 0xFFFF0000u);
-  }
-}
-
-// one register of two 16-bit numbers of dtype FROM as dtype TO (round to nearest even; the cast of the dequantized
-// value from the metadata dtype to the cache dtype when the two differ)
-template <int FROM, int TO> __device__ __forceinline__ uint32_t cast16(uint32_t x) {
-  if (FROM == TO) return x;
-  float lo, hi;
-  unpack16<FROM>(x, lo, hi);
-  return pack16<TO>(lo, hi);
-}
-
 // FP32 = false: fl(fl(code * scale) + zero) in the 16-bit metadata dtype DT, then cast to the cache dtype OUT;
 // true: code * scale + zero in fp32, rounded once to the cache dtype
 template <int DT, int OUT, bool FP32, int PA, int PB>

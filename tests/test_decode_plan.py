@@ -90,7 +90,8 @@ def test_other_geometries_take_the_general_tensor_core_kernel():
     assert plan(d, _lib.BF16, 8, _lib.DEQUANT_FP32, 5000).kernel == 3       # the fp32 flavour of the headline geometry
     assert plan(d, _lib.BF16, 16, _lib.DEQUANT_PER_OP, 5000).kernel == 0    # 8 query heads per kv head
     d.md_dtype = _lib.F16                                                    # fp16 metadata beside a bf16 cache
-    assert plan(d, _lib.BF16, 8, _lib.DEQUANT_PER_OP, 5000).kernel == 3
+    assert plan(d, _lib.BF16, 8, _lib.DEQUANT_PER_OP, 5000).kernel == 1     # the per-op kernel casts its operands
+    assert plan(d, _lib.BF16, 8, _lib.DEQUANT_FP32, 5000).kernel == 3
     assert plan(d, _lib.BF16, 8, _lib.DEQUANT_FUSED, 5000).kernel == 0
 
 

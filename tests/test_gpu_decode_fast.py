@@ -13,14 +13,16 @@ from tests.helpers import DT_TAG, to_np
 pytestmark = pytest.mark.gpu
 
 
-def run_case(dtype, *, batch=2, heads=2, hq=8, tokens=32 + 5 * 128 + 77, chunks=None, seed=0, outliers=True, **cfg):
+def run_case(dtype, *, batch=2, heads=2, hq=8, tokens=32 + 5 * 128 + 77, chunks=None, seed=0, outliers=True, metadata=None,
+             **cfg):
     tag = DT_TAG[dtype]
+    metadata = metadata or dtype
     keys, values, query = make_kvq(seed, batch, heads, tokens, 128, query_heads=hq, dtype=dtype,
                                    outlier_fraction=0.05 if outliers else 0.0)
     base = dict(bits=2, page_size=128, key_group_size=128, value_group_size=64, sink_tokens=32, hold_partial_pages=True)
     base.update(cfg)
-    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=dtype, **base))
-    oracle = orc.OracleCache(orc.CacheConfig(metadata_dtype=tag, **base), tag)
+    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=metadata, **base))
+    oracle = orc.OracleCache(orc.CacheConfig(metadata_dtype=DT_TAG[metadata], **base), tag)
     start = 0
     for chunk in chunks or [tokens]:
         cache.append(keys[:, :, start:start + chunk].cuda(), values[:, :, start:start + chunk].cuda())
@@ -46,6 +48,19 @@ def run_case(dtype, *, batch=2, heads=2, hq=8, tokens=32 + 5 * 128 + 77, chunks=
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_headline_geometry(dtype):
     run_case(dtype, promote_ratio=0.25, chunks=[32, 128, 128, 128, 128, 128, 77])
+
+
+@pytest.mark.parametrize("dtype,metadata", [(torch.bfloat16, torch.float16), (torch.float16, torch.bfloat16)])
+def test_metadata_dtype_differs_from_the_cache_dtype(dtype, metadata):
+    # the reference's default: fp16 scales and zero points, also beside a bf16 model (src/dart/cache.py:57); the
+    # dequantized value is rounded in the metadata dtype and then cast to the cache dtype (quantization.py:103-106)
+    run_case(dtype, metadata=metadata, seed=20, promote_ratio=0.25, chunks=[32, 128, 128, 128, 128, 128, 77])
+    run_case(dtype, metadata=metadata, seed=21, chunks=[300, 449])                       # uniform 2-bit keys
+    run_case(dtype, metadata=metadata, seed=22, promote_ratio=0.1)                       # 12 promoted channels
+    run_case(dtype, metadata=metadata, seed=23, promote_ratio=0.25, value_group_size=128, sink_tokens=0,
+             tokens=4 * 128 + 3)
+    run_case(dtype, metadata=metadata, seed=24, batch=1, heads=2, hq=8, tokens=32 + 3 * 128 + 40 + 30, promote_ratio=0.25,
+             local_tokens=1, value_local_tokens=128, chunks=[32 + 3 * 128 + 40] + [1] * 30)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])

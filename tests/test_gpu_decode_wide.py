@@ -130,7 +130,10 @@ def test_query_group_sizes(hq):
 def test_metadata_dtype_differs_from_the_cache_dtype(dtype, metadata, cfg):
     # the reference's scripts keep fp16 metadata beside bf16 models (its default metadata dtype): the dequantized
     # value is rounded in the metadata dtype and then cast to the cache dtype
-    run_case(dtype, metadata=metadata, seed=100, chunks=[32 + 2 * 128 + 40, 3 * 128 + 37], **cfg)
+    # 2-bit pages keep their own per-op kernel (it casts its operands); their fp32 flavour comes here
+    two_bit = cfg.get("bits", 2) == 2
+    run_case(dtype, metadata=metadata, seed=100, chunks=[32 + 2 * 128 + 40, 3 * 128 + 37], expect_kernel=1 if two_bit else 3,
+             **cfg)
     run_case(dtype, metadata=metadata, seed=101, flavour=_lib.DEQUANT_FP32, **cfg)
 
 
