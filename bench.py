@@ -415,8 +415,8 @@ def other_geometry_decode(device: torch.device, steps: int, peak: float) -> list
                 ("8-bit keys and values", dict(bits=8, promote_ratio=0.0), _lib.DEQUANT_PER_OP),
                 ("headline widths, value groups of 32", dict(value_group=32), _lib.DEQUANT_PER_OP),
                 ("headline geometry, fp32 flavour", dict(), _lib.DEQUANT_FP32),
-                ("headline geometry, fp16 metadata beside the bf16 cache (the reference scripts' setting)",
-                 dict(metadata="fp16"), _lib.DEQUANT_PER_OP)]
+                ("headline geometry, fp16 metadata beside the bf16 cache (the reference scripts' setting; per-op "
+                 "kernel with operand casts)", dict(metadata="fp16"), _lib.DEQUANT_PER_OP)]
     start_evt, stop_evt = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     try:
         for name, change, flavour in variants:

@@ -291,7 +291,8 @@ __device__ __forceinline__ void fused_page_half(const int HF, const int tb, cons
 
 // GN: value groups per token (1 or 2).  KP: promoted channels per page when that is a multiple of eight known to
 // the host (0, 8, 16, 24, 32), else -1 (read from the descriptor).
-template <int DT, int GN, int KP>
+// DT: dtype of the cache and the query; MD: dtype of the scales and zero points
+template <int DT, int MD, int GN, int KP>
 __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cache_desc d, FastArgs a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   FusedPairSmem* psm_all = reinterpret_cast<FusedPairSmem*>(smem_raw);
@@ -306,7 +307,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
     // dense tokens of one (batch, kv head): partial slot 0.  These short blocks come last in launch order and fill
     // the slots the stream blocks leave.
     const int bh = blockIdx.x - a.stream_blocks;
-    dense_block<DT>(d, a, bs, warp_out, bh);
+    dense_block<DT, MD>(d, a, bs, warp_out, bh);
     __syncthreads();
     block_merge(a, bs, warp_out, bh / d.kv_heads, bh % d.kv_heads, rep, 0);
     return;
@@ -419,12 +420,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
         uint32_t smax = max(max(sc4.x & 0xFFFFu, sc4.x >> 16), max(sc4.y & 0xFFFFu, sc4.y >> 16));
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) smax = max(smax, __shfl_xor_sync(0xffffffffu, smax, off));
-        pow2_normaliser(4.0f * q_absmax * md_to_float<DT>(smax), f, f_inv);
+        pow2_normaliser(4.0f * q_absmax * md_to_float<MD>(smax), f, f_inv);
 
         const int tp = 32 * hf + lane;
         float s0, s1, z0, z1;
-        md_pair_to_float<DT>(kscale2[tp], s0, s1);
-        md_pair_to_float<DT>(kzero2[tp], z0, z1);
+        md_pair_to_float<MD>(kscale2[tp], s0, s1);
+        md_pair_to_float<MD>(kzero2[tp], z0, z1);
         const float4 qa = *reinterpret_cast<const float4*>(bs.qf[2 * tp]);
         const float4 qb = *reinterpret_cast<const float4*>(bs.qf[2 * tp + 1]);
         const float sa = s0 * f, sb = s1 * f;
@@ -448,7 +449,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
           uint2 wh = make_uint2(0u, 0u), wl = make_uint2(0u, 0u);
           if (lane < K) {
             const int ch = reinterpret_cast<const int32_t*>(blob + d.key_off_index)[lane] & 127;
-            const float s4 = 4.0f * f * md_to_float<DT>(reinterpret_cast<const uint16_t*>(blob + d.key_off_scale)[ch]);
+            const float s4 = 4.0f * f * md_to_float<MD>(reinterpret_cast<const uint16_t*>(blob + d.key_off_scale)[ch]);
             const float4 qh = *reinterpret_cast<const float4*>(bs.qf[ch]);
             const float e0 = qh.x * s4, e1 = qh.y * s4, e2 = qh.z * s4, e3 = qh.w * s4;
             wh = make_uint2(pack_f16x2(e0, e1), pack_f16x2(e2, e3));
@@ -466,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_fused32_kernel(dartkv_cach
       pair_barrier(pair);
       if (issuer && pg != pg0 && pg + kPairs < p_end) issue(pg + kPairs, stage ^ 1);
 
-      fused_page_half<DT, GN>(hf, stage, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u,
+      fused_page_half<MD, GN>(hf, stage, d, ps, blob, utab, prom_steps, scale2, f_inv, g, c, sel_w, mask_u,
                               row_first - (d.sink_tokens + 128 * pg), st);
 
     }
@@ -509,7 +510,7 @@ constexpr size_t kFusedSmemBytes = sizeof(FusedPairSmem) * kPairs + sizeof(Fused
 int dartkv_decode_fused32_supported(const dartkv_cache_desc* d, int q_dtype, int query_heads) {
   if (d->head_dim != 128 || d->page_size != 128 || d->key_group != 128 || !d->regular_pages) return 0;
   if (d->dtype != DARTKV_F16 && d->dtype != DARTKV_BF16) return 0;
-  if (d->md_dtype != d->dtype || q_dtype != d->dtype) return 0;
+  if ((d->md_dtype != DARTKV_F16 && d->md_dtype != DARTKV_BF16) || q_dtype != d->dtype) return 0;
   if (d->value_bits != 2 || (d->value_group != 64 && d->value_group != 128)) return 0;
   if (d->key_mode == DARTKV_QUANTIZED_PAGE && d->key_bits != 2) return 0;
   if (d->key_page_bytes % 16 || d->key_page_bytes > kPageBytesK) return 0;   // at most 32 promoted channels
@@ -519,22 +520,36 @@ int dartkv_decode_fused32_supported(const dartkv_cache_desc* d, int q_dtype, int
   return 1;
 }
 
-// every (dtype, value groups, promoted count) variant of the kernel
+// every (cache dtype, metadata dtype, value groups, promoted count) variant of the kernel; a cache whose metadata
+// dtype differs from its dtype gets the promoted counts 0 and 32 specialized, the others read the count at run time
 using FusedKernel = void (*)(dartkv_cache_desc, FastArgs);
 template <int DT, int GN>
 static FusedKernel fused_variant_kp(int kp) {
   switch (kp) {
-    case 0: return decode_fused32_kernel<DT, GN, 0>;
-    case 8: return decode_fused32_kernel<DT, GN, 8>;
-    case 16: return decode_fused32_kernel<DT, GN, 16>;
-    case 24: return decode_fused32_kernel<DT, GN, 24>;
-    case 32: return decode_fused32_kernel<DT, GN, 32>;
-    default: return decode_fused32_kernel<DT, GN, -1>;
+    case 0: return decode_fused32_kernel<DT, DT, GN, 0>;
+    case 8: return decode_fused32_kernel<DT, DT, GN, 8>;
+    case 16: return decode_fused32_kernel<DT, DT, GN, 16>;
+    case 24: return decode_fused32_kernel<DT, DT, GN, 24>;
+    case 32: return decode_fused32_kernel<DT, DT, GN, 32>;
+    default: return decode_fused32_kernel<DT, DT, GN, -1>;
   }
 }
-static FusedKernel fused_variant(int dtype, int value_groups, int kp) {
-  if (dtype == DARTKV_BF16) return value_groups == 2 ? fused_variant_kp<DARTKV_BF16, 2>(kp) : fused_variant_kp<DARTKV_BF16, 1>(kp);
-  return value_groups == 2 ? fused_variant_kp<DARTKV_F16, 2>(kp) : fused_variant_kp<DARTKV_F16, 1>(kp);
+template <int DT, int MD, int GN>
+static FusedKernel fused_mixed_kp(int kp) {
+  switch (kp) {
+    case 0: return decode_fused32_kernel<DT, MD, GN, 0>;
+    case 32: return decode_fused32_kernel<DT, MD, GN, 32>;
+    default: return decode_fused32_kernel<DT, MD, GN, -1>;
+  }
+}
+static FusedKernel fused_variant(int dtype, int md, int value_groups, int kp) {
+  if (md == dtype) {
+    if (dtype == DARTKV_BF16) return value_groups == 2 ? fused_variant_kp<DARTKV_BF16, 2>(kp) : fused_variant_kp<DARTKV_BF16, 1>(kp);
+    return value_groups == 2 ? fused_variant_kp<DARTKV_F16, 2>(kp) : fused_variant_kp<DARTKV_F16, 1>(kp);
+  }
+  if (dtype == DARTKV_BF16)
+    return value_groups == 2 ? fused_mixed_kp<DARTKV_BF16, DARTKV_F16, 2>(kp) : fused_mixed_kp<DARTKV_BF16, DARTKV_F16, 1>(kp);
+  return value_groups == 2 ? fused_mixed_kp<DARTKV_F16, DARTKV_BF16, 2>(kp) : fused_mixed_kp<DARTKV_F16, DARTKV_BF16, 1>(kp);
 }
 
 int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, int q_dtype, int query_heads, float scale,
@@ -553,16 +568,17 @@ int dartkv_decode_fused32_launch(const dartkv_cache_desc* d, const void* query, 
     DARTKV_CUDA_OK(cudaGetDevice(&device));
     if (device < 0 || device >= 64 || !ready[device].load(std::memory_order_acquire)) {
       for (int dt : {DARTKV_BF16, DARTKV_F16})
-        for (int gn : {1, 2})
-          for (int kp : {-1, 0, 8, 16, 24, 32})
-            DARTKV_CUDA_OK(cudaFuncSetAttribute(fused_variant(dt, gn, kp), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                (int)kFusedSmemBytes));
+        for (int md : {DARTKV_BF16, DARTKV_F16})
+          for (int gn : {1, 2})
+            for (int kp : {-1, 0, 8, 16, 24, 32})
+              DARTKV_CUDA_OK(cudaFuncSetAttribute(fused_variant(dt, md, gn, kp), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)kFusedSmemBytes));
       if (device >= 0 && device < 64) ready[device].store(true, std::memory_order_release);
     }
   }
   const int promoted = d->key_mode == DARTKV_MIXED_PAGE ? d->promoted : 0;
   const int kp = (promoted % 8 == 0 && promoted <= 32) ? promoted : -1;
-  fused_variant(d->dtype, d->value_groups, kp)<<<grid, kThreads, kFusedSmemBytes, stream>>>(*d, a);
+  fused_variant(d->dtype, d->md_dtype, d->value_groups, kp)<<<grid, kThreads, kFusedSmemBytes, stream>>>(*d, a);
   DARTKV_LAUNCH_OK("decode_fused32_kernel");
   return DARTKV_OK;
 }

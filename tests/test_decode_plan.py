@@ -92,7 +92,7 @@ def test_other_geometries_take_the_general_tensor_core_kernel():
     d.md_dtype = _lib.F16                                                    # fp16 metadata beside a bf16 cache
     assert plan(d, _lib.BF16, 8, _lib.DEQUANT_PER_OP, 5000).kernel == 1     # the per-op kernel casts its operands
     assert plan(d, _lib.BF16, 8, _lib.DEQUANT_FP32, 5000).kernel == 3
-    assert plan(d, _lib.BF16, 8, _lib.DEQUANT_FUSED, 5000).kernel == 0
+    assert plan(d, _lib.BF16, 8, _lib.DEQUANT_FUSED, 5000).kernel == 2
 
 
 def test_plan_argument_errors():

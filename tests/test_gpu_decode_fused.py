@@ -20,8 +20,9 @@ pytestmark = pytest.mark.gpu
 
 
 def run_case(dtype, *, batch=2, heads=2, hq=8, tokens=32 + 5 * 128 + 77, chunks=None, seed=0, outliers=True,
-             data_scale=1.0, generic_bound=1e-4, **cfg):
+             data_scale=1.0, generic_bound=1e-4, metadata=None, **cfg):
     tag = DT_TAG[dtype]
+    metadata = metadata or dtype
     keys, values, query = make_kvq(seed, batch, heads, tokens, 128, query_heads=hq, dtype=dtype,
                                    outlier_fraction=0.05 if outliers else 0.0)
     if data_scale != 1.0:
@@ -29,8 +30,8 @@ def run_case(dtype, *, batch=2, heads=2, hq=8, tokens=32 + 5 * 128 + 77, chunks=
         values = (values.float() * data_scale).to(dtype)
     base = dict(bits=2, page_size=128, key_group_size=128, value_group_size=64, sink_tokens=32, hold_partial_pages=True)
     base.update(cfg)
-    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=dtype, **base))
-    oracle = orc.OracleCache(orc.CacheConfig(metadata_dtype=tag, **base), tag)
+    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=metadata, **base))
+    oracle = orc.OracleCache(orc.CacheConfig(metadata_dtype=DT_TAG[metadata], **base), tag)
     start = 0
     for chunk in chunks or [tokens]:
         cache.append(keys[:, :, start:start + chunk].cuda(), values[:, :, start:start + chunk].cuda())
@@ -58,6 +59,25 @@ def run_case(dtype, *, batch=2, heads=2, hq=8, tokens=32 + 5 * 128 + 77, chunks=
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_headline_geometry(dtype):
     run_case(dtype, promote_ratio=0.25, chunks=[32, 128, 128, 128, 128, 128, 77])
+
+
+@pytest.mark.parametrize("dtype,metadata", [(torch.bfloat16, torch.float16), (torch.float16, torch.bfloat16)])
+def test_metadata_dtype_differs_from_the_cache_dtype(dtype, metadata):
+    # fp16 scales and zero points beside a bf16 cache is the reference's default (src/dart/cache.py:57)
+    import ctypes
+
+    from dartkv_b200 import _lib
+
+    run_case(dtype, metadata=metadata, seed=30, promote_ratio=0.25, chunks=[32, 128, 128, 128, 128, 128, 77])
+    got, oracle, query, tag = run_case(dtype, metadata=metadata, seed=31, chunks=[300, 449])
+    cache = dart.DartKVCache(dart.DartKVCacheConfig(metadata_dtype=metadata, bits=2, page_size=128, key_group_size=128,
+                                                    value_group_size=64, sink_tokens=32, hold_partial_pages=True))
+    keys, values, _ = make_kvq(31, 2, 2, 300, 128, query_heads=8, dtype=dtype)
+    cache.append(keys.cuda(), values.cuda())
+    info = _lib.DecodePlanInfo()
+    assert _lib.LIB.dartkv_decode_plan(ctypes.byref(cache.descriptor), _lib.DTYPE_CODE[dtype], 8, _lib.DEQUANT_FUSED, 300,
+                                       ctypes.byref(info)) == 0
+    assert info.kernel == 2      # the tensor-core kernel of this flavour, not the CUDA-core one
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
