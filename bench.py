@@ -781,7 +781,7 @@ def qwen3_decode(args) -> None:
     attach_dart_fused_attention(model)
     cfg = dart.DartKVCacheConfig(bits=2, promote_ratio=0.25, page_size=128, key_group_size=128, value_group_size=64,
                                  sink_tokens=32, hold_partial_pages=True, local_tokens=1, value_local_tokens=128,
-                                 metadata_dtype=torch.bfloat16)
+                                 metadata_dtype=torch.float16)
     gen = torch.Generator().manual_seed(3)
     prompt = torch.randint(0, config.vocab_size, (batch, prompt_len), generator=gen).to(device)
 
@@ -839,7 +839,7 @@ def qwen3_decode(args) -> None:
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "config4", "model": "Qwen3-8B architecture, random-init bf16 weights (std 0.02)",
                    "batch": batch, "prompt": prompt_len, "new_tokens": new_tokens,
-                   "cache": "2-bit + 0.25 promotion, page 128, groups 128/64, 32 sinks, local 1, value local 128, bf16 metadata"},
+                   "cache": "2-bit + 0.25 promotion, page 128, groups 128/64, 32 sinks, local 1, value local 128, fp16 metadata (the setting of the reference's benchmark script)"},
         "attention_share_of_step": hot_ms / ms, "hot_path_ms_per_step": hot_ms / new_tokens,
         "reference_gpu": reference_gpu,
         "compression_ratio": cache.compression_ratio, "gpu_launches": int(launches), "clocks": clocks.summary(),
@@ -873,7 +873,7 @@ def reference_qwen3_decode(config, prompt, device, new_tokens: int) -> dict:
         model = ref_attach(model.eval())
         cfg = dart_ref.DartKVCacheConfig(bits=2, promote_ratio=0.25, page_size=128, key_group_size=128,
                                          value_group_size=64, sink_tokens=32, hold_partial_pages=True, local_tokens=1,
-                                         value_local_tokens=128, metadata_dtype=torch.bfloat16)
+                                         value_local_tokens=128, metadata_dtype=torch.float16)
         cache = RefCache(cfg)
         with torch.no_grad():
             logits = model(prompt, past_key_values=cache, use_cache=True).logits[:, -1]
