@@ -256,7 +256,7 @@ __device__ __forceinline__ void values_to_tile(const uint8_t* st, const WideGeom
   const bool group_per_word = (64 / kPieces) >> group_shift;
 #pragma unroll
   for (int p = 0; p < kPieces; ++p) {
-    const int q = (p + tok) & (kPieces - 1);   // lanes start at different pieces: fewer bank conflicts
+    const int q = p;
     const uint4 words = *reinterpret_cast<const uint4*>(codes + 16 * q);
     const uint32_t ws[4] = {words.x, words.y, words.z, words.w};
 #pragma unroll

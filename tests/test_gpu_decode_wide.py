@@ -137,5 +137,15 @@ def test_metadata_dtype_differs_from_the_cache_dtype(dtype, metadata, cfg):
     run_case(dtype, metadata=metadata, seed=101, flavour=_lib.DEQUANT_FP32, **cfg)
 
 
+def test_corners_of_the_supported_geometry():
+    # smallest groups with the widest codes (largest staged chunks: one block per SM), every channel promoted,
+    # one value group per token, a single query head per KV head
+    run_case(torch.bfloat16, bits=8, key_group_size=16, value_group_size=16, seed=110)
+    run_case(torch.float16, bits=4, key_group_size=16, value_group_size=128, seed=111)
+    run_case(torch.bfloat16, bits=4, promote_ratio=1.0, seed=112)
+    run_case(torch.float16, bits=8, promote_ratio=0.5, key_group_size=32, seed=113)
+    run_case(torch.bfloat16, bits=4, heads=4, hq=4, seed=114)
+
+
 def test_headline_geometry_keeps_its_own_kernels():
     run_case(torch.bfloat16, promote_ratio=0.25, seed=99, expect_kernel=1)
