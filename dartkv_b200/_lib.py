@@ -32,7 +32,7 @@ EXPORTS = (
     "dartkv_decode_attention", "dartkv_decode_plan", "dartkv_decode_status", "dartkv_builtin_scratch_bytes",
     "dartkv_decode_attention_builtin_scratch", "dartkv_shard_range", "dartkv_decode_split_override",
     "dartkv_lifecycle_plan", "dartkv_cache_append_step", "dartkv_decode_attention_scatter",
-    "dartkv_decode_attention_padded",
+    "dartkv_decode_attention_padded", "dartkv_cache_append_device_planned",
 )
 
 
@@ -146,6 +146,8 @@ def _load() -> ctypes.CDLL:
     lib.dartkv_lifecycle_plan.argtypes = [POINTER(LifecycleConfig), POINTER(LifecycleStateC), i32, POINTER(AppendPlan)]
     lib.dartkv_cache_append_step.argtypes = [POINTER(CacheDesc), POINTER(LifecycleConfig), POINTER(LifecycleStateC), p, p,
                                              i32, i64, i64, i64, p, p, POINTER(AppendPlan), p]
+    lib.dartkv_cache_append_device_planned.argtypes = [POINTER(CacheDesc), POINTER(LifecycleConfig), p, p, i32, i64, i64, i64,
+                                                       p, p]
     lib.dartkv_shard_range.argtypes = [i32, i32, i32, i32, POINTER(Shard)]
     lib.dartkv_decode_attention_builtin_scratch.argtypes = [POINTER(CacheDesc), p, i32, i32, c_float, i32, i32, p, p]
     for name in EXPORTS:

@@ -211,7 +211,7 @@ class DartKVCache:
                 "v_sink": torch.empty((batch, heads, max(1, cfg.sink_tokens), head_dim), dtype=dtype, device=device),
                 "k_ring": torch.empty((batch, heads, d.ring_tokens, head_dim), dtype=dtype, device=device),
                 "v_ring": torch.empty((batch, heads, d.ring_tokens, head_dim), dtype=dtype, device=device),
-                "state": torch.zeros(8, dtype=torch.int32, device=device),
+                "state": torch.zeros(32, dtype=torch.int32, device=device),   # 8 state words, then plan scratch
                 "nonfinite": torch.zeros(1, dtype=torch.int32, device=device),
             }
         hint = self._max_tokens_hint or max(2 * first_chunk, first_chunk + 1024)
@@ -336,6 +336,79 @@ class DartKVCache:
                     keys.stride(2), ptr(idx), ptr(self._pools["nonfinite"]), stream_ptr(device)))
             self._c_state = state
         # the step was accepted: bring the host-side segment bookkeeping up to date from its plan
+        life = self._life
+        if plan.sink_copy:
+            life.sink_pieces.append((plan.chunk_start, plan.sink_copy))
+        page = cfg.page_size
+        for i in range(plan.num_pages):
+            life.pages.append((plan.page_token_start + i * page,
+                               plan.last_page_tokens if i == plan.num_pages - 1 else page))
+        life.seen = plan.seen_after
+        life.k_packed_end = plan.k_packed_end_after
+        life.v_packed_end = plan.v_packed_end_after
+        self._layout_version += 1
+        self._invalidate_page_descriptors()
+
+    def append_device_planned(self, key_states: torch.Tensor, value_states: torch.Tensor) -> None:
+        """``append`` whose step is planned on the device: every launch has the same shape whatever the state of the
+        cache, so the call can sit in a CUDA graph (together with the decode attention) that is captured once and
+        replayed for every new token.  No counterpart in the reference, whose page bookkeeping is Python.
+
+        For the held-page lifecycle on the geometry of the page kernels (``hold_partial_pages=True``, no local
+        tokens, head_dim 128, 16-bit data, 128-token pages and key groups, magnitude selection) and an initialized
+        cache (the first chunk goes through ``append``).  Pools cannot grow under a captured graph: create the cache
+        with ``max_tokens``; outside a capture the pools grow here as in ``append``.  Under a capture this method
+        records the launches once; on every replay call ``advance_device_planned(chunk)`` so that the host-side
+        bookkeeping follows.
+        """
+
+        self._validate_inputs(key_states, value_states)
+        device = require_cuda(key_states, value_states)
+        if self._desc is None:
+            raise ValueError("the first chunk of a cache goes through append(); device-planned appends follow it")
+        keys, values = key_states.detach(), value_states.detach()
+        if keys.stride(-1) != 1 or values.stride() != keys.stride():
+            raise ValueError("device-planned appends take key and value chunks with equal strides and a contiguous head_dim")
+        cfg = self.config
+        if cfg.promote_ratio > 0.0 and cfg.channel_selection != "magnitude":
+            raise ValueError("device-planned appends select promoted channels by magnitude")
+        chunk = keys.shape[2]
+        state = self._plan_device_step(chunk)
+        d = self._desc
+        with device_guard(device):
+            check(LIB.dartkv_cache_append_device_planned(
+                ctypes.byref(d), ctypes.byref(self._c_cfg), ptr(keys), ptr(values), chunk, keys.stride(0), keys.stride(1),
+                keys.stride(2), ptr(self._pools["nonfinite"]), stream_ptr(device)))
+        self._commit_step(state)
+
+    def advance_device_planned(self, chunk: int) -> None:
+        """Host-side bookkeeping of one device-planned append of ``chunk`` tokens (the device plans the same step
+        from its own copy of the state): call it once per replay of a graph that holds ``append_device_planned``."""
+
+        self._commit_step(self._plan_device_step(chunk))
+
+    def _plan_device_step(self, chunk: int):
+        """The step's plan on a copy of the lifecycle state (left in ``self._plan``), pools grown if it needs that."""
+
+        cfg, d, plan = self.config, self._desc, self._plan
+        state = _lib.LifecycleStateC(self._c_state.seen, self._c_state.k_packed_end, self._c_state.v_packed_end,
+                                     self._c_state.key_pages)
+        check(LIB.dartkv_lifecycle_plan(ctypes.byref(self._c_cfg), ctypes.byref(state), chunk, ctypes.byref(plan)))
+        rows_needed = plan.value_end - cfg.sink_tokens if plan.value_end > plan.value_begin else 0
+        if plan.key_pages_after > d.max_key_pages or rows_needed > d.max_value_tokens:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("the cache pools are too small for this step and cannot grow under a graph capture: "
+                                   "create the cache with max_tokens")
+            self._ensure_capacity(
+                2 * plan.key_pages_after if plan.key_pages_after > d.max_key_pages else d.max_key_pages,
+                2 * rows_needed if rows_needed > d.max_value_tokens else d.max_value_tokens)
+        return state
+
+    def _commit_step(self, state) -> None:
+        """The step in ``self._plan`` was accepted: bring the host-side bookkeeping up to date."""
+
+        cfg, plan = self.config, self._plan
+        self._c_state = state
         life = self._life
         if plan.sink_copy:
             life.sink_pieces.append((plan.chunk_start, plan.sink_copy))

@@ -180,9 +180,19 @@ __device__ __forceinline__ double any_abs_as_double(uint32_t magnitude) {
 template <int DT, int KBITS, int TQ>
 __global__ void __launch_bounds__(64 * TQ) fast_key_pages_kernel(dartkv_cache_desc d, RowSource src, int first_slot,
                                                                  int num_pages, int page_token_start,
-                                                                 const int32_t* __restrict__ indices, int32_t* nonfinite) {
+                                                                 const int32_t* __restrict__ indices, int32_t* nonfinite,
+                                                                 const dartkv_append_plan* device_plan) {
   using P = Pack16<DT>;
   constexpr int TOK = kP / TQ;   // tokens per thread and pass
+  if (device_plan) {
+    // the step was planned on the device (the grid is the most pages such a step can bring): take the step's
+    // numbers from there; blocks beyond its pages have nothing to do
+    first_slot = device_plan->first_page;
+    num_pages = device_plan->num_pages;
+    page_token_start = device_plan->page_token_start;
+    src.chunk_start = device_plan->chunk_start;
+    if ((int)blockIdx.y >= num_pages) return;
+  }
   __shared__ __align__(16) uint32_t s_page[kP * 64];   // [token][channel pair]
   __shared__ __align__(16) uint32_t s_key[kD];
   __shared__ uint32_t s_part[TQ > 1 ? 3 * TQ * 64 : 1];      // [min | max | smallest magnitude][split][pair]
@@ -400,9 +410,15 @@ __global__ void __launch_bounds__(64 * TQ) fast_key_pages_kernel(dartkv_cache_de
 // value_group / 16.
 template <int DT, int VBITS>
 __global__ void __launch_bounds__(256) fast_value_rows_kernel(dartkv_cache_desc d, RowSource src, int value_begin,
-                                                              int count, int lanes_per_group, int32_t* nonfinite) {
+                                                              int count, int lanes_per_group, int32_t* nonfinite,
+                                                              const dartkv_append_plan* device_plan) {
   using P = Pack16<DT>;
   constexpr int STEPS = 2;
+  if (device_plan) {   // planned on the device: the grid covers the most rows such a step can pack
+    value_begin = device_plan->value_begin;
+    count = device_plan->value_end - device_plan->value_begin;
+    src.chunk_start = device_plan->chunk_start;
+  }
   const int bh = blockIdx.y, lane = threadIdx.x & 31;
   const int sub = lane >> 3, part = lane & 7;   // row within the step, 16-channel slice of the row
   const int first = (blockIdx.x * 8 + (threadIdx.x >> 5)) * (4 * STEPS);
@@ -500,56 +516,62 @@ int dartkv_append_fast_supported(const dartkv_cache_desc* d, const dartkv_append
 
 template <int DT, int TQ>
 static int launch_keys_split(const dartkv_cache_desc& d, const dartkv_append_plan& p, const RowSource& src,
-                             const int32_t* indices, int32_t* nonfinite, cudaStream_t stream) {
+                             const int32_t* indices, int32_t* nonfinite, cudaStream_t stream,
+                             const dartkv_append_plan* device_plan) {
   dim3 grid(d.batch * d.kv_heads, p.num_pages);
   if (d.key_mode == DARTKV_MIXED_PAGE)
-    fast_key_pages_kernel<DT, 0, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+    fast_key_pages_kernel<DT, 0, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite, device_plan);
   else if (d.key_bits == 2)
-    fast_key_pages_kernel<DT, 2, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+    fast_key_pages_kernel<DT, 2, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite, device_plan);
   else if (d.key_bits == 4)
-    fast_key_pages_kernel<DT, 4, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+    fast_key_pages_kernel<DT, 4, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite, device_plan);
   else
-    fast_key_pages_kernel<DT, 8, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite);
+    fast_key_pages_kernel<DT, 8, TQ><<<grid, 64 * TQ, 0, stream>>>(d, src, p.first_page, p.num_pages, p.page_token_start, indices, nonfinite, device_plan);
   DARTKV_LAUNCH_OK("fast_key_pages_kernel");
   return DARTKV_OK;
 }
 
 template <int DT>
 static int launch_keys(const dartkv_cache_desc& d, const dartkv_append_plan& p, const RowSource& src,
-                       const int32_t* indices, int32_t* nonfinite, cudaStream_t stream) {
-  return launch_keys_split<DT, APPEND_KEY_SPLITS>(d, p, src, indices, nonfinite, stream);
+                       const int32_t* indices, int32_t* nonfinite, cudaStream_t stream,
+                       const dartkv_append_plan* device_plan) {
+  return launch_keys_split<DT, APPEND_KEY_SPLITS>(d, p, src, indices, nonfinite, stream, device_plan);
 }
 
 template <int DT>
 static int launch_values(const dartkv_cache_desc& d, const dartkv_append_plan& p, const RowSource& src,
-                         int32_t* nonfinite, cudaStream_t stream) {
+                         int32_t* nonfinite, cudaStream_t stream, const dartkv_append_plan* device_plan) {
   const int count = p.value_end - p.value_begin;
   DARTKV_REQUIRE(d.batch * d.kv_heads <= 65535, "batch * kv_heads above 65535");
   const dim3 blocks((unsigned)((count + 63) / 64), d.batch * d.kv_heads);   // 8 warps per block, 8 rows per warp
   const int lpg = d.value_group / 16;
   if (d.value_bits == 2)
-    fast_value_rows_kernel<DT, 2><<<blocks, 256, 0, stream>>>(d, src, p.value_begin, count, lpg, nonfinite);
+    fast_value_rows_kernel<DT, 2><<<blocks, 256, 0, stream>>>(d, src, p.value_begin, count, lpg, nonfinite, device_plan);
   else if (d.value_bits == 4)
-    fast_value_rows_kernel<DT, 4><<<blocks, 256, 0, stream>>>(d, src, p.value_begin, count, lpg, nonfinite);
+    fast_value_rows_kernel<DT, 4><<<blocks, 256, 0, stream>>>(d, src, p.value_begin, count, lpg, nonfinite, device_plan);
   else
-    fast_value_rows_kernel<DT, 8><<<blocks, 256, 0, stream>>>(d, src, p.value_begin, count, lpg, nonfinite);
+    fast_value_rows_kernel<DT, 8><<<blocks, 256, 0, stream>>>(d, src, p.value_begin, count, lpg, nonfinite, device_plan);
   DARTKV_LAUNCH_OK("fast_value_rows_kernel");
   return DARTKV_OK;
 }
 
+// device_plan (optional): the step's plan in device memory, written by a kernel earlier on the stream; *p then
+// only sizes the grids (the most pages / rows the step can bring)
 int dartkv_append_fast_keys(const dartkv_cache_desc* d, const dartkv_append_plan* p, const void* keys, int64_t sb,
-                            int64_t sh, int64_t st, const int32_t* indices, int32_t* nonfinite, cudaStream_t stream) {
+                            int64_t sh, int64_t st, const int32_t* indices, int32_t* nonfinite, cudaStream_t stream,
+                            const dartkv_append_plan* device_plan) {
   if (p->num_pages == 0) return DARTKV_OK;
   DARTKV_REQUIRE(p->num_pages <= 65535, "too many pages in one append (limit 65535)");
   RowSource src{keys, d->k_ring, sb, sh, st, p->chunk_start, d->ring_tokens, d->kv_heads};
-  return d->dtype == DARTKV_F16 ? launch_keys<DARTKV_F16>(*d, *p, src, indices, nonfinite, stream)
-                                : launch_keys<DARTKV_BF16>(*d, *p, src, indices, nonfinite, stream);
+  return d->dtype == DARTKV_F16 ? launch_keys<DARTKV_F16>(*d, *p, src, indices, nonfinite, stream, device_plan)
+                                : launch_keys<DARTKV_BF16>(*d, *p, src, indices, nonfinite, stream, device_plan);
 }
 
 int dartkv_append_fast_values(const dartkv_cache_desc* d, const dartkv_append_plan* p, const void* values, int64_t sb,
-                              int64_t sh, int64_t st, int32_t* nonfinite, cudaStream_t stream) {
+                              int64_t sh, int64_t st, int32_t* nonfinite, cudaStream_t stream,
+                              const dartkv_append_plan* device_plan) {
   if (p->value_end <= p->value_begin) return DARTKV_OK;
   RowSource src{values, d->v_ring, sb, sh, st, p->chunk_start, d->ring_tokens, d->kv_heads};
-  return d->dtype == DARTKV_F16 ? launch_values<DARTKV_F16>(*d, *p, src, nonfinite, stream)
-                                : launch_values<DARTKV_BF16>(*d, *p, src, nonfinite, stream);
+  return d->dtype == DARTKV_F16 ? launch_values<DARTKV_F16>(*d, *p, src, nonfinite, stream, device_plan)
+                                : launch_values<DARTKV_BF16>(*d, *p, src, nonfinite, stream, device_plan);
 }

@@ -90,9 +90,22 @@ constexpr int kCopyRows = 8;   // rows per block of the dense copy
 // the ring; copy row r enumerates only the chunk tokens that can need a copy: the sink part, then
 // [ring_first, chunk end).  Block (0,0,0) also publishes the page table rows and the state words of the step
 // (nothing of this step reads them; later launches on the stream do).
+// With device_plan the step was planned on the device: the plan, the first ring token and the row count come from
+// there (the grid is sized for the most rows such a step can copy).
 __global__ void copy_dense_kernel(dartkv_cache_desc d, dartkv_append_plan p, const void* keys, const void* values,
                                   int64_t sb, int64_t sh, int64_t st, int ring_first, int rows, int vector_ok,
-                                  int32_t* nonfinite) {
+                                  int32_t* nonfinite, const dartkv_append_plan* device_plan) {
+  if (device_plan) {
+    p = *device_plan;
+    const int chunk_end = p.chunk_start + p.chunk_tokens;
+    const bool copies = p.sink_copy > 0 || p.ring_begin < chunk_end || p.value_end < chunk_end;
+    ring_first = p.chunk_tokens;
+    rows = 0;
+    if (copies) {
+      ring_first = max(p.sink_copy, min(p.ring_begin, max(p.value_end, p.chunk_start)) - p.chunk_start);
+      rows = p.sink_copy + (p.chunk_tokens - ring_first);
+    }
+  }
   if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) publish_append(d, p);
   const int bh = blockIdx.x, side = blockIdx.z;
   const int r_begin = blockIdx.y * kCopyRows, r_end = min(rows, r_begin + kCopyRows);
@@ -413,9 +426,11 @@ __global__ void page_to_ring_kernel(dartkv_cache_desc d, int slot_index, int pag
 // Common geometry (head_dim 128, 16-bit data, full 128-token pages, key group 128): append_fast.cu.
 int dartkv_append_fast_supported(const dartkv_cache_desc* d, const dartkv_append_plan* p, int64_t st);
 int dartkv_append_fast_keys(const dartkv_cache_desc* d, const dartkv_append_plan* p, const void* keys, int64_t sb,
-                            int64_t sh, int64_t st, const int32_t* indices, int32_t* nonfinite, cudaStream_t stream);
+                            int64_t sh, int64_t st, const int32_t* indices, int32_t* nonfinite, cudaStream_t stream,
+                            const dartkv_append_plan* device_plan = nullptr);
 int dartkv_append_fast_values(const dartkv_cache_desc* d, const dartkv_append_plan* p, const void* values, int64_t sb,
-                              int64_t sh, int64_t st, int32_t* nonfinite, cudaStream_t stream);
+                              int64_t sh, int64_t st, int32_t* nonfinite, cudaStream_t stream,
+                              const dartkv_append_plan* device_plan = nullptr);
 
 static int validate_desc(const dartkv_cache_desc* d) {
   DARTKV_REQUIRE(d != nullptr, "null descriptor");
@@ -503,7 +518,7 @@ extern "C" int dartkv_cache_append(const dartkv_cache_desc* desc, const dartkv_a
     const int vector_ok = (d.head_dim * esize) % 16 == 0 && (stride_b * esize) % 16 == 0 && (stride_h * esize) % 16 == 0 &&
                           (stride_t * esize) % 16 == 0 && ((uintptr_t)keys | (uintptr_t)values) % 16 == 0;
     copy_dense_kernel<<<dim3(rows > 0 ? bh : 1, row_blocks, rows > 0 ? 2 : 1), 128, 0, stream>>>(
-        d, p, keys, values, stride_b, stride_h, stride_t, ring_first, rows, vector_ok, nonfinite);
+        d, p, keys, values, stride_b, stride_h, stride_t, ring_first, rows, vector_ok, nonfinite, nullptr);
     DARTKV_LAUNCH_OK("copy_dense_kernel");
   }
   return DARTKV_OK;
@@ -531,22 +546,18 @@ extern "C" int dartkv_cache_materialize(const dartkv_cache_desc* desc, int side,
 // The integer bookkeeping of the reference's cache lifecycle (src/dart/cache.py:168-190, 403-470) as a host
 // function: which chunk tokens go to the sink rows, which become key pages, which value rows get packed and what
 // stays dense in the ring.  Pages are appended in sequence order, so the state is four integers.
-extern "C" int dartkv_lifecycle_plan(const dartkv_lifecycle_config* cfg, dartkv_lifecycle_state* state,
-                                     int chunk_tokens, dartkv_append_plan* plan) {
-  DARTKV_REQUIRE(cfg != nullptr && state != nullptr && plan != nullptr, "lifecycle_plan received a null pointer");
-  DARTKV_REQUIRE(chunk_tokens > 0, "key/value sequence and head dimensions must be non-empty");
-  DARTKV_REQUIRE(cfg->page_size > 0 && cfg->sink_tokens >= 0 && cfg->local_tokens >= 0 && cfg->value_local_tokens >= 0,
-                 "bad lifecycle configuration");
-  const int page = cfg->page_size, sink_total = cfg->sink_tokens;
-  const int seen = state->seen;
-  DARTKV_REQUIRE((int64_t)seen + chunk_tokens < (1ll << 31) - 2 * page, "token count overflows 32 bits");
+// The arithmetic itself, shared by the host entry point and the planner kernel of device-planned appends.
+__host__ __device__ static inline void lifecycle_core(const dartkv_lifecycle_config& cfg, dartkv_lifecycle_state& state,
+                                                      int chunk_tokens, dartkv_append_plan& plan) {
+  const int page = cfg.page_size, sink_total = cfg.sink_tokens;
+  const int seen = state.seen;
   const int sink_copy = min(max(0, sink_total - seen), chunk_tokens);
   const int rest = chunk_tokens - sink_copy;
   const int rest_start = seen + sink_copy;
   const int chunk_end = seen + chunk_tokens;
   const int sink_filled_after = min(chunk_end, sink_total);
   // invariant: packed_end is the end of the packed range, or min(seen, sink_tokens) while nothing is packed
-  const int k_end = state->k_packed_end, v_end = state->v_packed_end;
+  const int k_end = state.k_packed_end, v_end = state.v_packed_end;
   const int pending_k = seen - k_end, pending_v = seen - v_end;
   int num_pages = 0, last_page_tokens = page;
   const int page_token_start = pending_k ? k_end : rest_start;
@@ -554,17 +565,17 @@ extern "C" int dartkv_lifecycle_plan(const dartkv_lifecycle_config* cfg, dartkv_
   int value_end = value_begin;
   int requantize = 0;
   if (rest > 0) {
-    if (cfg->value_local_tokens) {
+    if (cfg.value_local_tokens) {
       // keys page by page behind `local_tokens`, values token by token behind the newest `value_local_tokens`;
       // a one-token append right after a prompt that ended on a page boundary re-quantizes the last page
-      if (seen > 0 && pending_k == 0 && cfg->local_tokens == 1 && rest == 1 && state->key_pages > 0) requantize = 1;
+      if (seen > 0 && pending_k == 0 && cfg.local_tokens == 1 && rest == 1 && state.key_pages > 0) requantize = 1;
       const int stream = pending_k + rest;
-      const int local = seen == 0 ? 0 : cfg->local_tokens;
+      const int local = seen == 0 ? 0 : cfg.local_tokens;
       num_pages = max(0, stream - local) / page;
-      value_end = value_begin + max(0, pending_v + rest - cfg->value_local_tokens);
-    } else if (cfg->hold_partial_pages || cfg->local_tokens) {
+      value_end = value_begin + max(0, pending_v + rest - cfg.value_local_tokens);
+    } else if (cfg.hold_partial_pages || cfg.local_tokens) {
       const int stream = pending_k + rest;
-      num_pages = max(0, stream - cfg->local_tokens) / page;
+      num_pages = max(0, stream - cfg.local_tokens) / page;
       value_end = value_begin + num_pages * page;
     } else {
       num_pages = (rest + page - 1) / page;
@@ -574,32 +585,42 @@ extern "C" int dartkv_lifecycle_plan(const dartkv_lifecycle_config* cfg, dartkv_
   }
   int k_end_after;
   if (num_pages > 0) k_end_after = page_token_start + (num_pages - 1) * page + last_page_tokens;
-  else if (state->key_pages > 0) k_end_after = k_end;
+  else if (state.key_pages > 0) k_end_after = k_end;
   else k_end_after = sink_filled_after;
   int v_end_after;
   if (value_end > value_begin) v_end_after = value_end;
   else if (v_end > sink_total) v_end_after = v_end;
   else v_end_after = sink_filled_after;
-  plan->chunk_start = seen;
-  plan->chunk_tokens = chunk_tokens;
-  plan->sink_copy = sink_copy;
-  plan->first_page = state->key_pages;
-  plan->num_pages = num_pages;
-  plan->page_token_start = page_token_start;
-  plan->last_page_tokens = last_page_tokens;
-  plan->value_begin = value_begin;
-  plan->value_end = value_end;
-  plan->ring_begin = max(k_end_after, rest_start);
-  plan->reserved = 0;
-  plan->seen_after = chunk_end;
-  plan->k_packed_end_after = k_end_after;
-  plan->v_packed_end_after = v_end_after;
-  plan->key_pages_after = state->key_pages + num_pages;
-  plan->requantize_last_page = requantize;
-  state->seen = chunk_end;
-  state->k_packed_end = k_end_after;
-  state->v_packed_end = v_end_after;
-  state->key_pages += num_pages;
+  plan.chunk_start = seen;
+  plan.chunk_tokens = chunk_tokens;
+  plan.sink_copy = sink_copy;
+  plan.first_page = state.key_pages;
+  plan.num_pages = num_pages;
+  plan.page_token_start = page_token_start;
+  plan.last_page_tokens = last_page_tokens;
+  plan.value_begin = value_begin;
+  plan.value_end = value_end;
+  plan.ring_begin = max(k_end_after, rest_start);
+  plan.reserved = 0;
+  plan.seen_after = chunk_end;
+  plan.k_packed_end_after = k_end_after;
+  plan.v_packed_end_after = v_end_after;
+  plan.key_pages_after = state.key_pages + num_pages;
+  plan.requantize_last_page = requantize;
+  state.seen = chunk_end;
+  state.k_packed_end = k_end_after;
+  state.v_packed_end = v_end_after;
+  state.key_pages += num_pages;
+}
+
+extern "C" int dartkv_lifecycle_plan(const dartkv_lifecycle_config* cfg, dartkv_lifecycle_state* state,
+                                     int chunk_tokens, dartkv_append_plan* plan) {
+  DARTKV_REQUIRE(cfg != nullptr && state != nullptr && plan != nullptr, "lifecycle_plan received a null pointer");
+  DARTKV_REQUIRE(chunk_tokens > 0, "key/value sequence and head dimensions must be non-empty");
+  DARTKV_REQUIRE(cfg->page_size > 0 && cfg->sink_tokens >= 0 && cfg->local_tokens >= 0 && cfg->value_local_tokens >= 0,
+                 "bad lifecycle configuration");
+  DARTKV_REQUIRE((int64_t)state->seen + chunk_tokens < (1ll << 31) - 2 * cfg->page_size, "token count overflows 32 bits");
+  lifecycle_core(*cfg, *state, chunk_tokens, *plan);
   return DARTKV_OK;
 }
 
@@ -625,5 +646,62 @@ extern "C" int dartkv_cache_append_step(const dartkv_cache_desc* desc, const dar
   rc = dartkv_cache_append(desc, &plan, keys, values, stride_b, stride_h, stride_t, indices, nonfinite, stream);
   if (rc) return rc;
   *state = next;
+  return DARTKV_OK;
+}
+
+// ---------------------------------------------------------------------------- device-planned append
+// The same step with nothing decided on the host: a one-thread kernel reads the lifecycle state the cache keeps on
+// the device (desc->state[0..3]), runs the planner above and leaves the plan in desc->state[8..23]; the page, value
+// row and copy kernels that follow on the stream read it there.  Their grids cover the most a chunk of this length
+// can bring, blocks beyond the step's real work return at once.  Every launch has the same shape whatever the
+// state, so a decode step (append + attention) can be captured in a CUDA graph once and replayed token after token.
+__global__ void plan_append_kernel(dartkv_cache_desc d, dartkv_lifecycle_config cfg, int chunk_tokens) {
+  dartkv_lifecycle_state state{d.state[0], d.state[2], d.state[3], d.state[1]};
+  dartkv_append_plan plan;
+  lifecycle_core(cfg, state, chunk_tokens, plan);
+  *reinterpret_cast<dartkv_append_plan*>(d.state + 8) = plan;
+}
+
+extern "C" int dartkv_cache_append_device_planned(const dartkv_cache_desc* desc, const dartkv_lifecycle_config* cfg,
+                                                  const void* keys, const void* values, int chunk_tokens,
+                                                  int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                                                  int32_t* nonfinite, void* stream_) {
+  int rc = validate_desc(desc);
+  if (rc) return rc;
+  DARTKV_REQUIRE(cfg != nullptr && keys != nullptr && values != nullptr, "append received a null pointer");
+  DARTKV_REQUIRE(chunk_tokens > 0 && chunk_tokens <= 32768, "device-planned appends take 1..32768 tokens");
+  DARTKV_REQUIRE(cfg->hold_partial_pages && cfg->local_tokens == 0 && cfg->value_local_tokens == 0,
+                 "device-planned appends serve the held-page lifecycle (hold_partial_pages, no local tokens)");
+  DARTKV_REQUIRE(cfg->page_size == desc->page_size && cfg->sink_tokens == desc->sink_tokens,
+                 "lifecycle configuration and descriptor disagree");
+  const dartkv_cache_desc& d = *desc;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  // the most this chunk can bring: pending tokens (fewer than a page) may complete one page more
+  dartkv_append_plan most{};
+  most.chunk_tokens = chunk_tokens;
+  most.num_pages = chunk_tokens / d.page_size + 1;
+  most.last_page_tokens = d.page_size;
+  most.value_begin = 0;
+  most.value_end = most.num_pages * d.page_size;
+  const int fast = dartkv_append_fast_supported(desc, &most, stride_t);
+  DARTKV_REQUIRE(fast == 3 && stride_b % 8 == 0 && stride_h % 8 == 0 && ((uintptr_t)keys | (uintptr_t)values) % 16 == 0,
+                 "device-planned appends need the geometry of the page kernels (head_dim 128, 16-bit data, 128-token "
+                 "pages and key groups, aligned inputs)");
+  const dartkv_append_plan* device_plan = reinterpret_cast<const dartkv_append_plan*>(d.state + 8);
+  plan_append_kernel<<<1, 1, 0, stream>>>(d, *cfg, chunk_tokens);
+  DARTKV_LAUNCH_OK("plan_append_kernel");
+  rc = dartkv_append_fast_keys(desc, &most, keys, stride_b, stride_h, stride_t, nullptr, nonfinite, stream, device_plan);
+  if (rc) return rc;
+  rc = dartkv_append_fast_values(desc, &most, values, stride_b, stride_h, stride_t, nonfinite, stream, device_plan);
+  if (rc) return rc;
+  const int bh = d.batch * d.kv_heads;
+  const int row_blocks = max(1, ceil_div(chunk_tokens, kCopyRows));
+  DARTKV_REQUIRE(row_blocks <= 65535, "append chunks this long must be split by the caller");
+  const int esize = dartkv_dtype_size(d.dtype);
+  const int vector_ok = (d.head_dim * esize) % 16 == 0 && (stride_b * esize) % 16 == 0 && (stride_h * esize) % 16 == 0 &&
+                        (stride_t * esize) % 16 == 0;
+  copy_dense_kernel<<<dim3(bh, row_blocks, 2), 128, 0, stream>>>(d, most, keys, values, stride_b, stride_h, stride_t, 0, 0,
+                                                                 vector_ok, nonfinite, device_plan);
+  DARTKV_LAUNCH_OK("copy_dense_kernel");
   return DARTKV_OK;
 }

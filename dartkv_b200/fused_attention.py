@@ -21,11 +21,14 @@ from .page_table import DartPageRun, DartPageTable
 
 def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional[float] = None,
                      flavour: int = _lib.DEQUANT_PER_OP, out: Optional[torch.Tensor] = None,
-                     peer_gather=None, row_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     peer_gather=None, row_start: Optional[torch.Tensor] = None,
+                     token_capacity: Optional[int] = None) -> torch.Tensor:
     """One query token per (batch, query head): ``query`` and the result are ``[B, Hq, D]``.
 
     ``row_start`` (``[B]`` integers, first live token of every batch row) serves left-padded batches: the tokens
     before a row's first live one get no weight and the pages that hold only such tokens are not read.
+    ``token_capacity`` sizes the work split for that many tokens instead of the current length (the kernels read
+    the exact length on the device): a call captured in a CUDA graph stays valid while the cache grows up to it.
 
     With ``peer_gather`` (a ``dartkv_b200.sharding.PeerGather``) the kernels also deliver this rank's rows to every
     rank of the node and the gathered tensor ``[B_total, Hq_total, D]`` of the step is returned instead.
@@ -34,6 +37,10 @@ def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional
     if cache.shape is None or cache.seen_tokens == 0:
         raise ValueError("cache is empty")
     batch, kv_heads, seen, head_dim = cache.shape
+    if token_capacity is not None:
+        if token_capacity < seen:
+            raise ValueError("token_capacity must be at least the number of tokens in the cache")
+        seen = int(token_capacity)
     if query.ndim != 3 or query.shape[0] != batch or query.shape[-1] != head_dim:
         raise ValueError("query batch and head_dim must match the cache")
     if query.shape[1] % kv_heads:
@@ -61,7 +68,7 @@ def decode_attention(query: torch.Tensor, cache: DartKVCache, *, scale: Optional
         for first in range(0, rep, 4):
             part = grouped[:, :, first:first + 4].reshape(batch, -1, head_dim)
             result_view[:, :, first:first + 4] = decode_attention(part, cache, scale=scale, flavour=flavour,
-                                                                   row_start=row_start).view(
+                                                                   row_start=row_start, token_capacity=token_capacity).view(
                 batch, kv_heads, -1, head_dim)
         return result
     if out is None:
@@ -107,6 +114,8 @@ def fused_dart_attention(
     page_runs: Optional[Sequence[DartPageRun]] = None,
     flavour: int = _lib.DEQUANT_PER_OP,
     row_start: Optional[torch.Tensor] = None,
+    token_capacity: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Single-token page attention, ``query [B, Hq, 1, D] -> [B, Hq, 1, D]``.
 
@@ -122,7 +131,8 @@ def fused_dart_attention(
 
     ``row_start`` (``[B]`` integers, not in the reference) masks the tokens before every row's first live one:
     left-padded batches of unequal prompts decode through the packed path instead of falling back to dense.
-    It applies to the single-token call only.
+    It applies to the single-token call only.  ``token_capacity`` and ``out`` (a ``[B, Hq, D]`` tensor that takes
+    the result) serve calls captured in a CUDA graph: see ``decode_attention``.
     """
 
     if query.ndim != 4:
@@ -157,7 +167,8 @@ def fused_dart_attention(
             if run.first_page_index < 0 or run.first_page_index + run.page_count > total:
                 raise ValueError("page_run is outside the current cache page range")
             starts.add(run.first_page_index)
-    return decode_attention(query[:, :, 0], cache, scale=scale, flavour=flavour, row_start=row_start).unsqueeze(2)
+    return decode_attention(query[:, :, 0], cache, scale=scale, flavour=flavour, row_start=row_start,
+                            token_capacity=token_capacity, out=out).unsqueeze(2)
 
 
 __all__ = ["fused_dart_attention", "decode_attention"]

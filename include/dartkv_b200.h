@@ -134,7 +134,8 @@ typedef struct dartkv_cache_desc {
   void* v_meta;            /* [B,H,max_value_tokens,2,value_groups] md_dtype: scale row then zero row */
   int32_t* page_start;     /* [max_key_pages] first token of each key page */
   int32_t* page_tokens;    /* [max_key_pages] tokens in each key page */
-  int32_t* state;          /* [8]: seen, key_pages, k_packed_end, v_packed_end, sink_filled, 0.. */
+  int32_t* state;          /* [32]: seen, key_pages, k_packed_end, v_packed_end, sink_filled, 0, 0, 0, then the
+                            * plan of a device-planned append (16 words) */
 } dartkv_cache_desc;
 
 /* Fill the byte-geometry fields from the configuration fields. */
@@ -182,6 +183,18 @@ int dartkv_cache_append_step(const dartkv_cache_desc* desc, const dartkv_lifecyc
                              dartkv_lifecycle_state* state, const void* keys, const void* values, int chunk_tokens,
                              int64_t stride_b, int64_t stride_h, int64_t stride_t, const int32_t* indices,
                              int32_t* nonfinite, dartkv_append_plan* plan_out, void* stream);
+/* The same step planned on the device (no counterpart in the reference, whose page bookkeeping is Python,
+ * src/dart/cache.py:403-470): a one-thread kernel runs the planner on the lifecycle state the cache keeps in
+ * desc->state[0..3] and leaves the plan in desc->state[8..23], where the page, value-row and copy kernels that
+ * follow on the stream read it.  Every launch has the same shape whatever the state, so append + decode attention
+ * can be captured in a CUDA graph once and replayed token after token (give dartkv_decode_attention the token
+ * capacity as `tokens`: the kernels read the exact count from desc->state).  For the held-page lifecycle
+ * (hold_partial_pages, no local tokens) on the geometry of the page kernels (head_dim 128, 16-bit data, 128-token
+ * pages and key groups, 16-byte aligned inputs), promoted channels selected by magnitude.  The caller keeps the
+ * pools large enough (dartkv_lifecycle_plan on a host copy of the state tells what a step needs). */
+int dartkv_cache_append_device_planned(const dartkv_cache_desc* desc, const dartkv_lifecycle_config* cfg,
+                                       const void* keys, const void* values, int chunk_tokens, int64_t stride_b,
+                                       int64_t stride_h, int64_t stride_t, int32_t* nonfinite, void* stream);
 
 /* Materialize tokens [t0, t1) of the cache as dense [B,H,t1-t0,D] tensors (cache.get(),
  * src/dart/cache.py:192-199); side 0 = keys, 1 = values. */
