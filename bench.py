@@ -446,6 +446,62 @@ def other_geometry_decode(device: torch.device, steps: int, peak: float) -> list
     return results
 
 
+def decode_step_graph(device: torch.device, batch: int = 32, ctx: int = 8192, steps: int = 64) -> dict:
+    """One generation step of a layer: append the new token's K and V, then decode attention.  Eager (host-planned
+    append through the Python mirror, two library calls per step) against one CUDA graph that holds the
+    device-planned append and the attention, captured once and replayed.  Config 3's shape is bound by the decode
+    kernel either way; the shape of one Qwen3-8B layer in config 4 (batch 8, context 1024) is bound by the host."""
+
+    import dartkv_b200 as dart
+
+    cache, query = build_device_cache(range(batch), ctx, WORKLOADS["config3"]["seed"], device)
+    capacity = ctx + 4 * steps + 256
+    gen = torch.Generator(device=device).manual_seed(11)
+    shape = (batch, GEOM["kv_heads"], 1, GEOM["head_dim"])
+    new_k = torch.randn(shape, generator=gen, device=device).to(torch.bfloat16)
+    new_v = torch.randn(shape, generator=gen, device=device).to(torch.bfloat16)
+    out = torch.empty(batch, GEOM["query_heads"], GEOM["head_dim"], dtype=torch.bfloat16, device=device)
+    start_evt, stop_evt = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def eager_step():
+        cache.append(new_k, new_v)
+        dart.fused_dart_attention(query, cache, fallback=False, out=out)
+
+    def planned_step():
+        cache.append_device_planned(new_k, new_v)
+        dart.fused_dart_attention(query, cache, fallback=False, out=out, token_capacity=capacity)
+
+    cache._ensure_capacity(capacity // GEOM["page"] + 2, capacity)   # pools may not move under the graph
+    for _ in range(3):
+        eager_step()
+    torch.cuda.synchronize(device)
+    start_evt.record()
+    for _ in range(steps):
+        eager_step()
+    stop_evt.record()
+    torch.cuda.synchronize(device)
+    eager_us = start_evt.elapsed_time(stop_evt) / steps * 1e3
+    planned_step()
+    torch.cuda.synchronize(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        planned_step()
+    graph.replay()
+    torch.cuda.synchronize(device)
+    start_evt.record()
+    for _ in range(steps):
+        cache.advance_device_planned(1)
+        graph.replay()
+    stop_evt.record()
+    torch.cuda.synchronize(device)
+    graph_us = start_evt.elapsed_time(stop_evt) / steps * 1e3
+    status = cache.decode_status()
+    del graph, cache
+    torch.cuda.empty_cache()
+    return {"what": f"append of one token per row + decode attention, batch {batch}, context {ctx} and growing",
+            "eager_us_per_step": eager_us, "cuda_graph_us_per_step": graph_us, "steps": steps, "decode_status": status}
+
+
 def reference_gpu_decode(wl, device: torch.device, steps: int) -> dict:
     """The reference's own Triton decode kernel (fused_dart_attention, fallback off) on this GPU, on a bounded
     sample of the workload: min(batch, 8) rows at full context, cache built by the reference's own append."""
@@ -722,6 +778,7 @@ def gpu_arm(args, wl) -> None:
         torch.cuda.empty_cache()
         if GEOM == HEADLINE:
             extra["other_geometries"] = other_geometry_decode(device, args.steps, peak)
+            extra["decode_step_graph"] = [decode_step_graph(device, 32, 8192), decode_step_graph(device, 8, 1024)]
         extra["append"] = append_microbench(device, steps=3, warmup=1)
         cpu = CpuDecode(wl["ctx"], wl["seed"], rows=1)
         step_s = cpu.time_steps(3, 1)
