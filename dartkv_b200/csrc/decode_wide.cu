@@ -70,9 +70,6 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
 template <int DT> __device__ __forceinline__ constexpr uint32_t magic16(int p) {
   return DT == DARTKV_F16 ? (uint32_t)(25 - p) << 10 : (uint32_t)(134 - p) << 7;
 }
-template <int DT> __device__ __forceinline__ constexpr float magic_value(int p) {
-  return DT == DARTKV_F16 ? (float)(1 << (10 - p)) : (float)(1 << (7 - p));
-}
 
 // One (scale, zero point) pair made ready for a run of code pairs whose codes sit at bit position PA or PB of
 // their 16-bit halves.
