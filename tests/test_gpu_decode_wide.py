@@ -106,6 +106,12 @@ def test_lifecycle_and_token_by_token_appends():
              value_local_tokens=128, chunks=[32 + 3 * 128 + 40] + [1] * 30)
     run_case(torch.bfloat16, bits=8, promote_ratio=0.25, seed=61, batch=1, tokens=32 + 2 * 128 + 50,
              chunks=[7, 25, 128, 100, 28, 50])
+    # tokens packed on one side only, with several key groups per page and small value groups
+    run_case(torch.float16, bits=4, key_group_size=32, value_group_size=32, seed=62, batch=1,
+             tokens=32 + 3 * 128 + 40 + 30, local_tokens=1, value_local_tokens=128, chunks=[32 + 3 * 128 + 40] + [1] * 30)
+    run_case(torch.bfloat16, bits=2, promote_ratio=0.25, key_group_size=64, value_group_size=16, seed=63, batch=1,
+             tokens=32 + 2 * 128 + 100 + 20, local_tokens=1, value_local_tokens=128, chunks=[32 + 2 * 128 + 100] + [1] * 20,
+             flavour=_lib.DEQUANT_FP32)
 
 
 @pytest.mark.parametrize("split", ["aligned", "unaligned:5"])
