@@ -354,9 +354,10 @@ class DartKVCache:
         cache, so the call can sit in a CUDA graph (together with the decode attention) that is captured once and
         replayed for every new token.  No counterpart in the reference, whose page bookkeeping is Python.
 
-        For the held-page lifecycle on the geometry of the page kernels (``hold_partial_pages=True``, no local
-        tokens, head_dim 128, 16-bit data, 128-token pages and key groups, magnitude selection) and an initialized
-        cache (the first chunk goes through ``append``).  Pools cannot grow under a captured graph: create the cache
+        For the lifecycles that only pack full pages (``hold_partial_pages``, ``local_tokens``,
+        ``value_local_tokens``) on the geometry of the page kernels (head_dim 128, 16-bit data, 128-token pages and
+        key groups, magnitude selection) and an initialized cache: the first chunk goes through ``append``, and so
+        does the one-token step that re-quantizes the boundary page right after a prompt (``ValueError`` here).  Pools cannot grow under a captured graph: create the cache
         with ``max_tokens``; outside a capture the pools grow here as in ``append``.  Under a capture this method
         records the launches once; on every replay call ``advance_device_planned(chunk)`` so that the host-side
         bookkeeping follows.
@@ -394,6 +395,9 @@ class DartKVCache:
         state = _lib.LifecycleStateC(self._c_state.seen, self._c_state.k_packed_end, self._c_state.v_packed_end,
                                      self._c_state.key_pages)
         check(LIB.dartkv_lifecycle_plan(ctypes.byref(self._c_cfg), ctypes.byref(state), chunk, ctypes.byref(plan)))
+        if plan.requantize_last_page:
+            raise ValueError("this step re-quantizes the boundary page (the first one-token append after a prompt that "
+                             "ended on a page boundary): run it through append()")
         rows_needed = plan.value_end - cfg.sink_tokens if plan.value_end > plan.value_begin else 0
         if plan.key_pages_after > d.max_key_pages or rows_needed > d.max_value_tokens:
             if torch.cuda.is_current_stream_capturing():

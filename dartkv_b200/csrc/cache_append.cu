@@ -655,6 +655,9 @@ extern "C" int dartkv_cache_append_step(const dartkv_cache_desc* desc, const dar
 // row and copy kernels that follow on the stream read it there.  Their grids cover the most a chunk of this length
 // can bring, blocks beyond the step's real work return at once.  Every launch has the same shape whatever the
 // state, so a decode step (append + attention) can be captured in a CUDA graph once and replayed token after token.
+// One step of the reference's lifecycle is not served: the one-token append that re-quantizes the boundary page
+// (src/dart/cache.py:427-439) can only be the first append after a prompt, and the host, whose copy of the state
+// tells it so, sends that one through the host-planned path.
 __global__ void plan_append_kernel(dartkv_cache_desc d, dartkv_lifecycle_config cfg, int chunk_tokens) {
   dartkv_lifecycle_state state{d.state[0], d.state[2], d.state[3], d.state[1]};
   dartkv_append_plan plan;
@@ -670,8 +673,10 @@ extern "C" int dartkv_cache_append_device_planned(const dartkv_cache_desc* desc,
   if (rc) return rc;
   DARTKV_REQUIRE(cfg != nullptr && keys != nullptr && values != nullptr, "append received a null pointer");
   DARTKV_REQUIRE(chunk_tokens > 0 && chunk_tokens <= 32768, "device-planned appends take 1..32768 tokens");
-  DARTKV_REQUIRE(cfg->hold_partial_pages && cfg->local_tokens == 0 && cfg->value_local_tokens == 0,
-                 "device-planned appends serve the held-page lifecycle (hold_partial_pages, no local tokens)");
+  DARTKV_REQUIRE(cfg->hold_partial_pages || cfg->local_tokens > 0 || cfg->value_local_tokens > 0,
+                 "device-planned appends serve the lifecycles that only pack full pages (hold_partial_pages, local_tokens or "
+                 "value_local_tokens)");
+  DARTKV_REQUIRE(cfg->local_tokens >= 0 && cfg->value_local_tokens >= 0, "bad lifecycle configuration");
   DARTKV_REQUIRE(cfg->page_size == desc->page_size && cfg->sink_tokens == desc->sink_tokens,
                  "lifecycle configuration and descriptor disagree");
   const dartkv_cache_desc& d = *desc;
@@ -682,7 +687,7 @@ extern "C" int dartkv_cache_append_device_planned(const dartkv_cache_desc* desc,
   most.num_pages = chunk_tokens / d.page_size + 1;
   most.last_page_tokens = d.page_size;
   most.value_begin = 0;
-  most.value_end = most.num_pages * d.page_size;
+  most.value_end = most.num_pages * d.page_size + chunk_tokens;   // whole pages, or token by token behind a local window
   const int fast = dartkv_append_fast_supported(desc, &most, stride_t);
   DARTKV_REQUIRE(fast == 3 && stride_b % 8 == 0 && stride_h % 8 == 0 && ((uintptr_t)keys | (uintptr_t)values) % 16 == 0,
                  "device-planned appends need the geometry of the page kernels (head_dim 128, 16-bit data, 128-token "

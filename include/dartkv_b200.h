@@ -188,10 +188,12 @@ int dartkv_cache_append_step(const dartkv_cache_desc* desc, const dartkv_lifecyc
  * desc->state[0..3] and leaves the plan in desc->state[8..23], where the page, value-row and copy kernels that
  * follow on the stream read it.  Every launch has the same shape whatever the state, so append + decode attention
  * can be captured in a CUDA graph once and replayed token after token (give dartkv_decode_attention the token
- * capacity as `tokens`: the kernels read the exact count from desc->state).  For the held-page lifecycle
- * (hold_partial_pages, no local tokens) on the geometry of the page kernels (head_dim 128, 16-bit data, 128-token
- * pages and key groups, 16-byte aligned inputs), promoted channels selected by magnitude.  The caller keeps the
- * pools large enough (dartkv_lifecycle_plan on a host copy of the state tells what a step needs). */
+ * capacity as `tokens`: the kernels read the exact count from desc->state).  For the lifecycles that only pack
+ * full pages (hold_partial_pages, local_tokens, value_local_tokens) on the geometry of the page kernels (head_dim
+ * 128, 16-bit data, 128-token pages and key groups, 16-byte aligned inputs), promoted channels selected by magnitude.
+ * The caller keeps the pools large enough and sends a step that re-quantizes the boundary page (it can only be the
+ * first append after a prompt) through dartkv_cache_append_step: dartkv_lifecycle_plan on a host copy of the state
+ * tells both. */
 int dartkv_cache_append_device_planned(const dartkv_cache_desc* desc, const dartkv_lifecycle_config* cfg,
                                        const void* keys, const void* values, int chunk_tokens, int64_t stride_b,
                                        int64_t stride_h, int64_t stride_t, int32_t* nonfinite, void* stream);

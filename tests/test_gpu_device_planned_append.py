@@ -40,7 +40,9 @@ def pools_equal(a, b):
 
 
 @pytest.mark.parametrize("chunk", [1, 7, 128, 300])
-@pytest.mark.parametrize("overrides", [dict(), dict(promote_ratio=0.0, bits=4), dict(value_group_size=128, sink_tokens=0)])
+@pytest.mark.parametrize("overrides", [dict(), dict(promote_ratio=0.0, bits=4), dict(value_group_size=128, sink_tokens=0),
+                                       dict(local_tokens=1, value_local_tokens=128), dict(local_tokens=5),
+                                       dict(hold_partial_pages=False, value_local_tokens=64)])
 def test_same_bytes_as_the_host_planned_append(chunk, overrides):
     tokens = 40 + 3 * 128 + 2 * chunk + 70
     keys, values, query = make_kvq(3, 2, 2, tokens, 128, query_heads=8, dtype=torch.bfloat16)
@@ -122,8 +124,18 @@ def test_what_device_planned_appends_refuse():
     keys, values = keys.cuda(), values.cuda()
     with pytest.raises(ValueError, match="first chunk"):
         new_cache().append_device_planned(keys, values)
+    flushing = new_cache(hold_partial_pages=False)
+    flushing.append(keys[:, :, :40], values[:, :, :40])
+    with pytest.raises(ValueError, match="only pack full pages"):
+        flushing.append_device_planned(keys[:, :, 40:41], values[:, :, 40:41])
+    assert flushing.seen_tokens == 40      # a refused step leaves the bookkeeping where it was
+    # Kitty lifecycle, prompt ending on a page boundary: the next one-token step re-quantizes that page
+    big_k, big_v, _ = make_kvq(8, 1, 2, 32 + 128 + 1, 128, query_heads=8, dtype=torch.bfloat16)
     kitty = new_cache(local_tokens=1, value_local_tokens=128)
-    kitty.append(keys[:, :, :40], values[:, :, :40])
-    with pytest.raises(ValueError, match="held-page lifecycle"):
-        kitty.append_device_planned(keys[:, :, 40:41], values[:, :, 40:41])
-    assert kitty.seen_tokens == 40      # a refused step leaves the bookkeeping where it was
+    kitty.append(big_k[:, :, :160].cuda(), big_v[:, :, :160].cuda())
+    with pytest.raises(ValueError, match="re-quantizes"):
+        kitty.append_device_planned(big_k[:, :, 160:].cuda(), big_v[:, :, 160:].cuda())
+    assert kitty.seen_tokens == 160
+    kitty.append(big_k[:, :, 160:].cuda(), big_v[:, :, 160:].cuda())
+    kitty.append_device_planned(big_k[:, :, 160:].cuda(), big_v[:, :, 160:].cuda())   # later steps are fine
+    assert kitty.seen_tokens == 162
