@@ -863,8 +863,8 @@ def qwen3_decode(args) -> None:
         spans.append((start, stop))
         return out
 
-    def run(measure: bool):
-        cache = DartHFCache(cfg, max_tokens=prompt_len + new_tokens + 128)
+    def run(measure: bool, graph_decode: bool = False):
+        cache = DartHFCache(cfg, max_tokens=prompt_len + new_tokens + 128, graph_decode=graph_decode)
         with torch.no_grad():
             logits = model(prompt, past_key_values=cache, use_cache=True).logits[:, -1]
             token = logits.argmax(-1, keepdim=True)
@@ -889,6 +889,11 @@ def qwen3_decode(args) -> None:
     with ClockSampler(0) as clocks:
         ms, launches, cache = run(True)
     hot_ms = sum(a.elapsed_time(b) for a, b in spans)
+    # the same run with every layer's generation step (cache update + attention) replayed from a CUDA graph
+    graph_ms, graph_launches, graph_cache = run(False, graph_decode=True)
+    graph_status = max(graph_cache.layer_for_attention(i).decode_status() for i in (0, config.num_hidden_layers - 1))
+    del graph_cache
+    torch.cuda.empty_cache()
     reference_gpu = reference_qwen3_decode(config, prompt, device, min(new_tokens, 16))
     line = {
         "metric": "qwen3_8b_arch_decode_tokens_per_s", "value": batch * new_tokens / (ms * 1e-3), "unit": "tokens/s",
@@ -898,6 +903,10 @@ def qwen3_decode(args) -> None:
                    "batch": batch, "prompt": prompt_len, "new_tokens": new_tokens,
                    "cache": "2-bit + 0.25 promotion, page 128, groups 128/64, 32 sinks, local 1, value local 128, fp16 metadata (the setting of the reference's benchmark script)"},
         "attention_share_of_step": hot_ms / ms, "hot_path_ms_per_step": hot_ms / new_tokens,
+        "graph_decode": {"value": batch * new_tokens / (graph_ms * 1e-3), "unit": "tokens/s",
+                         "ms_per_step": graph_ms / new_tokens, "decode_status": graph_status,
+                         "what": "DartHFCache(graph_decode=True): from the third generated token on, every layer "
+                                 "replays one CUDA graph holding the device-planned append and the decode attention"},
         "reference_gpu": reference_gpu,
         "compression_ratio": cache.compression_ratio, "gpu_launches": int(launches), "clocks": clocks.summary(),
         "e2e": {"value": batch * new_tokens / (ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 0,

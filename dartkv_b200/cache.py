@@ -369,7 +369,7 @@ class DartKVCache:
             raise ValueError("the first chunk of a cache goes through append(); device-planned appends follow it")
         keys, values = key_states.detach(), value_states.detach()
         if keys.stride(-1) != 1 or values.stride() != keys.stride():
-            raise ValueError("device-planned appends take key and value chunks with equal strides and a contiguous head_dim")
+            keys, values = keys.contiguous(), values.contiguous()
         cfg = self.config
         if cfg.promote_ratio > 0.0 and cfg.channel_selection != "magnitude":
             raise ValueError("device-planned appends select promoted channels by magnitude")

@@ -22,18 +22,84 @@ except ImportError as exc:  # pragma: no cover - exercised only without the opti
     raise ImportError("DartHFCache requires transformers; install the model dependencies first.") from exc
 
 
+class _LayerDecodeGraph:
+    """One layer's generation step as a CUDA graph: device-planned append of the new token + decode attention."""
+
+    def __init__(self) -> None:
+        self.graph = None
+        self.k_in = self.v_in = self.q_in = self.out = self.row_start = None
+        self.capacity = 0
+        self.pointers = ()
+
+    @staticmethod
+    def _pool_pointers(layer: DartKVCache):
+        return tuple(pool.data_ptr() for pool in layer._pools.values())
+
+    @classmethod
+    def capture(cls, layer: DartKVCache, query, keys, values, scale: float, row_start, capacity: int):
+        """Capture the step for ``layer`` with the current inputs and run it once (the caller has seen the layer
+        take a device-planned append before)."""
+
+        from ..fused_attention import fused_dart_attention
+
+        self = cls()
+        self.capacity = int(capacity)
+        self.k_in, self.v_in, self.q_in = torch.empty_like(keys), torch.empty_like(values), torch.empty_like(query)
+        self.out = torch.empty(query.shape[0], query.shape[1], query.shape[3], dtype=query.dtype, device=query.device)
+        self.row_start = torch.zeros(query.shape[0], dtype=torch.int32, device=query.device)
+        self._load(query, keys, values, row_start)
+        layer.decode_workspace(query.shape[1])          # allocated outside the capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            layer.append_device_planned(self.k_in, self.v_in)
+            fused_dart_attention(self.q_in, layer, scale=scale, fallback=False, row_start=self.row_start,
+                                 token_capacity=self.capacity, out=self.out)
+        self.graph = graph
+        self.pointers = self._pool_pointers(layer)
+        graph.replay()      # the capture recorded the step (and the bookkeeping counted it): now run it
+        return self
+
+    def _load(self, query, keys, values, row_start) -> None:
+        self.q_in.copy_(query)
+        self.k_in.copy_(keys)
+        self.v_in.copy_(values)
+        if row_start is not None:
+            self.row_start.copy_(row_start)
+            self.padded = True
+        elif self.padded:
+            self.row_start.zero_()
+            self.padded = False
+
+    padded = False
+
+    def usable(self, layer: DartKVCache, query) -> bool:
+        return (layer.seen_tokens + 1 <= self.capacity and query.shape == self.q_in.shape
+                and self.pointers == self._pool_pointers(layer))
+
+    def replay(self, layer: DartKVCache, query, keys, values, row_start) -> torch.Tensor:
+        self._load(query, keys, values, row_start)
+        layer.advance_device_planned(1)
+        self.graph.replay()
+        return self.output()
+
+    def output(self) -> torch.Tensor:
+        return self.out.unsqueeze(2)
+
+
 class DartHFCache(Cache):
     """A Transformers cache whose layers are packed Dart caches.
 
     ``update`` returns dense tensors for the standard attention backends unless the caller passes
     ``{"dart_fused_attention": True}`` in ``cache_kwargs`` (the fused decode hook does), in which
     case only the new K/V come back and nothing is materialized.  ``max_tokens`` pre-sizes every
-    layer's pools.
+    layer's pools.  ``graph_decode=True`` (needs ``max_tokens``; not in the reference) lets the decode hook replay
+    one CUDA graph per layer for the cache update and the attention of a generation step, see ``decode_step``.
     """
 
     is_compileable = False
 
-    def __init__(self, config: Optional[DartKVCacheConfig] = None, *, max_tokens: Optional[int] = None) -> None:
+    def __init__(self, config: Optional[DartKVCacheConfig] = None, *, max_tokens: Optional[int] = None,
+                 graph_decode: bool = False) -> None:
         parameters = inspect.signature(Cache.__init__).parameters
         if "layers" in parameters:
             super().__init__(layers=[])      # Transformers 5.x wants an explicit (empty) layer list
@@ -44,6 +110,10 @@ class DartHFCache(Cache):
         self._layers: Dict[int, DartKVCache] = {}
         self._last_update_prefill: Dict[int, bool] = {}
         self._seen_tokens = 0
+        if graph_decode and max_tokens is None:
+            raise ValueError("graph_decode needs max_tokens: the pools of a captured graph cannot grow")
+        self.graph_decode = bool(graph_decode)
+        self._decode_graphs: Dict[int, "_LayerDecodeGraph"] = {}
 
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
                cache_kwargs: Optional[dict] = None, *args, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
@@ -68,6 +138,52 @@ class DartHFCache(Cache):
         # append copies what it keeps (sink / ring rows) or packs it, so the inputs need no clone
         layer.append(key_states, value_states)
         return keys_to_return, values_to_return
+
+    def decode_step(self, query_states: torch.Tensor, key_states: torch.Tensor, value_states: torch.Tensor,
+                    layer_idx: int, *, scale: float, row_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Cache update and fused attention of one generation step of a layer: ``query [B,Hq,1,D]``, new
+        ``key/value [B,H,1,D]`` -> attention output ``[B,Hq,1,D]``.
+
+        With ``graph_decode`` the layer's second step after the prompt is captured in a CUDA graph (device-planned
+        append + decode attention sized for ``max_tokens``) that later steps replay: the inputs are copied into the
+        graph's buffers, the host only advances its bookkeeping.  The result is a view of the graph's output
+        buffer, valid until the layer's next step.  Steps the graph cannot take (the first one after the prompt,
+        a configuration outside the device-planned append, tokens beyond ``max_tokens``) run eagerly.
+        """
+
+        from ..fused_attention import fused_dart_attention
+
+        if layer_idx == 0:
+            self._seen_tokens += key_states.shape[-2]
+        layer = self.layer_for_attention(layer_idx)
+        self._last_update_prefill[layer_idx] = False
+        single = key_states.shape[-2] == 1 and query_states.shape[-2] == 1
+        graph = self._decode_graphs.get(layer_idx) if self.graph_decode and single else False
+        if isinstance(graph, _LayerDecodeGraph):
+            if graph.usable(layer, query_states):
+                return graph.replay(layer, query_states, key_states, value_states, row_start)
+        elif graph is None and getattr(layer, "_decoded_once", False):
+            # second step after the prompt: see whether this layer takes device-planned appends at all
+            try:
+                layer.append_device_planned(key_states, value_states)
+                self._decode_graphs[layer_idx] = "capture next"
+            except ValueError:
+                self._decode_graphs[layer_idx] = False      # eager from now on
+                layer.append(key_states, value_states)
+            return fused_dart_attention(query_states, layer, scale=scale, fallback=False, row_start=row_start)
+        elif graph == "capture next" and layer.seen_tokens + 1 <= self._max_tokens:
+            graph = _LayerDecodeGraph.capture(layer, query_states, key_states, value_states, scale, row_start,
+                                              self._max_tokens)
+            self._decode_graphs[layer_idx] = graph
+            return graph.output()
+        layer.append(key_states, value_states)
+        layer._decoded_once = True
+        return fused_dart_attention(query_states, layer, scale=scale, fallback=False, row_start=row_start)
+
+    def has_layer(self, layer_idx: int) -> bool:
+        """True once the layer's cache exists, i.e. after its prefill."""
+
+        return layer_idx in self._layers
 
     def layer_for_attention(self, layer_idx: int) -> DartKVCache:
         """A layer's packed cache for the fused attention hook."""

@@ -83,6 +83,17 @@ def build_dart_qwen3_attention_class():
             query_states, key_states = modules.apply_rotary_pos_emb(query_states, key_states, cos, sin)
 
             use_dart_decode = isinstance(cache, DartHFCache)
+            output_attentions = bool(kwargs.get("output_attentions", False))
+            if (use_dart_decode and cache.graph_decode and query_states.shape[-2] == 1 and not output_attentions
+                    and cache.has_layer(self.layer_idx)):
+                # cache update + packed attention of the step in one call (a CUDA graph per layer after the first steps)
+                layer = cache.layer_for_attention(self.layer_idx)
+                row_start = decode_row_start(cache, attention_mask, layer.get_seq_length() + 1)
+                if row_start is not False:
+                    attn_output = cache.decode_step(query_states, key_states, value_states, self.layer_idx,
+                                                    scale=self.scaling, row_start=row_start).transpose(1, 2)
+                    attn_output = attn_output.reshape(*input_shape, -1).contiguous()
+                    return self.o_proj(attn_output), None
             if cache is not None:
                 if use_dart_decode:
                     cache_kwargs = {"sin": sin, "cos": cos, "cache_position": cache_position, "dart_fused_attention": True}
@@ -90,7 +101,6 @@ def build_dart_qwen3_attention_class():
                 else:
                     key_states, value_states = cache.update(key_states, value_states, self.layer_idx)
 
-            output_attentions = bool(kwargs.get("output_attentions", False))
             fused_decode = (use_dart_decode and not cache.last_update_was_prefill(self.layer_idx)
                             and query_states.shape[-2] == 1 and not output_attentions)
             row_start = None

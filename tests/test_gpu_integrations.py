@@ -166,3 +166,65 @@ def test_fused_hook_honours_the_attention_mask(hole, monkeypatch):
         assert fused_calls == []                                    # both layers took the dense path
     else:
         assert [starts.tolist() for starts in fused_calls] == [[5, 0, 1]] * 2      # one packed call per layer
+
+
+def test_graph_decode_replays_the_layer_step_and_agrees_with_the_eager_hook():
+    """``DartHFCache(graph_decode=True)``: after the first two steps every layer replays one CUDA graph (append planned
+    on the device + decode attention); the logits follow the eager hook (the work split of the attention differs,
+    so sums are reordered) and the packed caches are byte-equal."""
+
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    from dartkv_b200.integrations.huggingface import _LayerDecodeGraph
+
+    torch.manual_seed(0)
+    config = Qwen3Config(vocab_size=97, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=1024)
+    config._attn_implementation = "eager"
+    model = attach_dart_fused_attention(Qwen3ForCausalLM(config).to(torch.bfloat16).cuda().eval())
+    cfg = dart.DartKVCacheConfig(bits=2, promote_ratio=0.25, page_size=128, key_group_size=128, value_group_size=64,
+                                 sink_tokens=32, hold_partial_pages=True, local_tokens=1, value_local_tokens=128,
+                                 metadata_dtype=torch.float16)
+    prompt = torch.randint(0, 97, (2, 32 + 128 + 40)).cuda()
+    steps = 150
+    eager, graphed = DartHFCache(cfg), DartHFCache(cfg, max_tokens=prompt.shape[1] + steps + 8, graph_decode=True)
+    with torch.no_grad():
+        logits_e = model(prompt, past_key_values=eager, use_cache=True).logits[:, -1]
+        logits_g = model(prompt, past_key_values=graphed, use_cache=True).logits[:, -1]
+        assert torch.equal(logits_e, logits_g)
+        for step in range(steps):
+            nxt = logits_e.argmax(-1, keepdim=True)
+            logits_e = model(nxt, past_key_values=eager, use_cache=True).logits[:, -1]
+            logits_g = model(nxt, past_key_values=graphed, use_cache=True).logits[:, -1]
+            torch.testing.assert_close(logits_g.float(), logits_e.float(), rtol=2e-2, atol=2e-2)
+    assert all(isinstance(graphed._decode_graphs[i], _LayerDecodeGraph) for i in range(2))
+    assert graphed.get_seq_length() == eager.get_seq_length() == prompt.shape[1] + steps
+    for index in range(2):
+        a, b = eager.layer_for_attention(index), graphed.layer_for_attention(index)
+        assert a.segment_table() == b.segment_table()
+        keys_a, values_a = a.get()
+        keys_b, values_b = b.get()
+        # layer 0 sees identical inputs: identical bytes; deeper layers inherit the reordered sums of the layers before
+        if index == 0:
+            assert torch.equal(keys_a, keys_b) and torch.equal(values_a, values_b)
+        assert b.decode_status() == 0
+
+
+def test_graph_decode_needs_max_tokens_and_falls_back_where_the_geometry_does_not_fit():
+    with pytest.raises(ValueError, match="max_tokens"):
+        DartHFCache(dart.DartKVCacheConfig(), graph_decode=True)
+    model = attach_dart_fused_attention(tiny_model(8, torch.float32))      # head_dim 8: generic kernels, eager steps
+    cfg = dart.DartKVCacheConfig(bits=4, page_size=4, hold_partial_pages=True, key_group_size=4, value_group_size=8,
+                                 sink_tokens=1, promote_ratio=0.25, metadata_dtype=torch.float32)
+    torch.manual_seed(4)
+    prompt = torch.randint(0, 97, (2, 9)).cuda()
+    plain, graphed = DartHFCache(cfg), DartHFCache(cfg, max_tokens=64, graph_decode=True)
+    with torch.no_grad():
+        a = model(prompt, past_key_values=plain, use_cache=True).logits[:, -1]
+        b = model(prompt, past_key_values=graphed, use_cache=True).logits[:, -1]
+        for _ in range(6):
+            nxt = a.argmax(-1, keepdim=True)
+            a = model(nxt, past_key_values=plain, use_cache=True).logits[:, -1]
+            b = model(nxt, past_key_values=graphed, use_cache=True).logits[:, -1]
+            assert torch.equal(a, b)
+    assert graphed._decode_graphs == {0: False, 1: False}
