@@ -228,3 +228,42 @@ def test_graph_decode_needs_max_tokens_and_falls_back_where_the_geometry_does_no
             b = model(nxt, past_key_values=graphed, use_cache=True).logits[:, -1]
             assert torch.equal(a, b)
     assert graphed._decode_graphs == {0: False, 1: False}
+
+
+def test_graph_decode_with_a_left_padded_batch():
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    from dartkv_b200.integrations.huggingface import _LayerDecodeGraph
+
+    torch.manual_seed(1)
+    config = Qwen3Config(vocab_size=97, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=1024)
+    config._attn_implementation = "eager"
+    model = attach_dart_fused_attention(Qwen3ForCausalLM(config).to(torch.bfloat16).cuda().eval())
+    cfg = dart.DartKVCacheConfig(bits=2, promote_ratio=0.25, page_size=128, key_group_size=128, value_group_size=64,
+                                 sink_tokens=32, hold_partial_pages=True, metadata_dtype=torch.bfloat16)
+    length, steps = 32 + 128 + 20, 12
+    prompt = torch.randint(0, 97, (2, length)).cuda()
+    mask = torch.ones(2, length, dtype=torch.long).cuda()
+    mask[0, :37] = 0
+    positions = (mask.cumsum(-1) - 1).clamp(min=0)
+    eager, graphed = DartHFCache(cfg), DartHFCache(cfg, max_tokens=length + steps + 8, graph_decode=True)
+    with torch.no_grad():
+        outs = []
+        for cache in (eager, graphed):
+            logits = model(prompt, attention_mask=mask, position_ids=positions, past_key_values=cache,
+                           use_cache=True).logits[:, -1]
+            step_mask, step_pos, trace = mask, positions[:, -1:], []
+            for _ in range(steps):
+                nxt = logits.argmax(-1, keepdim=True) if cache is eager else outs[0][len(trace)][0]
+                step_mask = torch.cat((step_mask, torch.ones_like(step_mask[:, :1])), dim=1)
+                step_pos = step_pos + 1
+                logits = model(nxt, attention_mask=step_mask, position_ids=step_pos, past_key_values=cache,
+                               use_cache=True).logits[:, -1]
+                trace.append((nxt, logits))
+            outs.append(trace)
+    for (tok_e, log_e), (tok_g, log_g) in zip(*outs):
+        assert torch.equal(tok_e, tok_g)
+        torch.testing.assert_close(log_g.float(), log_e.float(), rtol=2e-2, atol=2e-2)
+    assert all(isinstance(graphed._decode_graphs[i], _LayerDecodeGraph) for i in range(2))
+    assert graphed._decode_graphs[0].row_start.tolist() == [37, 0]
