@@ -894,6 +894,29 @@ def qwen3_decode(args) -> None:
     graph_status = max(graph_cache.layer_for_attention(i).decode_status() for i in (0, config.num_hidden_layers - 1))
     del graph_cache
     torch.cuda.empty_cache()
+    # and with the whole generation step (all layers, the model's own modules included) as ONE CUDA graph
+    from dartkv_b200.integrations import DartGraphedDecoder
+
+    def run_graphed():
+        cache = DartHFCache(cfg, max_tokens=prompt_len + new_tokens + 128)
+        with torch.no_grad():
+            logits = model(prompt, past_key_values=cache, use_cache=True).logits[:, -1]
+            token = logits.argmax(-1, keepdim=True)
+            decoder = DartGraphedDecoder(model, cache)
+            for _ in range(3):           # host-planned first step, warm-up, capture
+                token = decoder.step(token).argmax(-1, keepdim=True)
+            torch.cuda.synchronize(device)
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(new_tokens - 3):
+                token = decoder.step(token).argmax(-1, keepdim=True)
+            t1.record()
+            torch.cuda.synchronize(device)
+        status = max(cache.layer_for_attention(i).decode_status() for i in (0, config.num_hidden_layers - 1))
+        return t0.elapsed_time(t1) / (new_tokens - 3), status, decoder.graph is not None
+
+    step_ms, step_status, captured = run_graphed()
+    torch.cuda.empty_cache()
     reference_gpu = reference_qwen3_decode(config, prompt, device, min(new_tokens, 16))
     line = {
         "metric": "qwen3_8b_arch_decode_tokens_per_s", "value": batch * new_tokens / (ms * 1e-3), "unit": "tokens/s",
@@ -907,6 +930,10 @@ def qwen3_decode(args) -> None:
                          "ms_per_step": graph_ms / new_tokens, "decode_status": graph_status,
                          "what": "DartHFCache(graph_decode=True): from the third generated token on, every layer "
                                  "replays one CUDA graph holding the device-planned append and the decode attention"},
+        "graph_step": {"value": batch / (step_ms * 1e-3), "unit": "tokens/s", "ms_per_step": step_ms,
+                       "decode_status": step_status, "captured": captured,
+                       "what": "DartGraphedDecoder: the model's whole forward for one new token (36 layers, their "
+                               "device-planned cache appends and decode attention) replayed from one CUDA graph"},
         "reference_gpu": reference_gpu,
         "compression_ratio": cache.compression_ratio, "gpu_launches": int(launches), "clocks": clocks.summary(),
         "e2e": {"value": batch * new_tokens / (ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 0,

@@ -114,6 +114,9 @@ class DartHFCache(Cache):
             raise ValueError("graph_decode needs max_tokens: the pools of a captured graph cannot grow")
         self.graph_decode = bool(graph_decode)
         self._decode_graphs: Dict[int, "_LayerDecodeGraph"] = {}
+        # set by DartGraphedDecoder while it runs or captures whole steps: True, or the [B] first live tokens of a
+        # left-padded batch; decode steps then use device-planned appends and attention sized for max_tokens
+        self.planned_decode = None
 
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,
                cache_kwargs: Optional[dict] = None, *args, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
@@ -157,6 +160,10 @@ class DartHFCache(Cache):
             self._seen_tokens += key_states.shape[-2]
         layer = self.layer_for_attention(layer_idx)
         self._last_update_prefill[layer_idx] = False
+        if self.planned_decode is not None:
+            layer.append_device_planned(key_states, value_states)
+            return fused_dart_attention(query_states, layer, scale=scale, fallback=False, row_start=row_start,
+                                        token_capacity=self._max_tokens)
         single = key_states.shape[-2] == 1 and query_states.shape[-2] == 1
         graph = self._decode_graphs.get(layer_idx) if self.graph_decode and single else False
         if isinstance(graph, _LayerDecodeGraph):
@@ -179,6 +186,13 @@ class DartHFCache(Cache):
         layer.append(key_states, value_states)
         layer._decoded_once = True
         return fused_dart_attention(query_states, layer, scale=scale, fallback=False, row_start=row_start)
+
+    def advance_planned_decode_step(self) -> None:
+        """Host bookkeeping of one replayed generation step (every layer appended one token on the device)."""
+
+        self._seen_tokens += 1
+        for layer in self._layers.values():
+            layer.advance_device_planned(1)
 
     def has_layer(self, layer_idx: int) -> bool:
         """True once the layer's cache exists, i.e. after its prefill."""

@@ -84,11 +84,15 @@ def build_dart_qwen3_attention_class():
 
             use_dart_decode = isinstance(cache, DartHFCache)
             output_attentions = bool(kwargs.get("output_attentions", False))
-            if (use_dart_decode and cache.graph_decode and query_states.shape[-2] == 1 and not output_attentions
-                    and cache.has_layer(self.layer_idx)):
-                # cache update + packed attention of the step in one call (a CUDA graph per layer after the first steps)
+            if (use_dart_decode and (cache.graph_decode or cache.planned_decode is not None)
+                    and query_states.shape[-2] == 1 and not output_attentions and cache.has_layer(self.layer_idx)):
+                # cache update + packed attention of the step in one call (a CUDA graph per layer after the first
+                # steps, or part of a whole-step graph of DartGraphedDecoder, which cannot look into the mask)
                 layer = cache.layer_for_attention(self.layer_idx)
-                row_start = decode_row_start(cache, attention_mask, layer.get_seq_length() + 1)
+                if cache.planned_decode is not None:
+                    row_start = cache.planned_decode if torch.is_tensor(cache.planned_decode) else None
+                else:
+                    row_start = decode_row_start(cache, attention_mask, layer.get_seq_length() + 1)
                 if row_start is not False:
                     attn_output = cache.decode_step(query_states, key_states, value_states, self.layer_idx,
                                                     scale=self.scaling, row_start=row_start).transpose(1, 2)

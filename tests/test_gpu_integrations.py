@@ -267,3 +267,54 @@ def test_graph_decode_with_a_left_padded_batch():
         torch.testing.assert_close(log_g.float(), log_e.float(), rtol=2e-2, atol=2e-2)
     assert all(isinstance(graphed._decode_graphs[i], _LayerDecodeGraph) for i in range(2))
     assert graphed._decode_graphs[0].row_start.tolist() == [37, 0]
+
+
+@pytest.mark.parametrize("padded", [False, True])
+def test_whole_generation_step_as_one_cuda_graph(padded):
+    """DartGraphedDecoder: the model's forward for one new token is captured once (device-planned appends, attention
+    sized for the capacity) and replayed; tokens and logits follow the eager hook."""
+
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    from dartkv_b200.integrations import DartGraphedDecoder
+
+    torch.manual_seed(2)
+    config = Qwen3Config(vocab_size=97, hidden_size=64, intermediate_size=128, num_hidden_layers=3,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=1024)
+    config._attn_implementation = "sdpa"
+    model = attach_dart_fused_attention(Qwen3ForCausalLM(config).to(torch.bfloat16).cuda().eval())
+    cfg = dart.DartKVCacheConfig(bits=2, promote_ratio=0.25, page_size=128, key_group_size=128, value_group_size=64,
+                                 sink_tokens=32, hold_partial_pages=True, local_tokens=1, value_local_tokens=128,
+                                 metadata_dtype=torch.float16)
+    length, steps = 32 + 128, 140       # the prompt ends on a page boundary: the first step re-quantizes that page
+    prompt = torch.randint(0, 97, (2, length)).cuda()
+    mask = torch.ones(2, length, dtype=torch.long).cuda()
+    if padded:
+        mask[1, :21] = 0
+    positions = (mask.cumsum(-1) - 1).clamp(min=0)
+    eager, graphed = DartHFCache(cfg), DartHFCache(cfg, max_tokens=length + steps + 8)
+    with torch.no_grad():
+        logits_e = model(prompt, attention_mask=mask, position_ids=positions, past_key_values=eager,
+                         use_cache=True).logits[:, -1]
+        logits_g = model(prompt, attention_mask=mask, position_ids=positions, past_key_values=graphed,
+                         use_cache=True).logits[:, -1]
+        assert torch.equal(logits_e, logits_g)
+        decoder = DartGraphedDecoder(model, graphed, position_ids=positions[:, -1:] + 1,
+                                     row_start=torch.tensor([0, 21]) if padded else None)
+        step_mask, step_pos = mask, positions[:, -1:]
+        for step in range(steps):
+            nxt = logits_e.argmax(-1, keepdim=True)
+            step_mask = torch.cat((step_mask, torch.ones_like(step_mask[:, :1])), dim=1)
+            step_pos = step_pos + 1
+            logits_e = model(nxt, attention_mask=step_mask, position_ids=step_pos, past_key_values=eager,
+                             use_cache=True).logits[:, -1]
+            logits_g = decoder.step(nxt)
+            torch.testing.assert_close(logits_g.float(), logits_e.float(), rtol=3e-2, atol=3e-2)
+    assert decoder.graph is not None
+    assert graphed.get_seq_length() == eager.get_seq_length() == length + steps
+    first_e, first_g = eager.layer_for_attention(0), graphed.layer_for_attention(0)
+    assert first_e.segment_table() == first_g.segment_table()
+    keys_e, values_e = first_e.get()
+    keys_g, values_g = first_g.get()
+    assert torch.equal(keys_e, keys_g) and torch.equal(values_e, values_g)     # layer 0 sees identical inputs
+    assert all(graphed.layer_for_attention(i).decode_status() == 0 for i in range(3))
