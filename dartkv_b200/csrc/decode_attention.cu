@@ -291,9 +291,11 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_m, const floa
     for (int p = 0; p < peers.world_size; ++p) store_f(peers.out[p], out_dt, peer_row * D + c, acc * inv);
   }
   if (peers.world_size > 1) {
-    __threadfence_system();   // this thread's peer stores are visible system-wide before the block reports in
+    // the block's peer stores are ordered before the barrier; one cumulative system-scope fence after it makes
+    // them all visible system-wide before the block reports in (a fence per thread costs microseconds per wave)
     __syncthreads();
     if (threadIdx.x == 0) {
+      __threadfence_system();
       const unsigned int ticket = atomicAdd(done_counter, 1u);
       if (ticket == gridDim.x - 1) {
         *done_counter = 0;      // ready for the next call on this stream
