@@ -535,7 +535,16 @@ template <int DT>
 static int launch_keys(const dartkv_cache_desc& d, const dartkv_append_plan& p, const RowSource& src,
                        const int32_t* indices, int32_t* nonfinite, cudaStream_t stream,
                        const dartkv_append_plan* device_plan) {
+#ifdef APPEND_KEY_SPLITS_FIXED
   return launch_keys_split<DT, APPEND_KEY_SPLITS>(d, p, src, indices, nonfinite, stream, device_plan);
+#else
+  // Four token splits per page give a step of few pages more warps and a shorter critical path; with thousands of
+  // pages in flight the splits' extra combine work costs more than it hides: two splits (measured on bulk appends
+  // of bf16 [16,8,4096,128]: 123 us against 132 us; a 128-token step replayed from a graph: 10.1 against 9.9 us).
+  if ((long long)d.batch * d.kv_heads * p.num_pages >= 2048)
+    return launch_keys_split<DT, 2>(d, p, src, indices, nonfinite, stream, device_plan);
+  return launch_keys_split<DT, APPEND_KEY_SPLITS>(d, p, src, indices, nonfinite, stream, device_plan);
+#endif
 }
 
 template <int DT>
