@@ -30,6 +30,7 @@ class _LayerDecodeGraph:
         self.k_in = self.v_in = self.q_in = self.out = self.row_start = None
         self.capacity = 0
         self.pointers = ()
+        self.padded = False      # whether row_start currently holds a left padding
 
     @staticmethod
     def _pool_pointers(layer: DartKVCache):
@@ -69,8 +70,6 @@ class _LayerDecodeGraph:
         elif self.padded:
             self.row_start.zero_()
             self.padded = False
-
-    padded = False
 
     def usable(self, layer: DartKVCache, query) -> bool:
         return (layer.seen_tokens + 1 <= self.capacity and query.shape == self.q_in.shape
@@ -147,9 +146,10 @@ class DartHFCache(Cache):
         """Cache update and fused attention of one generation step of a layer: ``query [B,Hq,1,D]``, new
         ``key/value [B,H,1,D]`` -> attention output ``[B,Hq,1,D]``.
 
-        With ``graph_decode`` the layer's second step after the prompt is captured in a CUDA graph (device-planned
-        append + decode attention sized for ``max_tokens``) that later steps replay: the inputs are copied into the
-        graph's buffers, the host only advances its bookkeeping.  The result is a view of the graph's output
+        With ``graph_decode`` the layer's first step after the prompt runs eagerly, the second tries the
+        device-planned append, and the third is captured in a CUDA graph (device-planned append + decode attention
+        sized for ``max_tokens``) that later steps replay: the inputs are copied into the graph's buffers, the host
+        only advances its bookkeeping.  The result is a view of the graph's output
         buffer, valid until the layer's next step.  Steps the graph cannot take (the first one after the prompt,
         a configuration outside the device-planned append, tokens beyond ``max_tokens``) run eagerly.
         """
