@@ -57,3 +57,19 @@ def test_the_answer_is_kept_for_the_layers_of_one_step():
     assert decode_row_start(cache, mask, 9) is first
     mask[0, :3] = 0                              # modified in place: not the same step any more
     assert decode_row_start(cache, mask, 9).tolist() == [3, 0]
+
+
+def test_graphed_decoder_refuses_caches_it_cannot_replay():
+    import pytest
+
+    import dartkv_b200 as dart
+    from dartkv_b200.integrations import DartGraphedDecoder, DartHFCache
+
+    with pytest.raises(ValueError, match="max_tokens"):
+        DartGraphedDecoder(None, DartHFCache(dart.DartKVCacheConfig()))            # pools could move under the graph
+    with pytest.raises(ValueError, match="max_tokens"):
+        DartGraphedDecoder(None, object())
+    with pytest.raises(ValueError, match="prompt"):
+        DartGraphedDecoder(None, DartHFCache(dart.DartKVCacheConfig(), max_tokens=64))   # nothing cached yet
+    with pytest.raises(ValueError, match="max_tokens"):
+        DartHFCache(dart.DartKVCacheConfig(), graph_decode=True)
